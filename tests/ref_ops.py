@@ -1,0 +1,109 @@
+"""Plain PyTorch statement of every kernel, with the kernels' own calling convention.
+
+Each method computes in float32 what the CUDA kernel of the same name computes, on
+the same paged cache layout, one token at a time.  The GPU tests compare each
+kernel with its method here on sizes other than the engine's; the CPU tests run
+the engine's host logic (step function, cache manager, scheduler) through these
+methods instead of CUDA.  This class lives under tests/: the engine itself has no
+CPU path.
+"""
+from __future__ import annotations
+
+import torch
+
+F32 = torch.float32
+
+
+class RefOps:
+    name = "reference"
+
+    # ---- weights -------------------------------------------------------------------------
+    def pack_linear(self, w):
+        return w.contiguous()
+
+    def pack_gate_up(self, gate, up):
+        return torch.cat([gate, up], dim=0).contiguous()
+
+    # ---- elementwise / rowwise -----------------------------------------------------------
+    def embed(self, table, token_ids, out):
+        out.copy_(table[token_ids.long()].to(F32))
+
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        src = x if rows is None else x[rows.long()]
+        src = src.to(F32)
+        inv = torch.rsqrt((src * src).mean(dim=-1, keepdim=True) + eps)
+        out.copy_((src * inv * weight.to(F32)).to(out.dtype))
+
+    def linear(self, a, w, out, accumulate=False):
+        prod = a.to(F32) @ w.to(F32).T
+        if accumulate:
+            out.add_(prod)
+        else:
+            out.copy_(prod)
+
+    def gate_up_swiglu(self, h, w_gate_up, out):
+        inter = out.shape[1]
+        gu = h.to(F32) @ w_gate_up.to(F32).T
+        gate, up = gu[:, :inter], gu[:, inter:]
+        out.copy_((gate / (1.0 + torch.exp(-gate)) * up).to(out.dtype))
+
+    # ---- attention -----------------------------------------------------------------------
+    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+                           num_heads, num_kv_heads, head_dim):
+        t = qkv.shape[0]
+        nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+        half = head_dim // 2
+        q = qkv[:, :nq].reshape(t, num_heads, head_dim).to(F32)
+        k = qkv[:, nq:nq + nk].reshape(t, num_kv_heads, head_dim).to(F32)
+        v = qkv[:, nq + nk:].reshape(t, num_kv_heads, head_dim).to(F32)
+
+        def norm(x, w):
+            return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * w.to(F32)
+
+        ang = step.positions.to(F32)[:, None] * inv_freq.to(F32)[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+        def rot(x):
+            x0, x1 = x[..., :half], x[..., half:]
+            return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+
+        q = rot(norm(q, q_weight))
+        k = rot(norm(k, k_weight))
+        q_out.copy_(q.reshape(t, nq).to(q_out.dtype))
+        if cache.writes:
+            ps = cache.page_size
+            pos = step.positions.long()
+            page = cache.block_table[step.req_of_tok.long(), pos // ps].long()
+            cache.pages[page, 0, :, pos % ps, :] = k.to(cache.pages.dtype)
+            cache.pages[page, 1, :, pos % ps, :] = v.to(cache.pages.dtype)
+
+    def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,
+                        scale):
+        t = q.shape[0]
+        group = num_heads // num_kv_heads
+        ps = cache.page_size
+        qf = q.to(F32).reshape(t, num_heads, head_dim)
+        res = torch.empty_like(qf)
+        positions = step.positions.tolist()
+        reqs = step.req_of_tok.tolist()
+        for i in range(t):
+            pos, r = positions[i], reqs[i]
+            lo = 0 if window is None else max(0, pos - window + 1)
+            p = torch.arange(lo, pos + 1, device=q.device)
+            page = cache.block_table[r, p // ps].long()
+            k = cache.pages[page, 0, :, p % ps, :].to(F32)        # [P, kv, hd]
+            v = cache.pages[page, 1, :, p % ps, :].to(F32)
+            k = k.repeat_interleave(group, dim=1)                # [P, heads, hd]
+            v = v.repeat_interleave(group, dim=1)
+            scores = torch.einsum("hd,phd->hp", qf[i], k) * scale
+            prob = torch.softmax(scores, dim=-1)
+            res[i] = torch.einsum("hp,phd->hd", prob, v)
+        out.copy_(res.reshape(t, num_heads * head_dim).to(out.dtype))
+
+    # ---- sampling ------------------------------------------------------------------------
+    def argmax(self, logits, out):
+        # first maximum wins ties
+        mx = logits.max(dim=-1, keepdim=True).values
+        idx = torch.arange(logits.shape[1], device=logits.device).expand_as(logits)
+        big = torch.full_like(idx, logits.shape[1])
+        out.copy_(torch.where(logits == mx, idx, big).min(dim=-1).values.to(out.dtype))

@@ -1,0 +1,224 @@
+"""The cache manager: pages with a block table per request, and fixed-size state slots.
+
+Cache slots of the model's schedule are sorted into *groups*.  Slots whose mixers
+keep the same thing (same kv heads, head size and window) share one group: one
+pool of page ids, one block table per request, and one tensor
+``[slots_in_group, num_pages, 2, kv_heads, page_size, head_dim]`` (2 = keys,
+values), so that a page id addresses the same tokens in every layer of the group.
+Groups with different needs have pools of their own.  A group with a window gives
+a page back as soon as every position on it lies behind the window of the
+request's next token; all pages go back when the request ends.  Nothing is cleared
+on reuse: kernels read only positions below the request's length.
+
+Beside the pages every live request holds one *state slot*, an index into
+``[max_requests, *shape]`` tensors of the cache slots whose mixers keep state of
+fixed size.  Such state is zeroed when the slot is handed to a new request.
+
+The reference keeps one contiguous buffer per sequence, sized for ``--max-seq``
+tokens (src/inference.cu:146-148), and clears it wholesale (src/inference.cu:174-176).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Hashable, Optional, Sequence
+
+import torch
+
+from ..parts.base import FixedStateSpec, PagedKVSpec
+from .pages import IdPool, OutOfPages
+
+RELEASED = -1            # block-table entry of a page that a window has passed
+
+
+@dataclass
+class PagedKVView:
+    """What a paged mixer sees of its cache slot during one step."""
+    pages: Optional[torch.Tensor]        # [num_pages, 2, kv_heads, page_size, head_dim]
+    block_table: Optional[torch.Tensor]  # [requests, blocks] int32, RELEASED where passed
+    page_size: int
+    writes: bool
+
+
+@dataclass
+class StateView:
+    """What a mixer with fixed-size state sees of its cache slot during one step."""
+    state: Optional[torch.Tensor]        # [max_requests, *shape]
+    slots: Optional[torch.Tensor]        # [requests] int64: the state slot of each request
+    writes: bool
+
+
+class _PagedGroup:
+    def __init__(self, spec: PagedKVSpec, page_size: int, num_pages: int):
+        self.spec = spec
+        self.page_size = page_size
+        self.pool = IdPool(num_pages, "page")
+        self.cache_slots: list[int] = []
+        self.tables: dict[Hashable, list[int]] = {}
+        self.storage: Optional[torch.Tensor] = None
+
+    def blocks_for(self, length: int) -> int:
+        return -(-length // self.page_size)
+
+    def new_pages_needed(self, req, new_length: int) -> int:
+        return max(0, self.blocks_for(new_length) - len(self.tables[req]))
+
+    def first_needed_block(self, length: int) -> int:
+        """Index of the first block the token at position ``length`` may still read."""
+        if self.spec.window is None:
+            return 0
+        return max(0, length - self.spec.window + 1) // self.page_size
+
+
+class CacheManager:
+    def __init__(self, cache_specs: Sequence[PagedKVSpec | FixedStateSpec | None], *,
+                 page_size: int, num_pages: int, max_requests: int,
+                 kv_dtype: torch.dtype = torch.bfloat16, device=None):
+        if page_size < 1:
+            raise ValueError(f"page_size must be positive, got {page_size}")
+        self.page_size = page_size
+        self.num_pages = num_pages
+        self.max_requests = max_requests
+        self.kv_dtype = kv_dtype
+        self.device = device
+        self.groups: list[_PagedGroup] = []
+        self._slot_group: dict[int, tuple[int, int]] = {}      # cache slot -> (group, index in group)
+        self._state_specs: dict[int, FixedStateSpec] = {}
+        self._state_storage: dict[int, torch.Tensor] = {}
+        by_spec: dict[PagedKVSpec, int] = {}
+        for slot, spec in enumerate(cache_specs):
+            if isinstance(spec, PagedKVSpec):
+                if spec not in by_spec:
+                    by_spec[spec] = len(self.groups)
+                    self.groups.append(_PagedGroup(spec, page_size, num_pages))
+                g = by_spec[spec]
+                self._slot_group[slot] = (g, len(self.groups[g].cache_slots))
+                self.groups[g].cache_slots.append(slot)
+            elif isinstance(spec, FixedStateSpec):
+                self._state_specs[slot] = spec
+            elif spec is not None:
+                raise TypeError(f"cache slot {slot}: unknown cache spec {spec!r}")
+        self.state_slots = IdPool(max_requests, "state slot")
+        self._lengths: dict[Hashable, int] = {}
+        self._state_slot: dict[Hashable, int] = {}
+        if device is not None:
+            for g in self.groups:
+                s = g.spec
+                g.storage = torch.zeros(
+                    (len(g.cache_slots), num_pages, 2, s.num_kv_heads, page_size, s.head_dim),
+                    dtype=kv_dtype, device=device)
+            for slot, spec in self._state_specs.items():
+                self._state_storage[slot] = torch.zeros(
+                    (max_requests, *spec.shape), dtype=spec.dtype, device=device)
+
+    # ---- requests ------------------------------------------------------------------------
+    def add_request(self, req: Hashable) -> None:
+        if req in self._lengths:
+            raise KeyError(f"request {req!r} is already live")
+        slot = self.state_slots.take()
+        self._lengths[req] = 0
+        self._state_slot[req] = slot
+        for g in self.groups:
+            g.tables[req] = []
+        for t in self._state_storage.values():
+            t[slot].zero_()
+
+    def has_request(self, req: Hashable) -> bool:
+        return req in self._lengths
+
+    def live_requests(self) -> list:
+        return list(self._lengths)
+
+    def length(self, req: Hashable) -> int:
+        return self._lengths[req]
+
+    def state_slot(self, req: Hashable) -> int:
+        return self._state_slot[req]
+
+    def pages_needed(self, req: Hashable, num_tokens: int) -> list[int]:
+        """New pages each group must hand out before ``num_tokens`` more tokens fit."""
+        new_len = self._lengths[req] + num_tokens
+        return [g.new_pages_needed(req, new_len) for g in self.groups]
+
+    def can_append(self, req: Hashable, num_tokens: int) -> bool:
+        return all(n <= g.pool.num_free
+                   for n, g in zip(self.pages_needed(req, num_tokens), self.groups))
+
+    def append(self, req: Hashable, num_tokens: int) -> int:
+        """Reserve room for ``num_tokens`` more tokens; all groups or none.  Returns the start position."""
+        if num_tokens < 1:
+            raise ValueError("append needs at least one token")
+        need = self.pages_needed(req, num_tokens)
+        for n, g in zip(need, self.groups):
+            if n > g.pool.num_free:
+                raise OutOfPages(
+                    f"request {req!r} needs {n} more pages of {g.spec}, {g.pool.num_free} are free")
+        for n, g in zip(need, self.groups):
+            g.tables[req].extend(g.pool.take() for _ in range(n))
+        start = self._lengths[req]
+        self._lengths[req] = start + num_tokens
+        return start
+
+    def release_passed(self, req: Hashable) -> int:
+        """Give back pages that lie wholly behind a window.  Returns how many were freed."""
+        freed = 0
+        length = self._lengths[req]
+        for g in self.groups:
+            if g.spec.window is None:
+                continue
+            table = g.tables[req]
+            for b in range(min(g.first_needed_block(length), len(table))):
+                if table[b] != RELEASED:
+                    g.pool.give_back(table[b])
+                    table[b] = RELEASED
+                    freed += 1
+        return freed
+
+    def free_request(self, req: Hashable) -> None:
+        if req not in self._lengths:
+            raise KeyError(f"request {req!r} is not live")
+        for g in self.groups:
+            for page in g.tables.pop(req):
+                if page != RELEASED:
+                    g.pool.give_back(page)
+        self.state_slots.give_back(self._state_slot.pop(req))
+        del self._lengths[req]
+
+    # ---- what a step reads ----------------------------------------------------------------
+    def block_table(self, group: int, req: Hashable) -> list[int]:
+        return self.groups[group].tables[req]
+
+    def max_blocks(self, reqs: Sequence[Hashable]) -> int:
+        return max((len(g.tables[r]) for g in self.groups for r in reqs), default=0)
+
+    def group_of_slot(self, cache_slot: int) -> Optional[int]:
+        ent = self._slot_group.get(cache_slot)
+        return None if ent is None else ent[0]
+
+    def view(self, cache_slot: int, writes: bool, block_tables: Sequence[torch.Tensor],
+             state_slots: Optional[torch.Tensor]):
+        """The view of ``cache_slot`` for one step, given this step's device tables."""
+        if cache_slot in self._slot_group:
+            g, idx = self._slot_group[cache_slot]
+            grp = self.groups[g]
+            pages = None if grp.storage is None else grp.storage[idx]
+            return PagedKVView(pages, block_tables[g], self.page_size, writes)
+        if cache_slot in self._state_specs:
+            return StateView(self._state_storage.get(cache_slot), state_slots, writes)
+        return None
+
+    # ---- accounting ----------------------------------------------------------------------
+    def free_pages(self) -> list[int]:
+        return [g.pool.num_free for g in self.groups]
+
+    def check(self) -> None:
+        """No page lost, held twice or freed twice; tables and pools agree."""
+        for g in self.groups:
+            g.pool.check()
+            held = [p for t in g.tables.values() for p in t if p != RELEASED]
+            if len(held) != len(set(held)):
+                raise AssertionError("a page appears in two block tables")
+            if set(held) != g.pool._held:
+                raise AssertionError("block tables and the pool disagree on held pages")
+        self.state_slots.check()
+        if sorted(self._state_slot.values()) != sorted(self.state_slots._held):
+            raise AssertionError("state slots and live requests disagree")

@@ -1,0 +1,113 @@
+"""The ragged batch of one step, as the parts and kernels see it.
+
+A step runs the next tokens of some requests as one flat batch of ``T`` tokens:
+portions of prompts beside single decoded tokens, cut anywhere.  All integer
+metadata is packed into one pinned host buffer and copied to the device once.
+The reference passes flat ``tokens/positions/seq_ids`` the same way
+(src/inference.cu:190-198) but only ever sends whole prompts or one token per
+sequence (src/main.cpp:211-219,269-274).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass(frozen=True)
+class StepEntry:
+    """The next ``tokens`` of request ``req_id``; ``want`` lists the places among these
+    tokens (0-based) whose logits are asked for."""
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepBatch:
+    num_tokens: int
+    num_requests: int
+    num_logit_rows: int
+    act_dtype: torch.dtype
+    # host copies (launch geometry, kernel choice)
+    q_lens: list[int]
+    q_starts: list[int]
+    ctx_lens: list[int]
+    max_q_len: int
+    max_ctx_len: int
+    # device tensors, int32
+    token_ids: torch.Tensor          # [T]
+    positions: torch.Tensor          # [T] absolute position of each token in its request
+    req_of_tok: torch.Tensor         # [T] row of the token's request in the tables below
+    cu_q: torch.Tensor               # [R+1] first token of each request in the flat batch
+    q_start_dev: torch.Tensor        # [R] position of each request's first new token
+    ctx_len_dev: torch.Tensor        # [R] length of each request after this step
+    logit_rows: torch.Tensor         # [K] flat token indices whose logits are wanted
+    state_slots: torch.Tensor        # [R] state slot of each request
+    block_tables: list[torch.Tensor] = field(default_factory=list)   # per group [R, blocks]
+    scratch: dict = field(default_factory=dict)   # per-step values kernels may cache
+
+
+def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
+                     tables: Sequence[Sequence[Sequence[int]]], slots: Sequence[int],
+                     act_dtype: torch.dtype, device, min_blocks: int = 1) -> StepBatch:
+    """Pack one step.  ``starts[r]`` is the position of entry r's first token,
+    ``tables[g][r]`` its block table in group g (already covering the new tokens)."""
+    q_lens = [len(e.tokens) for e in entries]
+    r = len(entries)
+    t = sum(q_lens)
+    ctx = [s + n for s, n in zip(starts, q_lens)]
+    cu = np.zeros(r + 1, dtype=np.int64)
+    np.cumsum(q_lens, out=cu[1:])
+    rows: list[int] = []
+    for i, e in enumerate(entries):
+        for w in e.want:
+            if not 0 <= w < q_lens[i]:
+                raise IndexError(
+                    f"request {e.req_id!r}: wanted place {w} is outside its {q_lens[i]} tokens")
+            rows.append(int(cu[i]) + int(w))
+    k = len(rows)
+    widths = [max(min_blocks, max((len(tb) for tb in grp), default=0)) for grp in tables]
+    total = 3 * t + (r + 1) + 3 * r + k + sum(r * w for w in widths)
+    host = torch.empty(max(total, 1), dtype=torch.int32,
+                       pin_memory=(torch.device(device).type == "cuda"))
+    buf = host.numpy()
+    o = 0
+
+    def put(values, n):
+        nonlocal o
+        buf[o:o + n] = values
+        span = (o, o + n)
+        o += n
+        return span
+
+    tok = np.fromiter((int(x) for e in entries for x in e.tokens), dtype=np.int64, count=t)
+    pos = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, q_lens)]) if t else tok
+    roft = np.repeat(np.arange(r), q_lens)
+    spans = {
+        "tok": put(tok, t), "pos": put(pos, t), "roft": put(roft, t), "cu": put(cu, r + 1),
+        "qs": put(np.asarray(starts, dtype=np.int64), r), "ctx": put(np.asarray(ctx), r),
+        "slots": put(np.asarray(slots, dtype=np.int64), r), "rows": put(np.asarray(rows), k),
+    }
+    bt_spans = []
+    for grp, w in zip(tables, widths):
+        arr = np.full((r, w), -1, dtype=np.int64)
+        for i, tb in enumerate(grp):
+            arr[i, :len(tb)] = tb
+        bt_spans.append((put(arr.reshape(-1), r * w), w))
+    dev = host.to(device, non_blocking=True)
+
+    def view(name):
+        a, b = spans[name]
+        return dev[a:b]
+
+    return StepBatch(
+        num_tokens=t, num_requests=r, num_logit_rows=k, act_dtype=act_dtype,
+        q_lens=q_lens, q_starts=list(starts), ctx_lens=ctx,
+        max_q_len=max(q_lens, default=0), max_ctx_len=max(ctx, default=0),
+        token_ids=view("tok"), positions=view("pos"), req_of_tok=view("roft"), cu_q=view("cu"),
+        q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
+        state_slots=view("slots"),
+        block_tables=[dev[a:b].view(r, w) for (a, b), w in bt_spans])

@@ -1,0 +1,165 @@
+"""The engine: a model, its kernels, its cache, and the one step function.
+
+``Engine.step(entries)`` runs only the tokens it is given, as one batch, from
+the cache that earlier steps left, and returns float32 logits at the wanted
+places.  Everything above it (scheduler, generation, trace replay) goes through
+this call.  The reference's counterpart is ``Inference::forward``
+(src/inference.cu:178-265), which is tied to a contiguous per-sequence cache.
+"""
+from __future__ import annotations
+
+from typing import Any, Hashable, Mapping, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..config.registry import architecture_of, load_config
+from ..parts.model import CausalLM
+from ..weights.loader import load_model_weights
+from ..weights.random_init import random_tensor
+from .batch import StepBatch, StepEntry, build_step_batch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"engine dtype must be bfloat16 or float32, got {dtype}")
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"engine dtype must be bfloat16 or float32, got {dtype!r}") from None
+
+
+class Engine:
+    """A loaded model with its cache.
+
+    model_dir    folder with ``config.json`` and ``model.safetensors``; or
+    config+seed  a ``config.json`` dictionary and a seed: random weights made on the device.
+    dtype        ``bfloat16``: the kernels and precisions of serving (bfloat16 activations and
+                 cache, float32 residual stream, norms, softmax); ``float32``: everything in
+                 true 32-bit arithmetic.
+    max_tokens   how many tokens the cache holds over all live requests (each request's
+                 count rounded up to whole pages); or ``num_pages`` directly.
+    ops          the kernel set; by default the CUDA kernels, which must be available.
+    """
+
+    def __init__(self, model_dir: Optional[str] = None, *, config: Optional[Mapping[str, Any]] = None,
+                 seed: Optional[int] = None, dtype="bfloat16", device="cuda:0",
+                 page_size: int = 16, max_tokens: Optional[int] = None,
+                 num_pages: Optional[int] = None, max_requests: int = 64, ops=None):
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        if ops is None:
+            from ..kernels import cuda_ops
+            ops = cuda_ops(self.device)
+        self.ops = ops
+        if model_dir is not None:
+            arch, typed = load_config(model_dir)
+        elif config is not None:
+            arch = architecture_of(config)
+            typed = arch.from_dict(config)
+        else:
+            raise ValueError("Engine needs a model folder, or a configuration and a seed")
+        self.config = typed
+        self.plan = arch.build_plan(typed)
+        self.model = CausalLM(self.plan)
+        if model_dir is not None:
+            load_model_weights(self.model, model_dir, self.device, ops)
+        else:
+            if seed is None:
+                raise ValueError("random weights need a seed")
+            expected = self.model.expected_tensors()
+            self.model.load_weights(
+                lambda name: random_tensor(seed, name, expected[name], device=self.device), ops)
+        if num_pages is None:
+            if max_tokens is None:
+                max_tokens = self.plan.max_position
+            # every live request may waste up to one page less a token
+            num_pages = -(-max_tokens // page_size) + max_requests
+        self.page_size = page_size
+        self.cache = CacheManager(self.model.cache_specs(), page_size=page_size,
+                                  num_pages=num_pages, max_requests=max_requests,
+                                  kv_dtype=self.dtype, device=self.device)
+        self.last_batch: Optional[StepBatch] = None
+
+    # ---- requests ------------------------------------------------------------------------
+    def add_request(self, req_id: Hashable) -> None:
+        self.cache.add_request(req_id)
+
+    def finish(self, req_id: Hashable) -> None:
+        """Give back everything the request holds."""
+        self.cache.free_request(req_id)
+
+    def length(self, req_id: Hashable) -> int:
+        return self.cache.length(req_id)
+
+    # ---- the step ------------------------------------------------------------------------
+    def reserve(self, entries: Sequence[StepEntry]) -> list[int]:
+        """Make room in the cache for the step's tokens, for all entries or for none."""
+        seen = set()
+        new = []
+        for e in entries:
+            if e.req_id in seen:
+                raise ValueError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if len(e.tokens) < 1:
+                raise ValueError(f"request {e.req_id!r} brings no tokens")
+            if not self.cache.has_request(e.req_id):
+                new.append(e.req_id)
+        if len(new) > self.cache.state_slots.num_free:
+            raise OutOfPages(f"{len(new)} new requests, {self.cache.state_slots.num_free} slots free")
+        for r in new:
+            self.cache.add_request(r)
+        try:
+            need = [0] * len(self.cache.groups)
+            for e in entries:
+                end = self.cache.length(e.req_id) + len(e.tokens)
+                if end > self.plan.max_position:
+                    raise ValueError(
+                        f"request {e.req_id!r} would reach {end} tokens; the model's "
+                        f"max_position_embeddings is {self.plan.max_position}")
+                for g, n in enumerate(self.cache.pages_needed(e.req_id, len(e.tokens))):
+                    need[g] += n
+            free = self.cache.free_pages()
+            for g, n in enumerate(need):
+                if n > free[g]:
+                    raise OutOfPages(f"step needs {n} pages of group {g}, {free[g]} are free")
+        except Exception:
+            for r in new:
+                self.cache.free_request(r)
+            raise
+        return [self.cache.append(e.req_id, len(e.tokens)) for e in entries]
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; returns logits ``[wanted, vocab]`` in the order of entries and ``want``."""
+        entries = list(entries)
+        if not entries:
+            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        vocab = self.plan.vocab_size
+        for e in entries:
+            for tok in e.tokens:
+                if not 0 <= int(tok) < vocab:
+                    raise ValueError(f"request {e.req_id!r}: token id {tok} is outside [0, {vocab})")
+        starts = self.reserve(entries)
+        tables = [[self.cache.block_table(g, e.req_id) for e in entries]
+                  for g in range(len(self.cache.groups))]
+        slots = [self.cache.state_slot(e.req_id) for e in entries]
+        batch = build_step_batch(entries, starts, tables, slots, self.dtype, self.device)
+        logits = self.forward(batch)
+        for e in entries:
+            self.cache.release_passed(e.req_id)
+        self.last_batch = batch
+        return logits
+
+    def forward(self, batch: StepBatch) -> torch.Tensor:
+        views = {}
+        for entry in self.plan.schedule:
+            key = (entry.cache_slot, entry.writes_cache)
+            if key not in views:
+                views[key] = self.cache.view(entry.cache_slot, entry.writes_cache,
+                                             batch.block_tables, batch.state_slots)
+        return self.model.forward(self.ops, batch, views)

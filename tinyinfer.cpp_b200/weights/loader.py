@@ -1,0 +1,75 @@
+"""Load a model's tensors from a folder by tensor name, and say clearly what does not fit.
+
+Storage precision is never narrowed: bfloat16 stays bfloat16, float32 stays
+float32, float16 and float64 become float32, integer tables become int32.  The
+reference loads tensor by tensor and stops at the first problem
+(src/model.cpp:63-117); here the whole folder is checked first and one error
+lists every missing tensor, every unexpected tensor and every wrong shape.
+"""
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from ..parts.base import WeightSpec
+from .safetensors_io import SafetensorsError, open_model_files, tensor_index
+
+
+class WeightsError(ValueError):
+    """The folder's tensors do not match what the model needs."""
+
+    def __init__(self, where: str, missing, unexpected, wrong_shape):
+        self.missing = sorted(missing)
+        self.unexpected = sorted(unexpected)
+        self.wrong_shape = sorted(wrong_shape)          # (name, expected, found)
+        lines = [f"{where}: tensors do not match the model"]
+        if self.missing:
+            lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        if self.wrong_shape:
+            lines.append(f"  wrong shape ({len(self.wrong_shape)}): " + ", ".join(
+                f"{n} expected {list(e)} found {list(f)}" for n, e, f in self.wrong_shape))
+        super().__init__("\n".join(lines))
+
+
+def check_tensors(where: str, expected: Mapping[str, WeightSpec],
+                  found: Mapping[str, tuple[int, ...]]) -> None:
+    missing = [n for n in expected if n not in found]
+    unexpected = [n for n in found if n not in expected]
+    wrong = [(n, expected[n].shape, found[n]) for n in expected
+             if n in found and tuple(found[n]) != tuple(expected[n].shape)]
+    if missing or unexpected or wrong:
+        raise WeightsError(where, missing, unexpected, wrong)
+
+
+def storage_dtype(dtype: torch.dtype) -> torch.dtype:
+    """The dtype a stored tensor is kept in."""
+    if dtype in (torch.bfloat16, torch.float32):
+        return dtype
+    if dtype.is_floating_point:
+        return torch.float32
+    return torch.int32
+
+
+def load_model_weights(model, model_dir: str, device, ops) -> None:
+    """Check the folder against ``model.expected_tensors()`` and hand each part its tensors."""
+    files = open_model_files(model_dir)
+    try:
+        index = tensor_index(files)
+        expected = model.expected_tensors()
+        check_tensors(model_dir, expected, {n: f.shape(n) for n, f in index.items()})
+
+        def fetch(name: str) -> torch.Tensor:
+            t = index[name].get(name)
+            return t.to(device=device, dtype=storage_dtype(t.dtype), copy=True)
+
+        model.load_weights(fetch, ops)
+    finally:
+        for f in files:
+            f.close()
+
+
+__all__ = ["SafetensorsError", "WeightsError", "check_tensors", "load_model_weights",
+           "storage_dtype"]
