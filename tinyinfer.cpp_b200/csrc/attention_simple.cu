@@ -1,0 +1,227 @@
+// Attention on the CUDA cores, for every head size and both cache types.
+//
+//  * qk_norm_rope_store: per-head RMSNorm of q and k, NeoX rotation at the token's position,
+//    k and v written once per kv head into the token's page, q written for the attention kernel.
+//  * paged_attention_simple: one block per (token, query head); its warps share the keys of the
+//    token's context [lo, pos] (lo > 0 only for a window) and merge their online softmaxes.
+//
+// These are the true 32-bit kernels and the fallback of the bfloat16 path for shapes that
+// the tensor-core kernels refuse.  Cache layout: pages[page][0 = keys, 1 = values][kv head]
+// [slot][head_dim]; a token at position p of request r lies in page block_table[r][p / page_size],
+// slot p % page_size.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_HEAD_DIM = 256;
+constexpr int WARPS = 4;
+
+enum { TI_ERR_BAD_PAGE = 1 };
+
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
+                          const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                          float eps, const float* __restrict__ inv_freq,
+                          const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                          const int* __restrict__ block_table, int bt_stride,
+                          TC* __restrict__ pages, int num_pages, int page_size, int write_kv,
+                          int num_heads, int num_kv_heads, int head_dim,
+                          TQ* __restrict__ q_out, int* __restrict__ status) {
+    __shared__ float vec[WARPS][MAX_HEAD_DIM];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int item = blockIdx.y * WARPS + warp;
+    const int items = num_heads + 2 * num_kv_heads;
+    if (item >= items) return;
+    const int half = head_dim >> 1;
+    const int nq = num_heads * head_dim, nk = num_kv_heads * head_dim;
+    const int pos = positions[t];
+
+    // which vector: a query head, a key head or a value head
+    int kind, head;
+    if (item < num_heads) { kind = 0; head = item; }
+    else if (item < num_heads + num_kv_heads) { kind = 1; head = item - num_heads; }
+    else { kind = 2; head = item - num_heads - num_kv_heads; }
+    if (kind != 0 && !write_kv) return;
+    const float* src = qkv + (size_t)t * qkv_stride +
+                       (kind == 0 ? head * head_dim : kind == 1 ? nq + head * head_dim
+                                                                : nq + nk + head * head_dim);
+    TC* dst = nullptr;
+    if (kind != 0) {
+        const int r = req_of_tok[t];
+        const int page = block_table[(size_t)r * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+            return;
+        }
+        dst = pages + ((((size_t)page * 2 + (kind - 1)) * num_kv_heads + head) * page_size +
+                       pos % page_size) * head_dim;
+    }
+    if (kind == 2) {                                   // values are stored as they are
+        for (int d = lane; d < head_dim; d += 32) dst[d] = from_f32<TC>(src[d]);
+        return;
+    }
+    const float* w = kind == 0 ? q_weight : k_weight;
+    float ss = 0.0f;
+    for (int d = lane; d < head_dim; d += 32) {
+        const float v = src[d];
+        vec[warp][d] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+    __syncwarp();
+    for (int k = lane; k < half; k += 32) {
+        const float x0 = vec[warp][k] * inv * w[k];
+        const float x1 = vec[warp][k + half] * inv * w[k + half];
+        const float angle = (float)pos * inv_freq[k];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const float y0 = x0 * cs - x1 * sn;
+        const float y1 = x0 * sn + x1 * cs;
+        if (kind == 0) {
+            TQ* q = q_out + (size_t)t * nq + head * head_dim;
+            q[k] = from_f32<TQ>(y0);
+            q[k + half] = from_f32<TQ>(y1);
+        } else {
+            dst[k] = from_f32<TC>(y0);
+            dst[k + half] = from_f32<TC>(y1);
+        }
+    }
+}
+
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(WARPS * 32)
+paged_attention_simple_kernel(const TQ* __restrict__ q, const int* __restrict__ positions,
+                              const int* __restrict__ req_of_tok,
+                              const int* __restrict__ block_table, int bt_stride,
+                              const TC* __restrict__ pages, int num_pages, int page_size,
+                              int num_heads, int num_kv_heads, int head_dim, int window,
+                              float scale, TQ* __restrict__ out, int* __restrict__ status) {
+    constexpr int PER_LANE = MAX_HEAD_DIM / 32;
+    __shared__ float so[WARPS][MAX_HEAD_DIM];
+    __shared__ float sm[WARPS], sl[WARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y, t = blockIdx.x;
+    const int kvh = h / (num_heads / num_kv_heads);
+    const int pos = positions[t];
+    const int r = req_of_tok[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* table = block_table + (size_t)r * bt_stride;
+
+    float qv[PER_LANE], o[PER_LANE];
+    const TQ* qh = q + ((size_t)t * num_heads + h) * head_dim;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        qv[i] = d < head_dim ? to_f32(qh[d]) : 0.0f;
+        o[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    bool bad = false;
+    for (int p = lo + warp; p <= pos; p += WARPS) {
+        const int page = table[p / page_size];
+        if (page < 0 || page >= num_pages) { bad = true; continue; }
+        const TC* kp = pages + (((size_t)page * 2 * num_kv_heads + kvh) * page_size +
+                                p % page_size) * head_dim;
+        const TC* vp = kp + (size_t)num_kv_heads * page_size * head_dim;
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) s = fmaf(qv[i], to_f32(kp[d]), s);
+        }
+        s = warp_sum(s) * scale;
+        const float m_new = fmaxf(m, s);
+        const float alpha = expf(m - m_new);          // exp(-inf) = 0 on the first key
+        const float pr = expf(s - m_new);
+        l = l * alpha + pr;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) o[i] = fmaf(pr, to_f32(vp[d]), o[i] * alpha);
+        }
+        m = m_new;
+    }
+    if (bad && lane == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < head_dim) so[warp][d] = o[i];
+    }
+    if (lane == 0) { sm[warp] = m; sl[warp] = l; }
+    __syncthreads();
+    if (warp == 0) {
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, sm[w]);
+        float ltot = 0.0f, wt[WARPS];
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            wt[w] = sl[w] > 0.0f ? expf(sm[w] - mm) : 0.0f;
+            ltot += sl[w] * wt[w];
+        }
+        const float inv = 1.0f / ltot;
+        TQ* oh = out + ((size_t)t * num_heads + h) * head_dim;
+        for (int d = lane; d < head_dim; d += 32) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) acc = fmaf(so[w][d], wt[w], acc);
+            oh[d] = from_f32<TQ>(acc * inv);
+        }
+    }
+}
+
+}  // namespace
+
+#define TI_DISPATCH_QC(qd, cd, CALL)                                               \
+    if (qd == TI_F32 && cd == TI_F32) { CALL(float, float); }                      \
+    else if (qd == TI_BF16 && cd == TI_BF16) { CALL(bf16, bf16); }                 \
+    else if (qd == TI_F32 && cd == TI_BF16) { CALL(float, bf16); }                 \
+    else return ti_fail("attention: dtype codes q=%d cache=%d are not supported", qd, cd);
+
+extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const float* q_weight,
+                                     const float* k_weight, float eps, const float* inv_freq,
+                                     const int* positions, const int* req_of_tok,
+                                     const int* block_table, int bt_stride, void* pages,
+                                     int cache_dtype, int num_pages, int page_size, int write_kv,
+                                     int num_tokens, int num_heads, int num_kv_heads, int head_dim,
+                                     void* q_out, int q_dtype, int* status, void* stream) {
+    if (num_tokens == 0) return 0;
+    TI_REQUIRE(head_dim >= 2 && head_dim % 2 == 0 && head_dim <= MAX_HEAD_DIM,
+               "qk_norm_rope_store: head_dim %d must be even and at most %d", head_dim, MAX_HEAD_DIM);
+    const int items = num_heads + 2 * num_kv_heads;
+    dim3 grid(num_tokens, (items + WARPS - 1) / WARPS);
+    cudaStream_t s = (cudaStream_t)stream;
+#define CALL(TQ, TC)                                                                          \
+    qk_norm_rope_store_kernel<TQ, TC><<<grid, WARPS * 32, 0, s>>>(                             \
+        qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
+        bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,         \
+        head_dim, (TQ*)q_out, status)
+    TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
+#undef CALL
+    return ti_check_launch("qk_norm_rope_store");
+}
+
+extern "C" int ti_paged_attention_simple(const void* q, int q_dtype, const int* positions,
+                                         const int* req_of_tok, const int* block_table,
+                                         int bt_stride, const void* pages, int cache_dtype,
+                                         int num_pages, int page_size, int num_tokens,
+                                         int num_heads, int num_kv_heads, int head_dim, int window,
+                                         float scale, void* out, int* status, void* stream) {
+    if (num_tokens == 0) return 0;
+    TI_REQUIRE(head_dim >= 1 && head_dim <= MAX_HEAD_DIM,
+               "paged_attention: head_dim %d must be at most %d", head_dim, MAX_HEAD_DIM);
+    TI_REQUIRE(num_heads % num_kv_heads == 0, "paged_attention: %d heads over %d kv heads",
+               num_heads, num_kv_heads);
+    dim3 grid(num_tokens, num_heads);
+    cudaStream_t s = (cudaStream_t)stream;
+#define CALL(TQ, TC)                                                                           \
+    paged_attention_simple_kernel<TQ, TC><<<grid, WARPS * 32, 0, s>>>(                          \
+        (const TQ*)q, positions, req_of_tok, block_table, bt_stride, (const TC*)pages, num_pages, \
+        page_size, num_heads, num_kv_heads, head_dim, window, scale, (TQ*)out, status)
+    TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
+#undef CALL
+    return ti_check_launch("paged_attention_simple");
+}

@@ -1,0 +1,132 @@
+// Row-wise kernels: token embedding, RMSNorm (optionally of gathered rows), SwiGLU, argmax.
+// All arithmetic is float32; results are rounded once to the output type.
+#include "common.cuh"
+
+namespace {
+
+// x[t, :] = float32(table[token[t], :])
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             int hidden, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    const TW* row = table + (size_t)tokens[t] * hidden;
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// out[r, :] = x[src(r), :] * (1 / sqrt(mean(x^2) + eps)) * w, src(r) = rows ? rows[r] : r
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               const int* __restrict__ rows, float eps, int n,
+                               TO* __restrict__ out) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * n;
+    TO* o = out + (size_t)r * n;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    const float mean = block_sum(ss, scratch) / (float)n;
+    const float inv = 1.0f / sqrtf(mean + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * inv * w[i]);
+}
+
+// y[t, j] = silu(gu[t, j]) * gu[t, inter + j], silu(g) = g / (1 + exp(-g))
+template <typename TO>
+__global__ void swiglu_kernel(const float* __restrict__ gu, int inter, size_t total,
+                              TO* __restrict__ y) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / inter, j = i % inter;
+    const float g = gu[t * 2 * inter + j];
+    const float u = gu[t * 2 * inter + inter + j];
+    y[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+}
+
+__device__ __forceinline__ void keep_best(float v, int i, float& bv, int& bi) {
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+// Row argmax; among equal maxima the lowest index wins.
+__global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) keep_best(row[i], i, bv, bi);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        keep_best(ov, oi, bv, bi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            keep_best(ov, oi, bv, bi);
+        }
+        if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+}  // namespace
+
+extern "C" int ti_embed(const void* table, int table_dtype, const int* tokens, int num_tokens,
+                        int hidden, float* out, void* stream) {
+    if (num_tokens == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == TI_BF16)
+        embed_kernel<bf16><<<num_tokens, 256, 0, s>>>((const bf16*)table, tokens, hidden, out);
+    else if (table_dtype == TI_F32)
+        embed_kernel<float><<<num_tokens, 256, 0, s>>>((const float*)table, tokens, hidden, out);
+    else
+        return ti_fail("embed: table dtype code %d is not float32 or bfloat16", table_dtype);
+    return ti_check_launch("embed");
+}
+
+extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, int num_rows,
+                          int n, float eps, void* out, int out_dtype, void* stream) {
+    if (num_rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (out_dtype == TI_BF16)
+        rmsnorm_kernel<bf16><<<num_rows, threads, 0, s>>>(x, weight, rows, eps, n, (bf16*)out);
+    else if (out_dtype == TI_F32)
+        rmsnorm_kernel<float><<<num_rows, threads, 0, s>>>(x, weight, rows, eps, n, (float*)out);
+    else
+        return ti_fail("rmsnorm: output dtype code %d is not float32 or bfloat16", out_dtype);
+    return ti_check_launch("rmsnorm");
+}
+
+extern "C" int ti_swiglu(const float* gu, int num_tokens, int inter, void* out, int out_dtype,
+                         void* stream) {
+    const size_t total = (size_t)num_tokens * inter;
+    if (total == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == TI_BF16)
+        swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, inter, total, (bf16*)out);
+    else if (out_dtype == TI_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, inter, total, (float*)out);
+    else
+        return ti_fail("swiglu: output dtype code %d is not float32 or bfloat16", out_dtype);
+    return ti_check_launch("swiglu");
+}
+
+extern "C" int ti_argmax(const float* logits, int rows, int vocab, int* out, void* stream) {
+    if (rows == 0) return 0;
+    TI_REQUIRE(vocab > 0, "argmax: vocabulary size %d", vocab);
+    argmax_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, vocab, out);
+    return ti_check_launch("argmax");
+}

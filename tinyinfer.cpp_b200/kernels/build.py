@@ -1,0 +1,156 @@
+"""Compile the CUDA sources of ``csrc/`` for sm_100a with nvcc and load them with ctypes.
+
+Libraries are built on first use, in-tree under ``_build/`` (or under the temporary
+folder when the tree is read-only), one ``.so`` per library below, and rebuilt when a
+source, a header or a flag changes.  Only the library that is asked for is compiled,
+so a float32 engine does not wait for the bfloat16 tensor-core kernels.  While nvcc
+runs, a line is printed to stderr every few seconds.
+"""
+from __future__ import annotations
+
+import ctypes
+import fcntl
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+
+CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+
+# library name -> sources (each library is self-contained and links common.cu)
+LIBRARIES = {
+    "core": ["common.cu", "rowwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
+}
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+]
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("TINYINFER_NVCC"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+                 shutil.which("nvcc")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("nvcc was not found (looked at $TINYINFER_NVCC, $CUDA_HOME/bin, "
+                     "/usr/local/cuda/bin and PATH); the CUDA kernels cannot be built")
+
+
+def build_dir() -> str:
+    """In-tree ``_build`` when it can be written, else a per-user folder under the temp dir."""
+    override = os.environ.get("TINYINFER_BUILD_DIR")
+    cands = [override] if override else []
+    cands.append(os.path.join(os.path.dirname(CSRC), "_build"))
+    cands.append(os.path.join(tempfile.gettempdir(), f"tinyinfer_b200_build_{os.getuid()}"))
+    for d in cands:
+        try:
+            os.makedirs(d, exist_ok=True)
+            probe = os.path.join(d, f".probe_{os.getpid()}")
+            with open(probe, "w"):
+                pass
+            os.remove(probe)
+            return d
+        except OSError:
+            continue
+    raise BuildError("no writable folder for the compiled kernels: tried " + ", ".join(cands))
+
+
+def _digest(sources: list[str]) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    headers = sorted(n for n in os.listdir(CSRC) if n.endswith((".cuh", ".h")))
+    for name in list(sources) + headers:
+        h.update(name.encode())
+        with open(os.path.join(CSRC, name), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
+def _say(msg: str) -> None:
+    print(f"[tinyinfer_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def _run_all(cmds: dict[str, list[str]], what: str) -> None:
+    """Run the commands at once; report now and then; raise with the output of a failure."""
+    start = time.time()
+    procs = {n: subprocess.Popen(c, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for n, c in cmds.items()}
+    outputs: dict[str, str] = {}
+    last = start
+    while procs:
+        for n in list(procs):
+            if procs[n].poll() is not None:
+                outputs[n] = procs[n].communicate()[0]
+                if procs[n].returncode != 0:
+                    for other in procs.values():
+                        if other.poll() is None:
+                            other.kill()
+                    raise BuildError(f"{what}: {n} failed\n$ {' '.join(cmds[n])}\n{outputs[n]}")
+                del procs[n]
+        if procs:
+            time.sleep(0.2)
+            if time.time() - last >= 5.0:
+                last = time.time()
+                _say(f"{what}: still compiling {', '.join(sorted(procs))} "
+                     f"({int(last - start)} s)")
+
+
+def build_library(name: str, verbose: bool = True) -> str:
+    """Make sure ``lib<name>`` is built and current; returns the path of the ``.so``."""
+    sources = LIBRARIES[name]
+    out_dir = build_dir()
+    so_path = os.path.join(out_dir, f"libtinyinfer_b200_{name}.so")
+    stamp = so_path + ".sha256"
+    digest = _digest(sources)
+    with open(os.path.join(out_dir, f".{name}.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if os.path.isfile(so_path) and os.path.isfile(stamp):
+                with open(stamp) as fh:
+                    if fh.read().strip() == digest:
+                        return so_path
+            nvcc = find_nvcc()
+            if verbose:
+                _say(f"compiling the '{name}' kernels for sm_100a ({len(sources)} files) "
+                     f"into {out_dir}")
+            t0 = time.time()
+            objs = {}
+            cmds = {}
+            for src in sources:
+                obj = os.path.join(out_dir, f"{name}_{os.path.splitext(src)[0]}.o")
+                objs[src] = obj
+                cmds[src] = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+            _run_all(cmds, f"'{name}' kernels")
+            tmp = so_path + f".tmp{os.getpid()}"
+            _run_all({"link": [nvcc, "-shared", "-o", tmp, *objs.values()]},
+                     f"'{name}' kernels")
+            os.replace(tmp, so_path)
+            with open(stamp, "w") as fh:
+                fh.write(digest)
+            if verbose:
+                _say(f"'{name}' kernels ready ({time.time() - t0:.0f} s)")
+            return so_path
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+_LOADED: dict[str, ctypes.CDLL] = {}
+
+
+def load_library(name: str) -> ctypes.CDLL:
+    if name not in _LOADED:
+        _LOADED[name] = ctypes.CDLL(build_library(name))
+    return _LOADED[name]
+
+
+def build_all(verbose: bool = True) -> list[str]:
+    return [build_library(n, verbose) for n in LIBRARIES]

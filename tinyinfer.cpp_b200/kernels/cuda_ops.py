@@ -1,0 +1,202 @@
+"""The kernel set of the engine: thin bindings of the C entry points in ``csrc/``.
+
+Every method takes torch tensors on the CUDA device, checks what the C side cannot
+(dtypes, contiguity, shapes), and launches on torch's current stream.  There is no
+fallback: if the device or the compiled library is missing, construction fails.
+
+The kernel set's calling convention (also implemented by the plain PyTorch
+statement in the tests):
+
+pack_linear(w) -> w'                         a product's weight in the layout the kernels want
+pack_gate_up(gate, up) -> w'                 the stacked gate/up weight
+embed(table, token_ids, out)                 out[t] = float32(table[token_ids[t]])
+rmsnorm(x, weight, eps, out, rows=None)      out[r] = norm(x[rows[r]] or x[r]), rounded to out.dtype
+linear(a, w, out, accumulate=False)          out (+)= a @ w.T in float32
+gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
+qk_norm_rope_store(...)                      q/k head norm, rotation, k/v into pages, q out
+paged_attention(...)                         causal attention over the pages of each token's request
+argmax(logits, out) / sample(...)            next token per row
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not float32 or bfloat16") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError(
+                "the engine runs on a CUDA device only (there is no CPU path); "
+                f"device {device!r} is not usable here")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(
+                f"the kernels are built for sm_100a; device {device!r} is sm_{major}{minor}")
+        self.core = load_library("core")
+        self.core.ti_last_error.restype = ctypes.c_char_p
+        self._declare()
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ---- plumbing ------------------------------------------------------------------------
+    def _declare(self) -> None:
+        c = self.core
+        c.ti_embed.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp]
+        c.ti_rmsnorm.argtypes = [_vp, _vp, _vp, _i, _i, _f, _vp, _i, _vp]
+        c.ti_swiglu.argtypes = [_vp, _i, _i, _vp, _i, _vp]
+        c.ti_argmax.argtypes = [_vp, _i, _i, _vp, _vp]
+        c.ti_gemm_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]
+        c.ti_qk_norm_rope_store.argtypes = [
+            _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
+            _vp, _i, _vp, _vp]
+        c.ti_paged_attention_simple.argtypes = [
+            _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]
+        c.ti_sample.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _ok(self, rc: int, lib=None) -> None:
+        if rc != 0:
+            raise KernelError((lib or self.core).ti_last_error().decode("utf-8", "replace"))
+
+    def check_status(self) -> None:
+        """Raise if a kernel met a block-table entry outside the pool since the last check."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise KernelError(f"a kernel reported device status {code} (1: page id outside the pool)")
+
+    # ---- weights -------------------------------------------------------------------------
+    def pack_linear(self, w: torch.Tensor) -> torch.Tensor:
+        _code(w, "pack_linear")
+        return w.contiguous()
+
+    def pack_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        return torch.cat([gate, up], dim=0).contiguous()
+
+    # ---- rowwise -------------------------------------------------------------------------
+    def embed(self, table, token_ids, out):
+        _need(out.dtype == torch.float32 and out.is_contiguous(), "embed: out must be float32")
+        _need(token_ids.dtype == torch.int32, "embed: token ids must be int32")
+        self._ok(self.core.ti_embed(table.data_ptr(), _code(table, "embed"), token_ids.data_ptr(),
+                                    token_ids.shape[0], table.shape[1], out.data_ptr(),
+                                    self._stream()))
+
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "rmsnorm: x must be float32")
+        _need(weight.dtype == torch.float32 and weight.shape[0] == x.shape[1],
+              "rmsnorm: weight must be float32 of the row length")
+        _need(out.is_contiguous() and out.shape[1] == x.shape[1], "rmsnorm: bad out")
+        n_rows = x.shape[0] if rows is None else rows.shape[0]
+        _need(out.shape[0] == n_rows, "rmsnorm: out has the wrong number of rows")
+        if rows is not None:
+            _need(rows.dtype == torch.int32, "rmsnorm: rows must be int32")
+        self._ok(self.core.ti_rmsnorm(x.data_ptr(), weight.data_ptr(), _ptr(rows), n_rows,
+                                      x.shape[1], float(eps), out.data_ptr(),
+                                      _code(out, "rmsnorm"), self._stream()))
+
+    def linear(self, a, w, out, accumulate=False):
+        m, k = a.shape
+        n = w.shape[0]
+        _need(w.shape[1] == k and tuple(out.shape) == (m, n), "linear: shapes do not agree")
+        _need(out.dtype == torch.float32, "linear: out must be float32")
+        _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
+              "linear: rows must be contiguous")
+        self._ok(self.core.ti_gemm_simple(
+            a.data_ptr(), _code(a, "linear"), w.data_ptr(), _code(w, "linear"), out.data_ptr(),
+            m, n, k, a.stride(0), w.stride(0), out.stride(0), int(bool(accumulate)),
+            self._stream()))
+
+    def gate_up_swiglu(self, h, w_gate_up, out):
+        inter = out.shape[1]
+        _need(w_gate_up.shape[0] == 2 * inter, "gate_up_swiglu: weight must hold gate and up rows")
+        gu = torch.empty((h.shape[0], 2 * inter), dtype=torch.float32, device=h.device)
+        self.linear(h, w_gate_up, gu)
+        self._ok(self.core.ti_swiglu(gu.data_ptr(), h.shape[0], inter, out.data_ptr(),
+                                     _code(out, "swiglu"), self._stream()))
+
+    # ---- attention -----------------------------------------------------------------------
+    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+                           num_heads, num_kv_heads, head_dim):
+        t = qkv.shape[0]
+        _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1, "qk_norm_rope_store: qkv float32")
+        _need(qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim,
+              "qk_norm_rope_store: qkv width does not match the head counts")
+        _need(inv_freq.shape[0] == head_dim // 2 and inv_freq.dtype == torch.float32,
+              "qk_norm_rope_store: the rotation table must hold head_dim/2 float32 values")
+        pages, bt = cache.pages, cache.block_table
+        _need(pages.is_contiguous() and tuple(pages.shape[1:]) ==
+              (2, num_kv_heads, cache.page_size, head_dim), "qk_norm_rope_store: page layout")
+        _need(bt.dtype == torch.int32 and bt.stride(1) == 1, "qk_norm_rope_store: block table int32")
+        self._ok(self.core.ti_qk_norm_rope_store(
+            qkv.data_ptr(), qkv.stride(0), q_weight.data_ptr(), k_weight.data_ptr(), float(eps),
+            inv_freq.data_ptr(), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
+            bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
+            cache.page_size, int(bool(cache.writes)), t, num_heads, num_kv_heads, head_dim,
+            q_out.data_ptr(), _code(q_out, "q"), self.status.data_ptr(), self._stream()))
+
+    def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,
+                        scale):
+        pages, bt = cache.pages, cache.block_table
+        _need(q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype,
+              "paged_attention: q and out must be contiguous and of one dtype")
+        _need(pages.is_contiguous() and tuple(pages.shape[1:]) ==
+              (2, num_kv_heads, cache.page_size, head_dim), "paged_attention: page layout")
+        self._ok(self.core.ti_paged_attention_simple(
+            q.data_ptr(), _code(q, "q"), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
+            bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
+            cache.page_size, q.shape[0], num_heads, num_kv_heads, head_dim,
+            int(window or 0), float(scale), out.data_ptr(), self.status.data_ptr(),
+            self._stream()))
+
+    # ---- sampling ------------------------------------------------------------------------
+    def argmax(self, logits, out):
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "argmax: float32 logits")
+        _need(out.dtype == torch.int32 and out.shape[0] == logits.shape[0], "argmax: int32 out")
+        self._ok(self.core.ti_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1],
+                                     out.data_ptr(), self._stream()))
+
+    def sample(self, logits, temperature, top_k, top_p, uniform, out):
+        rows = logits.shape[0]
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: float32 logits")
+        for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                            ("top_p", top_p, torch.float32), ("uniform", uniform, torch.float32),
+                            ("out", out, torch.int32)):
+            _need(t.dtype == dt and t.shape[0] == rows and t.is_contiguous(),
+                  f"sample: {name} must be {dt} with one value per row")
+        self._ok(self.core.ti_sample(logits.data_ptr(), rows, logits.shape[1],
+                                     temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
+                                     uniform.data_ptr(), out.data_ptr(), self._stream()))
