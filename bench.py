@@ -1,0 +1,315 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096]
+    python bench.py --impl reference        # the reference arm (see below)
+
+Default run: the Qwen3-0.6B layer sizes (28 layers, hidden 1024, 16 heads over 8 kv heads of
+128, intermediate 3072, vocabulary 151936, tied head) with seeded random weights, 8 requests
+decoding at a context of 4,096 tokens, pages of 16 tokens.  A step is one decode step of the
+whole batch.  Prints one JSON line:
+
+value      decoded tokens a second, timed on the device with CUDA events over K graph-replayed
+           steps with the argmax on the device (nothing is read back inside the timed region);
+e2e        the same through the Python entry point: every step copies its host token ids to
+           the device from pinned memory and reads the chosen tokens back;
+prefill    one request's 2,048-token prompt in one step: tokens a second and the step's
+           flops / time / bf16 peak;
+roofline   the bytes a decode step has to read (every weight once, and the keys and values of
+           the live requests) / its time, against the copy bandwidth;
+points     decode tokens a second at batch 1 and 64.
+
+Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
+measurement on this pool (6.65 TB/s, 1.59 PFLOP/s), and the fractions say which.  The working
+set (1.2 GB of weights and gigabytes of cache) is far larger than the 126 MB L2, so no flush is
+needed between steps.  Keys and values of the decoding requests are filled with random numbers
+instead of being computed from prompts: a decode step's work does not depend on their values.
+
+The reference arm: beyondHJM/tinyinfer.cpp is a CMake project of C++/CUDA executables, not a
+Python package, so the offline `pip install` fails ("Neither 'setup.py' nor 'pyproject.toml'
+found") and `--impl reference` reports it as unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_0_6B = dict(
+    architectures=["Qwen3ForCausalLM"], num_hidden_layers=28, hidden_size=1024,
+    num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
+    vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+    max_position_embeddings=4096)
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self):
+        self.lines: list[str] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(self.NAMES, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def model_numbers(cfg):
+    h, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+    nq = cfg["num_attention_heads"] * cfg["head_dim"]
+    nk = cfg["num_key_value_heads"] * cfg["head_dim"]
+    inter, vocab = cfg["intermediate_size"], cfg["vocab_size"]
+    layer_params = (nq + 2 * nk) * h + h * nq + 3 * inter * h
+    head_params = vocab * h
+    weight_bytes = 2 * (L * layer_params + head_params) + 4 * (L * (2 * h + 2 * cfg["head_dim"]) + h)
+    if not cfg["tie_word_embeddings"]:
+        pass                                     # the embedding table is gathered, not streamed
+    kv_bytes_per_token = L * 2 * nk * 2
+    return dict(layer_params=layer_params, head_params=head_params, weight_bytes=weight_bytes,
+                kv_bytes_per_token=kv_bytes_per_token, nq=nq)
+
+
+def prefill_flops(cfg, t):
+    n = model_numbers(cfg)
+    gemm = 2.0 * t * cfg["num_hidden_layers"] * n["layer_params"] + 2.0 * n["head_params"]
+    attn = cfg["num_hidden_layers"] * 4.0 * n["nq"] * t * (t + 1) / 2.0
+    return gemm + attn
+
+
+def fill_requests(engine, batch, context, torch):
+    """``batch`` live requests holding ``context`` tokens each, keys and values random."""
+    ids = [("bench", i) for i in range(batch)]
+    engine.cache.reserve_step([(r, context) for r in ids], engine.plan.max_position)
+    for g in engine.cache.groups:
+        g.storage.normal_(0.0, 1.0)
+    return ids
+
+
+def decode_device_timed(engine, ids, steps, warmup, torch):
+    """K graph-replayed decode steps with the argmax on the device; nothing is read back
+    inside the timed region, so host work overlaps the device's."""
+    from tinyinfer_b200 import StepEntry
+    b = len(ids)
+    out = torch.empty(b, dtype=torch.int32, device=engine.device)
+
+    def one():
+        logits = engine.decode_step([StepEntry(r, [1], [0]) for r in ids])
+        engine.ops.argmax(logits, out)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    before = engine.ops.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler() as clocks:
+        start.record()
+        for _ in range(steps):
+            one()
+        stop.record()
+        torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    return ms / steps, clocks.summary(), engine.ops.launches - before
+
+
+def decode_e2e(engine, ids, steps, warmup, torch):
+    """The same steps as a user runs them: host token ids in, chosen token ids out."""
+    from tinyinfer_b200 import StepEntry
+    from tinyinfer_b200.sampling import Sampler, SamplingParams
+    sampler = Sampler(engine.ops, engine.device)
+    params = [SamplingParams()] * len(ids)
+    tokens = [1] * len(ids)
+    numbers = list(range(len(ids)))
+
+    def one(tokens):
+        logits = engine.decode_step([StepEntry(r, [t], [0]) for r, t in zip(ids, tokens)])
+        return sampler(logits, params, numbers, [0] * len(ids)).tolist()
+
+    for _ in range(warmup):
+        tokens = one(tokens)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tokens = one(tokens)
+    torch.cuda.synchronize()
+    sec = time.perf_counter() - t0
+    bk = engine._graphs.buckets[max(engine._graphs.buckets)]
+    return sec / steps * 1e3, bk.total * 4, len(ids) * 4
+
+
+def measure_decode(engine, batch, context, steps, warmup, torch, e2e=False):
+    start_ctx = context - (steps + warmup) * (2 if e2e else 1) - 2
+    ids = fill_requests(engine, batch, start_ctx, torch)
+    try:
+        dev = decode_device_timed(engine, ids, steps, warmup, torch)
+        host = decode_e2e(engine, ids, steps, warmup, torch) if e2e else None
+    finally:
+        for r in ids:
+            engine.finish(r)
+    return dev, host
+
+
+def measure_prefill(engine, tokens, reps, torch):
+    from tinyinfer_b200 import StepEntry
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, engine.plan.vocab_size, (tokens,), generator=g).tolist()
+    times = []
+    for i in range(reps + 1):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([StepEntry(("prefill", i), prompt, [tokens - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.finish(("prefill", i))
+        if i:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "beyondHJM/tinyinfer.cpp is a CMake C++/CUDA project; pip reports "
+                          "\"Neither 'setup.py' nor 'pyproject.toml' found\", so it cannot be "
+                          "installed offline as the contract asks"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; this engine does no work on several (asked for {args.gpus})")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    from tinyinfer_b200 import Engine
+
+    cfg = dict(QWEN3_0_6B)
+    cfg["max_position_embeddings"] = max(args.context, 2048)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk, pk_kind = peaks()
+    nums = model_numbers(cfg)
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE,
+                    max_tokens=max_batch * args.context, max_requests=max_batch + 1)
+
+    (ms, clocks, launches), (e2e_ms, h2d, d2h) = measure_decode(
+        engine, args.batch, args.context, args.steps, warmup, torch, e2e=True)
+    ctx_mid = args.context - args.steps // 2
+    step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            (pms, _, _), _ = measure_decode(engine, b, args.context, min(args.steps, 32), warmup, torch)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+
+    pf_tokens = 2048
+    pf_ms = measure_prefill(engine, pf_tokens, 3, torch)
+    pf_frac = prefill_flops(cfg, pf_tokens) / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+
+    value = args.batch / (ms * 1e-3)
+    line = {
+        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-0.6B shape)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights, random token ids, random keys and values",
+        "config": {
+            "model": "Qwen3-0.6B shape", "layers": cfg["num_hidden_layers"],
+            "layers_full": full_layers, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "tied": True, "global_batch": args.batch,
+            "seq_len": args.context, "page_size": PAGE, "parallelism": "single GPU",
+            "cuda_graph": True, "l2": "working set > L2, no flush", "peaks": pk_kind,
+        },
+        "clocks": clocks,
+        "e2e": {"value": round(args.batch / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(pf_tokens / (pf_ms * 1e-3), 1), "tokens": pf_tokens,
+                    "ms": round(pf_ms, 3), "frac": round(pf_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        # the reference publishes one number that compares: ~318 tok/s for one sequence with
+        # CUDA graphs on an A100 (README.md:118-119); the batch-1 point stands against it
+        "vs_baseline_b1": round(points["decode_b1"] / 318.0, 2) if "decode_b1" in points else None,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -17,6 +17,9 @@ F32 = torch.float32
 class RefOps:
     name = "reference"
 
+    def check_status(self):
+        pass
+
     # ---- weights -------------------------------------------------------------------------
     def pack_linear(self, w):
         return w.contiguous()
@@ -107,3 +110,27 @@ class RefOps:
         idx = torch.arange(logits.shape[1], device=logits.device).expand_as(logits)
         big = torch.full_like(idx, logits.shape[1])
         out.copy_(torch.where(logits == mx, idx, big).min(dim=-1).values.to(out.dtype))
+
+    def sample(self, logits, temperature, top_k, top_p, uniform, out):
+        """Sort-based statement of the sampling kernel's rule (see csrc/sampling.cu)."""
+        for r in range(logits.shape[0]):
+            x = logits[r].double()
+            t = float(temperature[r])
+            if not t > 0.0:
+                out[r] = int((x == x.max()).nonzero()[0])
+                continue
+            keep = torch.ones_like(x, dtype=torch.bool)
+            k = int(top_k[r])
+            if 0 < k < x.numel():
+                keep &= x >= torch.sort(x, descending=True).values[k - 1]
+            e = torch.where(keep, torch.exp((x - x.max()) / t), torch.zeros_like(x))
+            p = float(top_p[r])
+            if p < 1.0:
+                vals, order = torch.sort(e, descending=True, stable=True)
+                cum = torch.cumsum(vals, 0)
+                cut = int((cum >= p * e.sum()).nonzero()[0])
+                keep &= x >= x[order[cut]]
+                e = torch.where(keep, e, torch.zeros_like(e))
+            run = torch.cumsum(e, 0)
+            hit = (run > float(uniform[r]) * e.sum()).nonzero()
+            out[r] = int(hit[0]) if hit.numel() else int(keep.nonzero()[-1])

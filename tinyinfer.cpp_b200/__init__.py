@@ -8,10 +8,11 @@ generation on top (``engine``), sampling (``sampling``) and hand-written CUDA
 kernels (``csrc``, bound in ``kernels``).
 """
 from .config import ConfigError, Qwen3Config, load_config, register_architecture
-from .engine import Engine, StepEntry
+from .engine import Engine, LLM, StepEntry
+from .sampling import SamplingParams
 from .weights import WeightsError, write_random_model
 
 __version__ = "0.1.0"
 
-__all__ = ["ConfigError", "Engine", "Qwen3Config", "StepEntry", "WeightsError", "load_config",
+__all__ = ["ConfigError", "Engine", "LLM", "Qwen3Config", "SamplingParams", "StepEntry", "WeightsError", "load_config",
            "register_architecture", "write_random_model"]

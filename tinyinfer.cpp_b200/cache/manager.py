@@ -11,7 +11,7 @@ request's next token; all pages go back when the request ends.  Nothing is clear
 on reuse: kernels read only positions below the request's length.
 
 Beside the pages every live request holds one *state slot*, an index into
-``[max_requests, *shape]`` tensors of the cache slots whose mixers keep state of
+``[max_requests + 1, *shape]`` tensors of the cache slots whose mixers keep state of
 fixed size.  Such state is zeroed when the slot is handed to a new request.
 
 The reference keeps one contiguous buffer per sequence, sized for ``--max-seq``
@@ -60,7 +60,7 @@ class _PagedGroup:
         return -(-length // self.page_size)
 
     def new_pages_needed(self, req, new_length: int) -> int:
-        return max(0, self.blocks_for(new_length) - len(self.tables[req]))
+        return max(0, self.blocks_for(new_length) - len(self.tables.get(req, ())))
 
     def first_needed_block(self, length: int) -> int:
         """Index of the first block the token at position ``length`` may still read."""
@@ -97,18 +97,22 @@ class CacheManager:
                 self._state_specs[slot] = spec
             elif spec is not None:
                 raise TypeError(f"cache slot {slot}: unknown cache spec {spec!r}")
+        self.null_page = num_pages
         self.state_slots = IdPool(max_requests, "state slot")
         self._lengths: dict[Hashable, int] = {}
         self._state_slot: dict[Hashable, int] = {}
         if device is not None:
             for g in self.groups:
                 s = g.spec
+                # one page more than the pool hands out: ``null_page``, where padding rows of a
+                # fixed-size (graph) batch write and read without touching a request's pages
                 g.storage = torch.zeros(
-                    (len(g.cache_slots), num_pages, 2, s.num_kv_heads, page_size, s.head_dim),
+                    (len(g.cache_slots), num_pages + 1, 2, s.num_kv_heads, page_size, s.head_dim),
                     dtype=kv_dtype, device=device)
             for slot, spec in self._state_specs.items():
+                # one slot more than requests can hold, for padding rows
                 self._state_storage[slot] = torch.zeros(
-                    (max_requests, *spec.shape), dtype=spec.dtype, device=device)
+                    (max_requests + 1, *spec.shape), dtype=spec.dtype, device=device)
 
     # ---- requests ------------------------------------------------------------------------
     def add_request(self, req: Hashable) -> None:
@@ -135,8 +139,9 @@ class CacheManager:
         return self._state_slot[req]
 
     def pages_needed(self, req: Hashable, num_tokens: int) -> list[int]:
-        """New pages each group must hand out before ``num_tokens`` more tokens fit."""
-        new_len = self._lengths[req] + num_tokens
+        """New pages each group must hand out before ``num_tokens`` more tokens fit
+        (a request that is not live yet counts from length 0)."""
+        new_len = self._lengths.get(req, 0) + num_tokens
         return [g.new_pages_needed(req, new_len) for g in self.groups]
 
     def can_append(self, req: Hashable, num_tokens: int) -> bool:
@@ -157,6 +162,40 @@ class CacheManager:
         start = self._lengths[req]
         self._lengths[req] = start + num_tokens
         return start
+
+    def reserve_step(self, items: Sequence[tuple[Hashable, int]],
+                     max_position: Optional[int] = None) -> list[int]:
+        """Make room for one step: ``items`` are (request, number of new tokens).  Requests
+        that are not live yet are added.  Either every item gets its room or nothing
+        changes and ``OutOfPages`` is raised.  Returns each item's start position."""
+        seen = set()
+        new = []
+        for req, n in items:
+            if req in seen:
+                raise ValueError(f"request {req!r} appears twice in one step")
+            seen.add(req)
+            if n < 1:
+                raise ValueError(f"request {req!r} brings no tokens")
+            if req not in self._lengths:
+                new.append(req)
+        if len(new) > self.state_slots.num_free:
+            raise OutOfPages(
+                f"{len(new)} new requests, {self.state_slots.num_free} request slots are free")
+        need = [0] * len(self.groups)
+        for req, n in items:
+            end = self._lengths.get(req, 0) + n
+            if max_position is not None and end > max_position:
+                raise ValueError(
+                    f"request {req!r} would reach {end} tokens; the model allows {max_position}")
+            for g, k in enumerate(self.pages_needed(req, n)):
+                need[g] += k
+        for g, k in enumerate(need):
+            if k > self.groups[g].pool.num_free:
+                raise OutOfPages(
+                    f"the step needs {k} pages of group {g}, {self.groups[g].pool.num_free} are free")
+        for req in new:
+            self.add_request(req)
+        return [self.append(req, n) for req, n in items]
 
     def release_passed(self, req: Hashable) -> int:
         """Give back pages that lie wholly behind a window.  Returns how many were freed."""

@@ -61,6 +61,7 @@ class Qwen3Config:
     tie_word_embeddings: bool = False
     sliding_window: Optional[int] = None
     layer_types: tuple[str, ...] = ()
+    eos_token_ids: tuple[int, ...] = ()
 
     ARCHITECTURE = "Qwen3ForCausalLM"
 
@@ -117,7 +118,16 @@ class Qwen3Config:
                     f"'{SLIDING}' layers need a positive integer 'sliding_window', got {window!r}")
         else:
             window = None
+        eos = cfg.get("eos_token_id")
+        if eos is None:
+            eos = []
+        elif isinstance(eos, int) and not isinstance(eos, bool):
+            eos = [eos]
+        if not isinstance(eos, (list, tuple)) or any(
+                isinstance(e, bool) or not isinstance(e, int) or not 0 <= e < vocab for e in eos):
+            raise ConfigError(f"'eos_token_id' must be token ids below vocab_size, got {eos!r}")
         return Qwen3Config(
+            eos_token_ids=tuple(eos),
             num_hidden_layers=layers, hidden_size=hidden, num_attention_heads=heads,
             num_key_value_heads=kv_heads, head_dim=head_dim, intermediate_size=inter,
             vocab_size=vocab, max_position_embeddings=max_pos,
@@ -129,6 +139,7 @@ class Qwen3Config:
         """The ``config.json`` content that reads back as this configuration."""
         d = asdict(self)
         d["layer_types"] = list(self.layer_types)
+        d["eos_token_id"] = list(d.pop("eos_token_ids")) or None
         d["architectures"] = [self.ARCHITECTURE]
         d["model_type"] = "qwen3"
         d["hidden_act"] = "silu"

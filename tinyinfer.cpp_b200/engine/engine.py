@@ -85,6 +85,7 @@ class Engine:
                                   num_pages=num_pages, max_requests=max_requests,
                                   kv_dtype=self.dtype, device=self.device)
         self.last_batch: Optional[StepBatch] = None
+        self._graphs = None
 
     # ---- requests ------------------------------------------------------------------------
     def add_request(self, req_id: Hashable) -> None:
@@ -100,39 +101,8 @@ class Engine:
     # ---- the step ------------------------------------------------------------------------
     def reserve(self, entries: Sequence[StepEntry]) -> list[int]:
         """Make room in the cache for the step's tokens, for all entries or for none."""
-        seen = set()
-        new = []
-        for e in entries:
-            if e.req_id in seen:
-                raise ValueError(f"request {e.req_id!r} appears twice in one step")
-            seen.add(e.req_id)
-            if len(e.tokens) < 1:
-                raise ValueError(f"request {e.req_id!r} brings no tokens")
-            if not self.cache.has_request(e.req_id):
-                new.append(e.req_id)
-        if len(new) > self.cache.state_slots.num_free:
-            raise OutOfPages(f"{len(new)} new requests, {self.cache.state_slots.num_free} slots free")
-        for r in new:
-            self.cache.add_request(r)
-        try:
-            need = [0] * len(self.cache.groups)
-            for e in entries:
-                end = self.cache.length(e.req_id) + len(e.tokens)
-                if end > self.plan.max_position:
-                    raise ValueError(
-                        f"request {e.req_id!r} would reach {end} tokens; the model's "
-                        f"max_position_embeddings is {self.plan.max_position}")
-                for g, n in enumerate(self.cache.pages_needed(e.req_id, len(e.tokens))):
-                    need[g] += n
-            free = self.cache.free_pages()
-            for g, n in enumerate(need):
-                if n > free[g]:
-                    raise OutOfPages(f"step needs {n} pages of group {g}, {free[g]} are free")
-        except Exception:
-            for r in new:
-                self.cache.free_request(r)
-            raise
-        return [self.cache.append(e.req_id, len(e.tokens)) for e in entries]
+        return self.cache.reserve_step([(e.req_id, len(e.tokens)) for e in entries],
+                                       self.plan.max_position)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one batch; returns logits ``[wanted, vocab]`` in the order of entries and ``want``."""
@@ -153,6 +123,27 @@ class Engine:
         for e in entries:
             self.cache.release_passed(e.req_id)
         self.last_batch = batch
+        return logits
+
+    def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step in which every request brings one token and wants its logits, replayed from a
+        CUDA graph.  Returns ``[requests, vocab]``; the tensor is reused by the next call."""
+        entries = list(entries)
+        vocab = self.plan.vocab_size
+        for e in entries:
+            if len(e.tokens) != 1 or list(e.want) != [0]:
+                raise ValueError("decode_step takes one token per request and wants its logits")
+            if not 0 <= int(e.tokens[0]) < vocab:
+                raise ValueError(f"request {e.req_id!r}: token id {e.tokens[0]} is outside [0, {vocab})")
+        if not entries:
+            return torch.empty((0, vocab), dtype=torch.float32, device=self.device)
+        if self._graphs is None:
+            from .graphs import DecodeGraphs
+            self._graphs = DecodeGraphs(self)
+        starts = self.reserve(entries)
+        logits = self._graphs.run(entries, starts)
+        for e in entries:
+            self.cache.release_passed(e.req_id)
         return logits
 
     def forward(self, batch: StepBatch) -> torch.Tensor:

@@ -1,0 +1,114 @@
+"""The Python entry point: token ids in, generated token ids out.
+
+``LLM`` owns an engine, a scheduler and a sampler and runs the loop the reference runs in
+``main`` (prefill, then one token per live sequence per step, src/main.cpp:210-297), but over
+the one step function: prompt portions and decoding tokens share batches, and requests
+come and go while others are running.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Any, Mapping, Optional, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .batch import StepEntry
+from .engine import Engine
+from .scheduler import Request, Scheduler
+
+
+@dataclass
+class Generation:
+    prompt: list[int]
+    tokens: list[int]
+    finish_reason: Optional[str]
+    preemptions: int = 0
+
+
+@dataclass
+class RunStats:
+    steps: int = 0
+    prompt_tokens: int = 0        # tokens run as parts of prompts (recomputed ones included)
+    decode_tokens: int = 0        # tokens run one at a time after a request's prompt
+    generated: int = 0
+    preemptions: int = 0
+    seconds: float = 0.0
+    step_log: list = field(default_factory=list)
+
+
+class LLM:
+    """model_dir or (config, seed); ``max_seq`` caps a request's context (the reference's
+    ``--max-seq``, default 2048, src/main.cpp:131,150); the cache holds ``kv_tokens`` tokens
+    (default ``max_num_seqs * max_seq``, what the reference allocates, src/inference.cu:146-148)."""
+
+    def __init__(self, model_dir: Optional[str] = None, *, config: Optional[Mapping[str, Any]] = None,
+                 seed: Optional[int] = None, dtype="bfloat16", device="cuda:0",
+                 max_seq: int = 2048, max_num_seqs: int = 16, max_batched_tokens: int = 2048,
+                 chunk: Optional[int] = None, page_size: int = 16,
+                 kv_tokens: Optional[int] = None, cuda_graph: bool = False, ops=None):
+        if kv_tokens is None:
+            kv_tokens = max_num_seqs * max_seq
+        self.engine = Engine(model_dir, config=config, seed=seed, dtype=dtype, device=device,
+                             page_size=page_size, num_pages=-(-kv_tokens // page_size),
+                             max_requests=max_num_seqs, ops=ops)
+        self.max_seq = min(max_seq, self.engine.plan.max_position)
+        self.max_num_seqs = max_num_seqs
+        self.max_batched_tokens = max_batched_tokens
+        self.chunk = chunk
+        self.cuda_graph = cuda_graph
+        self.sampler = Sampler(self.engine.ops, self.engine.device)
+        eos = getattr(self.engine.config, "eos_token_ids", ())
+        self.eos_token_ids = tuple(eos)
+        self.stats = RunStats()
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: SamplingParams | Sequence[SamplingParams] = SamplingParams(),
+                 log_steps: bool = False) -> list[Generation]:
+        if isinstance(params, SamplingParams):
+            params = [params] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        engine = self.engine
+        sched = Scheduler(engine.cache, max_num_seqs=self.max_num_seqs,
+                          max_batched_tokens=self.max_batched_tokens, chunk=self.chunk,
+                          max_position=self.max_seq, eos_token_ids=self.eos_token_ids)
+        requests = [Request(req_id=("gen", i), prompt=[int(t) for t in p], params=sp)
+                    for i, (p, sp) in enumerate(zip(prompts, params))]
+        for r in requests:
+            sched.add(r)
+        stats = self.stats = RunStats()
+        t0 = time.perf_counter()
+        while sched.has_work():
+            plan = sched.schedule()
+            if not plan:
+                raise RuntimeError("the scheduler found nothing to run although requests wait; "
+                                   "the cache pool is too small for the oldest request")
+            entries = []
+            for s in plan:
+                toks = s.request.tokens[s.start:s.start + s.count]
+                entries.append(StepEntry(s.request.req_id, toks, [s.count - 1] if s.samples else []))
+            if self.cuda_graph and all(s.count == 1 and s.samples for s in plan):
+                logits = engine.decode_step(entries)
+            else:
+                logits = engine.step(entries)
+            samplers = [s for s in plan if s.samples]
+            ids = self.sampler(logits, [s.request.params for s in samplers],
+                               [s.request.number for s in samplers],
+                               [len(s.request.output) for s in samplers])
+            sampled = ids.tolist()
+            stats.steps += 1
+            for s in plan:
+                if s.count == 1 and s.start >= len(s.request.prompt):
+                    stats.decode_tokens += 1
+                else:
+                    stats.prompt_tokens += s.count
+            stats.generated += len(sampled)
+            if log_steps:
+                stats.step_log.append([(s.request.req_id, s.start, s.count) for s in plan])
+            sched.step_done(plan, sampled)
+        engine.ops.check_status()
+        stats.preemptions = sched.num_preemptions
+        stats.seconds = time.perf_counter() - t0
+        return [Generation(r.prompt, r.output, r.finish_reason, r.preemptions) for r in requests]

@@ -1,0 +1,109 @@
+"""CUDA-graph replay of decode steps.
+
+A step in which every request brings exactly one token and wants its logits has a fixed
+shape once the batch is padded to a bucket (1, 2, 4, ... requests).  For each bucket the
+whole forward is captured once over static device buffers (token ids, positions, block
+tables, lengths); a later step copies its integers into those buffers with one transfer
+and replays the graph.  Padding rows use the cache's null page, so they touch no request.
+Kernels take everything that varies between steps from device memory, and a row's result
+does not depend on the batch around it, so replay gives the same logits as the eager step.
+The reference captures one graph per decode batch size (src/inference.cu:267-295) and
+checks replay against eager the same way (src/inference.cu:297-341).
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .batch import StepBatch, StepEntry
+
+
+def bucket_of(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class _Bucket:
+    def __init__(self, engine, size: int):
+        cache = engine.cache
+        dev = engine.device
+        self.size = size
+        self.width = -(-engine.plan.max_position // cache.page_size)
+        groups = len(cache.groups)
+        b = size
+        # layout of the packed integers: tok, pos, ctx, slots, then one table per group
+        self.total = 4 * b + groups * b * self.width
+        self.host = torch.empty(self.total, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
+        d = self.dev
+        ar = torch.arange(b, dtype=torch.int32, device=dev)
+        tables = [d[4 * b + g * b * self.width: 4 * b + (g + 1) * b * self.width].view(b, self.width)
+                  for g in range(groups)]
+        self.batch = StepBatch(
+            num_tokens=b, num_requests=b, num_logit_rows=b, act_dtype=engine.dtype,
+            q_lens=[1] * b, q_starts=[0] * b, ctx_lens=[engine.plan.max_position] * b,
+            max_q_len=1, max_ctx_len=engine.plan.max_position,
+            token_ids=d[0:b], positions=d[b:2 * b], req_of_tok=ar,
+            cu_q=torch.arange(b + 1, dtype=torch.int32, device=dev),
+            q_start_dev=d[b:2 * b], ctx_len_dev=d[2 * b:3 * b], logit_rows=ar,
+            state_slots=d[3 * b:4 * b], block_tables=tables)
+        self.batch.scratch["graph"] = True
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def fill(self, engine, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
+        cache = engine.cache
+        b, w = self.size, self.width
+        n = len(entries)
+        buf = self.host.numpy()
+        buf[:4 * b] = 0
+        buf[2 * b:3 * b] = 1                                      # padding rows: one token
+        buf[3 * b:4 * b] = cache.max_requests                     # padding rows: spare state slot
+        buf[4 * b:] = cache.null_page
+        buf[0:n] = [int(e.tokens[0]) for e in entries]
+        buf[b:b + n] = starts
+        buf[2 * b:2 * b + n] = np.asarray(starts) + 1
+        buf[3 * b:3 * b + n] = [cache.state_slot(e.req_id) for e in entries]
+        for g in range(len(cache.groups)):
+            base = 4 * b + g * b * w
+            for i, e in enumerate(entries):
+                tb = cache.block_table(g, e.req_id)
+                buf[base + i * w: base + i * w + len(tb)] = tb
+        self.dev.copy_(self.host, non_blocking=True)
+
+
+class DecodeGraphs:
+    def __init__(self, engine):
+        self.engine = engine
+        self.buckets: dict[int, _Bucket] = {}
+
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        eng = self.engine
+        size = bucket_of(len(entries))
+        bk = self.buckets.get(size)
+        if bk is None:
+            bk = self.buckets[size] = _Bucket(eng, size)
+        bk.fill(eng, entries, starts)
+        if bk.graph is None:
+            # run once outside capture (loads kernels, sizes the allocator), then capture
+            side = torch.cuda.Stream(device=eng.device)
+            side.wait_stream(torch.cuda.current_stream(eng.device))
+            with torch.cuda.stream(side):
+                eng.forward(bk.batch)
+            torch.cuda.current_stream(eng.device).wait_stream(side)
+            torch.cuda.synchronize(eng.device)
+            graph = torch.cuda.CUDAGraph()
+            before = getattr(eng.ops, "launches", 0)
+            with torch.cuda.graph(graph):
+                bk.logits = eng.forward(bk.batch)
+            bk.graph = graph
+            bk.launches = getattr(eng.ops, "launches", 0) - before
+        bk.graph.replay()
+        if hasattr(eng.ops, "launches"):
+            eng.ops.launches += bk.launches
+        return bk.logits[:len(entries)]

@@ -69,6 +69,9 @@ class CudaOps:
         self.core.ti_last_error.restype = ctypes.c_char_p
         self._declare()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # kernels launched so far: entry points called eagerly, plus, for every graph replay,
+        # the entry points that were captured into that graph
+        self.launches = 0
 
     # ---- plumbing ------------------------------------------------------------------------
     def _declare(self) -> None:
@@ -89,6 +92,7 @@ class CudaOps:
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def _ok(self, rc: int, lib=None) -> None:
+        self.launches += 1
         if rc != 0:
             raise KernelError((lib or self.core).ti_last_error().decode("utf-8", "replace"))
 
