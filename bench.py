@@ -235,6 +235,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -258,10 +260,19 @@ def main() -> int:
         cfg["num_hidden_layers"] = args.layers
     pk, pk_kind = peaks()
     nums = model_numbers(cfg)
-    max_batch = max(args.batch, 1 if args.no_points else 64)
+    max_batch = max(args.batch, 1 if (args.no_points or args.only) else 64)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE,
                     max_tokens=max_batch * args.context, max_requests=max_batch + 1)
 
+    if args.only == "decode":
+        (ms, _, launches), _ = measure_decode(engine, args.batch, args.context, args.steps, warmup, torch)
+        print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context,
+                          "ms_per_step": round(ms, 4), "gpu_launches": launches}))
+        return 0
+    if args.only == "prefill":
+        pf_ms = measure_prefill(engine, 2048, max(1, args.steps), torch)
+        print(json.dumps({"only": "prefill", "tokens": 2048, "ms": round(pf_ms, 3)}))
+        return 0
     (ms, clocks, launches), (e2e_ms, h2d, d2h) = measure_decode(
         engine, args.batch, args.context, args.steps, warmup, torch, e2e=True)
     ctx_mid = args.context - args.steps // 2

@@ -1,0 +1,268 @@
+"""Each CUDA kernel alone against its plain PyTorch statement, at sizes other than the engine's."""
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from ref_ops import RefOps
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tinyinfer_b200.kernels import cuda_ops
+    return cuda_ops(DEV)
+
+
+def _rand(shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=DEV) * scale).to(dtype)
+
+
+def _sum_rtol(k):
+    """Bound on the rounding of a float32 sum of k products, as a fraction of the largest
+    output: the error of a running sum grows like sqrt(k) roundings of 2^-24 each."""
+    return 2e-7 * max(4.0, math.sqrt(k))
+
+
+def _close(got, want, rtol, what):
+    got, want = got.double(), want.double()
+    err = (got - want).abs().max().item()
+    scale = want.abs().max().item()
+    assert err <= rtol * max(scale, 1e-30), f"{what}: error {err:.3e} against scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(ops, dtype):
+    table = _rand((331, 80), dtype)
+    tok = torch.tensor([0, 330, 7, 7, 100], dtype=torch.int32, device=DEV)
+    out, ref = torch.empty((5, 80), device=DEV), torch.empty((5, 80), device=DEV)
+    ops.embed(table, tok, out)
+    RefOps().embed(table, tok, ref)
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("n", [1, 48, 80, 1000, 5120])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(ops, n, out_dtype):
+    x = _rand((7, n), scale=3.0)
+    w = 1 + _rand((n,), seed=1, scale=0.1)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    for r in (None, rows):
+        k = 7 if r is None else 3
+        out = torch.empty((k, n), dtype=out_dtype, device=DEV)
+        ref = torch.empty((k, n), dtype=out_dtype, device=DEV)
+        ops.rmsnorm(x, w, 1e-5, out, rows=r)
+        RefOps().rmsnorm(x, w, 1e-5, ref, rows=r)
+        _close(out, ref, 1e-6 if out_dtype == torch.float32 else 8e-3, f"rmsnorm n={n}")
+
+
+@pytest.mark.parametrize("a_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 5, 3), (5, 261, 1024), (70, 130, 50), (129, 64, 17), (3, 331, 80)])
+def test_linear_every_dtype_and_size(ops, a_dtype, w_dtype, shape):
+    m, n, k = shape
+    a, w = _rand((m, k), a_dtype), _rand((n, k), w_dtype, seed=1)
+    base = _rand((m, n), seed=2)
+    for acc in (False, True):
+        out, ref = base.clone(), base.clone()
+        ops.linear(a, w, out, accumulate=acc)
+        RefOps().linear(a, w, ref, accumulate=acc)
+        _close(out, a.double() @ w.double().T + (base.double() if acc else 0), _sum_rtol(k),
+               f"linear {shape} acc={acc}")
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 33, 64])
+@pytest.mark.parametrize("nk", [(48, 64), (100, 96), (4096, 1024), (1024, 3072), (331, 128)])
+def test_linear_few_rows_bf16(ops, m, nk):
+    """The decode product (tensor cores, operands straight from global memory)."""
+    n, k = nk
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1)
+    base = _rand((m, n), seed=2)
+    for acc in (False, True):
+        out = base.clone()
+        ops.linear(a, w, out, accumulate=acc)
+        want = a.double() @ w.double().T + (base.double() if acc else 0)
+        _close(out, want, _sum_rtol(k), f"few rows m={m} n={n} k={k} acc={acc}")
+    # a row's result does not depend on how many rows there are
+    alone = torch.empty((1, n), device=DEV)
+    ops.linear(a[m - 1:m], w, alone)
+    full = torch.empty((m, n), device=DEV)
+    ops.linear(a, w, full)
+    assert torch.equal(alone[0], full[m - 1])
+
+
+@pytest.mark.parametrize("m", [65, 128, 129, 300, 1000])
+@pytest.mark.parametrize("nk", [(128, 64), (136, 72), (4096, 1024), (1024, 3072), (1000, 520), (331, 128)])
+def test_linear_many_rows_bf16(ops, m, nk):
+    """The prefill product (tcgen05, TMA, tensor memory); (331, 128) falls to the plain kernel."""
+    n, k = nk
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1)
+    base = _rand((m, n), seed=2)
+    for acc in (False, True):
+        out = base.clone()
+        ops.linear(a, w, out, accumulate=acc)
+        ops.check_status()
+        want = a.double() @ w.double().T + (base.double() if acc else 0)
+        _close(out, want, _sum_rtol(k), f"many rows m={m} n={n} k={k} acc={acc}")
+    # a row's result does not depend on how many rows there are (above the few-rows kernel)
+    if m >= 70:
+        part = torch.empty((70, n), device=DEV)
+        ops.linear(a[m - 70:], w, part)
+        full = torch.empty((m, n), device=DEV)
+        ops.linear(a, w, full)
+        assert torch.equal(part, full[m - 70:])
+
+
+@pytest.mark.parametrize("m", [1, 8, 40, 64, 100])
+@pytest.mark.parametrize("hk", [(128, 320), (1024, 3072), (80, 176), (64, 24)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gate_up_swiglu(ops, m, hk, dtype):
+    hidden, inter = hk
+    wdt = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    gate, up = _rand((inter, hidden), wdt, seed=1, scale=0.2), _rand((inter, hidden), wdt, seed=2, scale=0.2)
+    h = _rand((m, hidden), dtype)
+    out = torch.empty((m, inter), dtype=dtype, device=DEV)
+    ref = torch.empty((m, inter), dtype=dtype, device=DEV)
+    ops.gate_up_swiglu(h, ops.pack_gate_up(gate, up), out)
+    r = RefOps()
+    r.gate_up_swiglu(h, r.pack_gate_up(gate, up), ref)
+    _close(out, ref, 2e-5 if dtype == torch.float32 else 8e-3, f"swiglu m={m} {hk}")
+
+
+def _paged_case(num_heads, num_kv, hd, page_size, ctx_lens, q_lens, dtype, seed=0):
+    """Requests with ``ctx_lens[r]`` tokens of which the last ``q_lens[r]`` are new; pages are
+    handed out in a scrambled order so that neighbours in a request are far apart in memory."""
+    r = len(ctx_lens)
+    blocks = [-(-c // page_size) for c in ctx_lens]
+    num_pages = sum(blocks) + 3
+    perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max(blocks)
+    bt = torch.full((r, width), -1, dtype=torch.int32)
+    it = iter(perm)
+    for i, b in enumerate(blocks):
+        bt[i, :b] = torch.tensor([next(it) for _ in range(b)], dtype=torch.int32)
+    pages = _rand((num_pages, 2, num_kv, page_size, hd), dtype, seed=seed + 1)
+    positions, req_of_tok, dec, chk, tiles = [], [], [], [], []
+    for i, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
+        if ql > 1:
+            tiles += [[i, len(positions) + lo, min(64, ql - lo)] for lo in range(0, ql, 64)]
+        for j in range(ql):
+            (dec if ql == 1 else chk).append(len(positions))
+            positions.append(c - ql + j)
+            req_of_tok.append(i)
+    ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), decode_rows=ti(dec),
+                           chunk_rows=ti(chk), chunk_tiles=ti(tiles).view(-1, 3), max_position=max(ctx_lens), max_ctx_len=max(ctx_lens))
+    cache = SimpleNamespace(pages=pages, block_table=bt.to(DEV), page_size=page_size, writes=True)
+    q = _rand((len(positions), num_heads * hd), dtype, seed=seed + 2)
+    return step, cache, q
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("geom", [(4, 2, 16, 16), (3, 1, 48, 16), (16, 8, 128, 16), (8, 1, 64, 32),
+                                  (6, 3, 80, 16), (32, 2, 32, 16), (5, 5, 144, 16), (2, 1, 256, 64)])
+@pytest.mark.parametrize("window", [None, 1, 37])
+def test_paged_attention(ops, dtype, geom, window):
+    """Decoding rows and prompt portions side by side, lengths around the edges of pages and
+    tiles, against the plain statement."""
+    heads, kv, hd, ps = geom
+    ctx = [1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 200, 517, 40, 129, 300, 64, 700]
+    qls = [1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 23, 2, 300, 64, 131]
+    step, cache, q = _paged_case(heads, kv, hd, ps, ctx, qls, dtype)
+    out, ref = torch.zeros_like(q), torch.zeros_like(q)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(q, step, cache, out, heads, kv, hd, window, scale)
+    RefOps().paged_attention(q, step, cache, ref, heads, kv, hd, window, scale)
+    ops.check_status()
+    _close(out, ref, 2e-5 if dtype == torch.float32 else 1.5e-2, f"attention {geom} window={window}")
+
+
+def test_decode_attention_finds_a_far_key(ops):
+    """One key among thousands carries the whole weight: its value must come back."""
+    heads, kv, hd, ps = 8, 2, 64, 16
+    ctx = [3000, 2049]
+    step, cache, q = _paged_case(heads, kv, hd, ps, ctx, [1, 1], torch.bfloat16, seed=5)
+    cache.pages.mul_(0.05)
+    targets = [(0, 1234), (1, 2048 - 33)]
+    for r, p in targets:
+        page = int(cache.block_table[r, p // ps])
+        for h in range(kv):
+            cache.pages[page, 0, h, p % ps, :] = 4.0
+            cache.pages[page, 1, h, p % ps, :] = torch.arange(hd, device=DEV).to(torch.bfloat16)
+    q.fill_(4.0)
+    out = torch.zeros_like(q)
+    ops.paged_attention(q, step, cache, out, heads, kv, hd, None, 1.0 / math.sqrt(hd))
+    want = torch.arange(hd, device=DEV).to(torch.bfloat16).float().repeat(heads)
+    for row in range(2):
+        assert (out[row].float() - want).abs().max() < 0.51, "the far key's value was not returned"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("geom", [(4, 2, 16, 16), (3, 1, 48, 16), (16, 8, 128, 32), (5, 5, 144, 16)])
+def test_qk_norm_rope_store(ops, dtype, geom):
+    heads, kv, hd, ps = geom
+    ctx, qls = [5, 33, 64, 100], [5, 1, 17, 2]
+    step, cache, _ = _paged_case(heads, kv, hd, ps, ctx, qls, dtype)
+    t = step.positions.shape[0]
+    qkv = _rand((t, (heads + 2 * kv) * hd), seed=3, scale=2.0)
+    qw, kw = 1 + _rand((hd,), seed=4, scale=0.1), 1 + _rand((hd,), seed=5, scale=0.1)
+    inv_freq = torch.pow(torch.tensor(1e6, dtype=torch.float64),
+                         -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(DEV)
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.pages = cache.pages.clone()
+    q_out = torch.empty((t, heads * hd), dtype=dtype, device=DEV)
+    q_ref = torch.empty_like(q_out)
+    ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, inv_freq, step, cache, q_out, heads, kv, hd)
+    RefOps().qk_norm_rope_store(qkv, qw, kw, 1e-6, inv_freq, step, ref_cache, q_ref, heads, kv, hd)
+    tol = 3e-6 if dtype == torch.float32 else 8e-3
+    _close(q_out, q_ref, tol, "rotated queries")
+    _close(cache.pages, ref_cache.pages, tol, "pages after the store")
+    ops.check_status()
+
+
+def test_argmax_first_maximum_wins(ops):
+    logits = _rand((5, 151936))
+    logits[1, 77] = logits[1, 150000] = 50.0
+    logits[2, :] = 0.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    ref = torch.empty(5, dtype=torch.int32, device=DEV)
+    RefOps().argmax(logits, ref)
+    assert out.tolist() == ref.tolist() and out[1] == 77 and out[2] == 0
+
+
+def test_sample_matches_sorted_statement(ops):
+    vocab = 1537
+    logits = _rand((64, vocab), scale=3.0)
+    temp = torch.full((64,), 0.8, device=DEV)
+    temp[:4] = 0.0
+    top_k = torch.tensor([0, 5, 50, 1] * 16, dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 0.9, 0.5, 0.95] * 16, device=DEV)
+    u = torch.rand(64, generator=torch.Generator().manual_seed(1)).to(DEV)
+    out = torch.empty(64, dtype=torch.int32, device=DEV)
+    ref = torch.empty(64, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, top_k, top_p, u, out)
+    RefOps().sample(logits, temp, top_k, top_p, u, ref)
+    agree = (out == ref).float().mean().item()
+    assert agree >= 0.95, f"only {agree:.2f} of the rows agree with the sorted statement"
+    # a disagreement can only come from a rounding difference at a boundary: the tokens
+    # must then be neighbours among the kept ones
+    assert all(int(k) != 1 or int(o) == int(logits[i].argmax())
+               for i, (k, o) in enumerate(zip(top_k.tolist(), out.tolist())) if temp[i] > 0)
+
+
+def test_sample_follows_the_distribution(ops):
+    vocab, n = 50, 4000
+    base = _rand((1, vocab), scale=1.5)
+    logits = base.expand(n, vocab).contiguous()
+    u = torch.rand(n, generator=torch.Generator().manual_seed(2)).to(DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.ones(n, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+               torch.ones(n, device=DEV), u, out)
+    freq = torch.bincount(out.long(), minlength=vocab).float() / n
+    prob = torch.softmax(base[0], dim=-1)
+    assert (freq - prob).abs().max().item() < 0.03

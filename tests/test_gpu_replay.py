@@ -21,7 +21,7 @@ from util import BF16_RTOL, FP32_RTOL, TINY, assert_close_logits, make_model, ra
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [70, 45, 120, 33, 90, 64, 17, 2], "B": [100, 9, 33, 64, 250, 77, 1, 130],
-           "C": [150, 40, 300, 64, 97, 210, 31]}
+           "C": [150, 40, 300, 64, 97, 210, 31], "D": [200, 33, 520, 64, 130, 95, 17, 2]}
 TOL = {"float32": FP32_RTOL, "bfloat16": BF16_RTOL}
 FAMILIES = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
             "mixed": traces.mixed}
@@ -72,7 +72,7 @@ def _compare(steps, outputs, plain, rtol, what):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuttings_match_plain(tmp_path_factory, name, family, dtype):
     model_dir = make_model(tmp_path_factory.getbasetemp(), name)
     steps = FAMILIES[family](_requests(name))

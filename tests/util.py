@@ -25,7 +25,14 @@ TINY_C = dict(architectures=ARCH, num_hidden_layers=4, hidden_size=80, num_atten
               max_position_embeddings=512, sliding_window=24,
               layer_types=["full_attention", "sliding_attention", "sliding_attention",
                            "full_attention"])
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# sizes that the tensor-core kernels of the bfloat16 path take (head size 64, widths that are
+# multiples of 32), with one windowed layer
+TINY_D = dict(architectures=ARCH, num_hidden_layers=3, hidden_size=128, num_attention_heads=8,
+              num_key_value_heads=2, head_dim=64, intermediate_size=320, vocab_size=1008,
+              rope_theta=200000.0, rms_norm_eps=2e-6, tie_word_embeddings=True,
+              max_position_embeddings=1024, sliding_window=40,
+              layer_types=["full_attention", "sliding_attention", "full_attention"])
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 FP32_RTOL = 2e-5      # of the largest reference logit: float32 engine against float64 plain
 BF16_RTOL = 2e-2      # bfloat16 engine against plain with the reference's rounding points

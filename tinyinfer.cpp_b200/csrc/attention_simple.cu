@@ -93,7 +93,8 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(WARPS * 32)
-paged_attention_simple_kernel(const TQ* __restrict__ q, const int* __restrict__ positions,
+paged_attention_simple_kernel(const TQ* __restrict__ q, const int* __restrict__ rows,
+                              const int* __restrict__ positions,
                               const int* __restrict__ req_of_tok,
                               const int* __restrict__ block_table, int bt_stride,
                               const TC* __restrict__ pages, int num_pages, int page_size,
@@ -103,7 +104,7 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, const int* __restrict__ 
     __shared__ float so[WARPS][MAX_HEAD_DIM];
     __shared__ float sm[WARPS], sl[WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y, t = blockIdx.x;
+    const int h = blockIdx.y, t = rows ? rows[blockIdx.x] : blockIdx.x;
     const int kvh = h / (num_heads / num_kv_heads);
     const int pos = positions[t];
     const int r = req_of_tok[t];
@@ -204,22 +205,25 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
     return ti_check_launch("qk_norm_rope_store");
 }
 
-extern "C" int ti_paged_attention_simple(const void* q, int q_dtype, const int* positions,
+// `rows` (may be null) lists the tokens to compute; without it all `num_rows` tokens are computed.
+extern "C" int ti_paged_attention_simple(const void* q, int q_dtype, const int* rows,
+                                         const int* positions,
                                          const int* req_of_tok, const int* block_table,
                                          int bt_stride, const void* pages, int cache_dtype,
-                                         int num_pages, int page_size, int num_tokens,
+                                         int num_pages, int page_size, int num_rows,
                                          int num_heads, int num_kv_heads, int head_dim, int window,
                                          float scale, void* out, int* status, void* stream) {
-    if (num_tokens == 0) return 0;
+    if (num_rows == 0) return 0;
     TI_REQUIRE(head_dim >= 1 && head_dim <= MAX_HEAD_DIM,
                "paged_attention: head_dim %d must be at most %d", head_dim, MAX_HEAD_DIM);
     TI_REQUIRE(num_heads % num_kv_heads == 0, "paged_attention: %d heads over %d kv heads",
                num_heads, num_kv_heads);
-    dim3 grid(num_tokens, num_heads);
+    dim3 grid(num_rows, num_heads);
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TQ, TC)                                                                           \
     paged_attention_simple_kernel<TQ, TC><<<grid, WARPS * 32, 0, s>>>(                          \
-        (const TQ*)q, positions, req_of_tok, block_table, bt_stride, (const TC*)pages, num_pages, \
+        (const TQ*)q, rows, positions, req_of_tok, block_table, bt_stride, (const TC*)pages,     \
+        num_pages,                                                                              \
         page_size, num_heads, num_kv_heads, head_dim, window, scale, (TQ*)out, status)
     TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
 #undef CALL

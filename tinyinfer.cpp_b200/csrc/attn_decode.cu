@@ -1,0 +1,359 @@
+// Paged flash-decoding for single-token rows (bfloat16 cache, head_dim a multiple of 16 up to 128).
+//
+// A row is one new token of a request; it attends to the keys [lo, pos] of its request's
+// pages (lo > 0 only with a window).  The keys are cut into tiles of 32; the tiles of a row
+// are dealt to `num_splits` blocks per kv head.  A block is ONE warp: it streams its tiles
+// through a ring of shared-memory stages with cp.async, computes the scores of all query
+// heads of the kv group at once on the tensor cores (mma.sync m16n8k16, the group's heads
+// are the 16 rows of the A operand), keeps a float32 online softmax per head, multiplies the
+// probabilities with the values, and writes an unnormalised partial result with its running
+// maximum and sum.  A second kernel merges the partial results of a row.  The work is bound
+// by the bytes of keys and values; the tensor cores only keep the arithmetic out of the way.
+//
+// Everything that changes from step to step (positions, block tables) is read from device
+// memory, and the cut into splits depends only on the row's own length and on `num_splits`,
+// so a launch can be replayed from a CUDA graph.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE = 32;       // keys per tile
+constexpr int STAGES = 3;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;               // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                         unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(32)
+attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
+                   const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                   const int* __restrict__ block_table, int bt_stride,
+                   const bf16* __restrict__ pages, int num_pages, int page_size,
+                   int num_heads, int num_kv_heads, int window, float scale_log2,
+                   float* __restrict__ part_o, float* __restrict__ part_ml,
+                   int* __restrict__ status) {
+    constexpr int ROW_BYTES = HD * 2 + 16;          // padded: ldmatrix rows fall in distinct banks
+    constexpr int CHUNKS = HD / 8;                  // 16-byte chunks per key
+    constexpr int KSTEPS = HD / 16;
+    constexpr int NT_O = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int lane = threadIdx.x;
+    const int split = blockIdx.x, num_splits = gridDim.x;
+    const int kvh = blockIdx.y;
+    const int row = blockIdx.z;
+    const int group = num_heads / num_kv_heads;
+    const int t = rows ? rows[row] : row;
+    const int pos = positions[t];
+    const int* table = block_table + (size_t)req_of_tok[t] * bt_stride;
+    const int ctx = pos + 1;
+    const int lo = window > 0 ? max(0, ctx - window) : 0;
+    const int tile_lo = lo / TILE, tile_hi = (ctx + TILE - 1) / TILE;
+    const int per_split = (tile_hi - tile_lo + num_splits - 1) / num_splits;
+    const int my_lo = tile_lo + split * per_split;
+    const int my_hi = min(tile_hi, my_lo + per_split);
+
+    const int g = lane >> 2, tq = lane & 3;
+    const size_t kv_stride = (size_t)num_kv_heads * page_size * HD;   // keys -> values of a page
+    // partial results of this block: heads kvh*group + r, r < group
+    const size_t part_base = ((size_t)row * num_heads + (size_t)kvh * group) * num_splits + split;
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+    if (my_lo < my_hi) {
+        // queries of the group as the A operand: row r of the tile is head kvh*group + r
+        unsigned qa[KSTEPS][4];
+        const bf16* qbase = q + ((size_t)t * num_heads + (size_t)kvh * group) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int k0 = ks * 16 + tq * 2;
+            qa[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0) : 0u;
+            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0) : 0u;
+            qa[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0 + 8) : 0u;
+            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0 + 8) : 0u;
+        }
+
+        auto issue = [&](int tile, int stage) {
+            unsigned char* kdst = smem + (size_t)stage * 2 * TILE * ROW_BYTES;
+            unsigned char* vdst = kdst + TILE * ROW_BYTES;
+            // a tile is two runs of 16 keys; a run lies inside one page and is contiguous there
+            // (16 * HD elements), so a lane's source addresses advance by 512 bytes per copy
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int key0 = tile * TILE + r * 16;
+                int pg = -1;
+                if (key0 < ctx && key0 + 16 > lo) {
+                    pg = table[key0 / page_size];
+                    if (pg < 0 || pg >= num_pages) {
+                        if (lane == 0) atomicCAS(status, 0, 1);
+                        pg = -1;
+                    }
+                }
+                const bool valid = pg >= 0;
+                const bf16* ksrc = pages;
+                if (valid)
+                    ksrc = pages + (((size_t)pg * 2 * num_kv_heads + kvh) * page_size +
+                                    key0 % page_size) * HD + lane * 8;
+                const bf16* vsrc = valid ? ksrc + kv_stride : pages;
+#pragma unroll
+                for (int i = 0; i < 16 * CHUNKS / 32; ++i) {
+                    const int c = i * 32 + lane;                 // 16-byte chunk of the run
+                    const int off = (r * 16 + c / CHUNKS) * ROW_BYTES + (c % CHUNKS) * 16;
+                    cp_async16(kdst + off, ksrc + (valid ? i * 256 : 0), valid);
+                    cp_async16(vdst + off, vsrc + (valid ? i * 256 : 0), valid);
+                }
+            }
+        };
+
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (my_lo + s < my_hi) issue(my_lo + s, s);
+            cp_async_commit();
+        }
+        for (int tile = my_lo; tile < my_hi; ++tile) {
+            const int stage = (tile - my_lo) % STAGES;
+            if (tile + STAGES - 1 < my_hi) issue(tile + STAGES - 1, (tile - my_lo + STAGES - 1) % STAGES);
+            cp_async_commit();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            const unsigned char* ks = smem + (size_t)stage * 2 * TILE * ROW_BYTES;
+            const unsigned char* vs = ks + TILE * ROW_BYTES;
+
+            // scores of 16 heads x 32 keys
+            float s_acc[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                for (int jp = 0; jp < 2; ++jp) {
+                    unsigned b[4];
+                    // lanes 0-15: keys of tile 2jp, dims kk*16 (+8); lanes 16-31: keys of tile 2jp+1
+                    const int key = jp * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int dim = kk * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(b, ks + key * ROW_BYTES + dim * 2);
+                    mma_bf16(s_acc[2 * jp], qa[kk], b[0], b[1]);
+                    mma_bf16(s_acc[2 * jp + 1], qa[kk], b[2], b[3]);
+                }
+            }
+            // mask, scale, online softmax (rows g and g + 8 of the head tile)
+            const bool edge = tile * TILE < lo || tile * TILE + TILE > ctx;
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = s_acc[j][e] * scale_log2;
+                    if (edge) {
+                        const int key = tile * TILE + j * 8 + tq * 2 + (e & 1);
+                        if (key < lo || key >= ctx) v = -INFINITY;
+                    }
+                    s_acc[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+            float alpha[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                alpha[r] = m_new == -INFINITY ? 1.0f : exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+            }
+            // a tile always holds at least one visible key, so the running maxima are finite
+            float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2f(s_acc[j][e] - m_run[e >> 1]);
+                    s_acc[j][e] = p;
+                    sum[e >> 1] += p;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + sum[r];
+            if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < NT_O; ++i) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                    o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
+            }
+            // probabilities (bfloat16) times values
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                unsigned pa[4];
+                pa[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+                pa[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+                pa[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < NT_O / 2; ++dp) {
+                    unsigned b[4];
+                    // lanes 0-7: keys kk*16.., dims dp*16; 8-15: keys +8; 16-31: dims dp*16 + 8
+                    const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int dim = dp * 16 + (lane >> 4) * 8;
+                    ldmatrix_x4_trans(b, vs + key * ROW_BYTES + dim * 2);
+                    mma_bf16(o[2 * dp], pa, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+                }
+            }
+            __syncwarp();                         // the stage may be refilled
+        }
+        cp_async_wait<0>();
+    }
+    // the sums of a row live in the four lanes of a quad
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int head = g + 8 * r;
+        if (head >= group) continue;
+        const size_t idx = part_base + (size_t)head * num_splits;
+        float* po = part_o + idx * HD;
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+            *reinterpret_cast<float2*>(po + i * 8 + tq * 2) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+        }
+        if (tq == 0) {
+            part_ml[idx * 2] = m_run[r];
+            part_ml[idx * 2 + 1] = l_run[r];
+        }
+    }
+}
+
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s.  One warp per
+// (row, head); the sums run over the splits in ascending order.
+__global__ void __launch_bounds__(128)
+attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         const int* __restrict__ rows, int num_rows, int num_heads, int num_splits,
+                         int head_dim, bf16* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= num_rows * num_heads) return;
+    const int row = item / num_heads, h = item % num_heads;
+    const int t = rows ? rows[row] : row;
+    const size_t base = (size_t)item * num_splits;
+    float mmax = -INFINITY;
+    for (int s = lane; s < num_splits; s += 32) mmax = fmaxf(mmax, part_ml[(base + s) * 2]);
+    mmax = warp_max(mmax);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane*4 .. lane*4 + 3
+    float total = 0.0f;
+    const int d0 = lane * 4;
+    for (int s = 0; s < num_splits; ++s) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+        if (ml.x == -INFINITY) continue;
+        const float wgt = exp2f(ml.x - mmax);
+        total += ml.y * wgt;
+        if (d0 < head_dim) {
+            const float4 v = *reinterpret_cast<const float4*>(part_o + (base + s) * head_dim + d0);
+            acc[0] += v.x * wgt; acc[1] += v.y * wgt; acc[2] += v.z * wgt; acc[3] += v.w * wgt;
+        }
+    }
+    if (d0 < head_dim) {
+        const float inv = 1.0f / total;
+        bf16* o = out + ((size_t)t * num_heads + h) * head_dim + d0;
+        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+    }
+}
+
+template <int HD>
+int launch_decode(const bf16* q, const int* rows, int num_rows, const int* positions,
+                  const int* req_of_tok, const int* block_table, int bt_stride, const bf16* pages,
+                  int num_pages, int page_size, int num_heads, int num_kv_heads, int window,
+                  float scale, int num_splits, float* part_o, float* part_ml, bf16* out,
+                  int* status, cudaStream_t s) {
+    constexpr int SMEM = STAGES * 2 * TILE * (HD * 2 + 16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return ti_fail("attn_decode: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(num_splits, num_kv_heads, num_rows);
+    attn_decode_kernel<HD><<<grid, 32, SMEM, s>>>(q, rows, positions, req_of_tok, block_table,
+                                                  bt_stride, pages, num_pages, page_size, num_heads,
+                                                  num_kv_heads, window, scale * LOG2E, part_o,
+                                                  part_ml, status);
+    if (int rc = ti_check_launch("attn_decode")) return rc;
+    attn_decode_merge_kernel<<<(num_rows * num_heads + 3) / 4, 128, 0, s>>>(
+        part_o, part_ml, rows, num_rows, num_heads, num_splits, HD, out);
+    return ti_check_launch("attn_decode_merge");
+}
+
+}  // namespace
+
+// 1 if (head_dim, heads per kv head, page_size) can run on this kernel, else 0.
+extern "C" int ti_attn_decode_supported(int head_dim, int group, int page_size) {
+    return head_dim >= 16 && head_dim <= 128 && head_dim % 16 == 0 && group >= 1 && group <= 16 &&
+           page_size >= 16 && page_size % 16 == 0;
+}
+
+// Scratch the caller provides: part_o [num_rows, num_heads, num_splits, head_dim] float32 and
+// part_ml [num_rows, num_heads, num_splits, 2] float32.
+extern "C" int ti_attn_decode(const void* q, const int* rows, int num_rows, const int* positions,
+                              const int* req_of_tok, const int* block_table, int bt_stride,
+                              const void* pages, int num_pages, int page_size, int num_heads,
+                              int num_kv_heads, int head_dim, int window, float scale,
+                              int num_splits, float* part_o, float* part_ml, void* out,
+                              int* status, void* stream) {
+    if (num_rows == 0) return 0;
+    TI_REQUIRE(num_heads % num_kv_heads == 0, "attn_decode: %d heads over %d kv heads", num_heads,
+               num_kv_heads);
+    TI_REQUIRE(ti_attn_decode_supported(head_dim, num_heads / num_kv_heads, page_size),
+               "attn_decode: head_dim %d (multiple of 16 up to 128), %d heads per kv head (up to 16) "
+               "or page size %d (multiple of 16) is not supported",
+               head_dim, num_heads / num_kv_heads, page_size);
+    TI_REQUIRE(num_splits >= 1 && num_rows <= 65535 && num_kv_heads <= 65535,
+               "attn_decode: grid out of range");
+#define CASE(HD)                                                                                   \
+    case HD:                                                                                       \
+        return launch_decode<HD>((const bf16*)q, rows, num_rows, positions, req_of_tok,            \
+                                 block_table, bt_stride, (const bf16*)pages, num_pages, page_size, \
+                                 num_heads, num_kv_heads, window, scale, num_splits, part_o,       \
+                                 part_ml, (bf16*)out, status, (cudaStream_t)stream)
+    switch (head_dim) {
+        CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
+    }
+#undef CASE
+    return ti_fail("attn_decode: head_dim %d", head_dim);
+}

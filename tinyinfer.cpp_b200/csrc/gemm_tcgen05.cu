@@ -1,0 +1,291 @@
+// Matrix product on the 5th-generation tensor cores: C[M,N] (+)= A[M,K] * W[N,K]^T, bfloat16
+// operands, float32 accumulation in tensor memory.  This is the prefill product (M > 64).
+//
+// One block computes one 128 x 128 tile of C.  Warp 0 feeds a ring of shared-memory stages
+// with TMA tile loads (64 elements of K = one 128-byte swizzled row per matrix row); warp 1
+// issues tcgen05.mma (128 x 128 x 16, both operands K-major from shared memory, accumulator
+// in TMEM) and hands each stage back with tcgen05.commit; warps 2-5 wait for the last
+// commit, read the accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes = rows that
+// its position in the warpgroup allows) and run the epilogue: store, accumulate into C (the
+// residual stream), or SwiGLU over 8 gate + 8 up columns into bfloat16.  Rows and columns past
+// M, N and K are zero-filled by TMA on the way in and skipped on the way out.
+//
+// The k order of the accumulation is fixed (ascending blocks of 64, 16 at a time), so an
+// output element does not depend on M or on the tile around it.  Every wait on an mbarrier
+// is bounded: on a timeout the block records status 2, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16;
+constexpr int STAGES = 6;
+constexpr int STAGE_A = BM * BK * 2, STAGE_B = BN * BK * 2;
+constexpr int SMEM_BYTES = STAGES * (STAGE_A + STAGE_B) + 1024 /* alignment */ + 256 /* barriers */;
+constexpr int THREADS = 192;
+constexpr unsigned TMEM_COLS = 128;
+constexpr long long WAIT_LIMIT = 1LL << 31;          // cycles; about a second
+
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2 };
+enum { TI_ERR_TIMEOUT = 2 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
+                 "r"(bytes) : "memory");
+}
+// Waits until the barrier's phase with the given parity has completed; gives up after WAIT_LIMIT cycles.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    const long long start = clock64();
+    for (;;) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (clock64() - start > WAIT_LIMIT) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// K-major operand in 128-byte swizzled rows: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc(const void* p) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(p) & 0x3FFFF) >> 4);           // start address
+    d |= (unsigned long long)1 << 16;                                  // leading byte offset (unused)
+    d |= (unsigned long long)(1024 >> 4) << 32;                        // stride byte offset
+    d |= (unsigned long long)1 << 46;                                  // descriptor version
+    d |= (unsigned long long)2 << 61;                                  // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da,
+                                          unsigned long long db, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    float* __restrict__ c, bf16* __restrict__ out_act, int m, int n, int k, int ldc,
+                    int ld_act, int mode, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* stage_a = smem;
+    unsigned char* stage_b = smem + STAGES * STAGE_A;
+    unsigned long long* bars = (unsigned long long*)(smem + STAGES * (STAGE_A + STAGE_B));
+    unsigned long long* full = bars;                 // [STAGES] TMA -> MMA
+    unsigned long long* empty = bars + STAGES;       // [STAGES] MMA -> TMA
+    unsigned long long* acc_ready = bars + 2 * STAGES;
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int num_kb = (k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(&full[s], STAGE_A + STAGE_B);
+                tma_load_2d(stage_a + s * STAGE_A, &map_a, &full[s], kb * BK, m0);
+                tma_load_2d(stage_b + s * STAGE_B, &map_w, &full[s], kb * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // bf16 x bf16 -> f32, both K-major, N at bit 17 (/8), M at bit 24 (/16)
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                   ((unsigned)(BM >> 4) << 24);
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&full[s], (kb / STAGES) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned long long da = umma_desc(stage_a + s * STAGE_A);
+                const unsigned long long db = umma_desc(stage_b + s * STAGE_B);
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    // 16 elements of K = 32 bytes further inside the swizzled row
+                    umma_bf16(tmem_base, da + (unsigned long long)(kk * UMMA_K * 2 >> 4),
+                              db + (unsigned long long)(kk * UMMA_K * 2 >> 4), idesc,
+                              (kb | kk) != 0);
+                }
+                umma_commit(&empty[s]);               // the stage is free once these MMAs have read it
+            }
+            umma_commit(acc_ready);                   // all MMAs done: the accumulator is complete
+        }
+    } else {
+        const int quarter = warp & 3;                 // the TMEM lanes this warp may read
+        ok = mbar_wait(acc_ready, 0);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const int row = m0 + quarter * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float v[32];
+                tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
+                if (row >= m) continue;
+                const int col = n0 + c0;
+                if (mode == MODE_SWIGLU) {
+                    // columns: 8 gate, their 8 up, 8 gate, their 8 up
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        if (col + half * 16 >= n) break;
+                        unsigned packed[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float g0 = v[half * 16 + 2 * i], g1 = v[half * 16 + 2 * i + 1];
+                            const float u0 = v[half * 16 + 8 + 2 * i], u1 = v[half * 16 + 9 + 2 * i];
+                            __nv_bfloat162 y = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0,
+                                                                     g1 / (1.0f + expf(-g1)) * u1);
+                            packed[i] = *reinterpret_cast<unsigned*>(&y);
+                        }
+                        *reinterpret_cast<uint4*>(out_act + (size_t)row * ld_act + (col + half * 16) / 2) =
+                            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                } else {
+                    float* dst = c + (size_t)row * ldc + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (col + i >= n) break;
+                        float4 x = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        if (mode == MODE_ACCUMULATE) {
+                            const float4 old = *reinterpret_cast<const float4*>(dst + i);
+                            x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(dst + i) = x;
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) atomicCAS(status, 0, TI_ERR_TIMEOUT);
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
+                     ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// rows x cols bfloat16, row-major with `ld` elements between rows; tiles of 128 rows x 64 columns
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return ti_fail("gemm_tcgen05: the driver lacks cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {BK, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                    elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ti_fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int ti_gemm_tcgen05_supported(int m, int n, int k, int lda, int ldw, int ldc, int mode) {
+    if (m < 1 || n < 1 || k < 8 || k % 8 || lda % 8 || ldw % 8) return 0;
+    if (mode == MODE_SWIGLU) return n % 16 == 0;
+    return n % 4 == 0 && ldc % 4 == 0;
+}
+
+// mode 0: c = a w^T; 1: c += a w^T; 2: out_act[m, n/2] = SwiGLU over groups of 8 gate + 8 up columns.
+extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out_act, int m, int n,
+                               int k, int lda, int ldw, int ldc, int ld_act, int mode, int* status,
+                               void* stream) {
+    if (m == 0 || n == 0) return 0;
+    TI_REQUIRE(ti_gemm_tcgen05_supported(m, n, k, lda, ldw, ldc, mode),
+               "gemm_tcgen05: K=%d and the row strides %d, %d must be multiples of 8, N=%d a multiple "
+               "of 4 (16 with SwiGLU)", k, lda, ldw, n);
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+    TI_REQUIRE(mode == MODE_SWIGLU ? ((uintptr_t)out_act % 16 == 0 && ld_act % 8 == 0)
+                                   : (uintptr_t)c % 16 == 0,
+               "gemm_tcgen05: the output must be 16-byte aligned");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_BYTES);
+        if (e != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_a, map_w;
+    if (int rc = make_map(&map_a, a, m, k, lda)) return rc;
+    if (int rc = make_map(&map_w, w, n, k, ldw)) return rc;
+    dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+    TI_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d rows exceed the grid limit", m);
+    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
+        map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    return ti_check_launch("gemm_tcgen05");
+}

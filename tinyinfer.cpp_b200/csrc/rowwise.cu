@@ -33,15 +33,18 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * inv * w[i]);
 }
 
-// y[t, j] = silu(gu[t, j]) * gu[t, inter + j], silu(g) = g / (1 + exp(-g))
+// y[t, j] = silu(gate_j) * up_j, silu(g) = g / (1 + exp(-g)).  Stacked layout: gate_j = gu[t, j],
+// up_j = gu[t, inter + j].  Interleaved layout (groups of 8 gate columns followed by their 8 up
+// columns): gate_j = gu[t, 16 (j / 8) + j % 8], up_j eight columns further.
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, int inter, size_t total,
-                              TO* __restrict__ y) {
+                              int interleaved, TO* __restrict__ y) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / inter, j = i % inter;
-    const float g = gu[t * 2 * inter + j];
-    const float u = gu[t * 2 * inter + inter + j];
+    const size_t gcol = interleaved ? (j / 8) * 16 + j % 8 : j;
+    const float g = gu[t * 2 * inter + gcol];
+    const float u = gu[t * 2 * inter + gcol + (interleaved ? 8 : inter)];
     y[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
 }
 
@@ -109,16 +112,17 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
     return ti_check_launch("rmsnorm");
 }
 
-extern "C" int ti_swiglu(const float* gu, int num_tokens, int inter, void* out, int out_dtype,
-                         void* stream) {
+extern "C" int ti_swiglu(const float* gu, int num_tokens, int inter, int interleaved, void* out,
+                         int out_dtype, void* stream) {
+    TI_REQUIRE(!interleaved || inter % 8 == 0, "swiglu: interleaved layout needs inter %% 8 == 0");
     const size_t total = (size_t)num_tokens * inter;
     if (total == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dtype == TI_BF16)
-        swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, inter, total, (bf16*)out);
+        swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, inter, total, interleaved, (bf16*)out);
     else if (out_dtype == TI_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, inter, total, (float*)out);
+        swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, inter, total, interleaved, (float*)out);
     else
         return ti_fail("swiglu: output dtype code %d is not float32 or bfloat16", out_dtype);
     return ti_check_launch("swiglu");

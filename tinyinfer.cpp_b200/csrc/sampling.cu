@@ -85,15 +85,16 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     const float p = top_p[row];
     if (p < 1.0f) {
         const float want = p * total;
-        unsigned thr_p = thr;                     // never below the top-k threshold
+        unsigned thr_p = 0u;                      // built bit by bit; the top-k cut stays in force
         for (int b = 31; b >= 0; --b) {
-            if (thr_p & (1u << b)) continue;
             const unsigned trial = thr_p | (1u << b);
+            const unsigned cut = trial > thr ? trial : thr;
             float ms = 0.0f;
             for (int i = tid; i < vocab; i += THREADS)
-                if (order_key(x[i]) >= trial) ms += expf((x[i] - mx) * inv_t);
+                if (order_key(x[i]) >= cut) ms += expf((x[i] - mx) * inv_t);
             if (block_sum_all(ms, fs) >= want) thr_p = trial;
         }
+        if (thr_p < thr) thr_p = thr;
         if (thr_p != thr) {
             thr = thr_p;
             s = 0.0f;

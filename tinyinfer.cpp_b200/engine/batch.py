@@ -16,6 +16,9 @@ import numpy as np
 import torch
 
 
+PREFILL_TILE_ROWS = 64     # query rows per block of the prompt-portion attention kernel
+
+
 @dataclass(frozen=True)
 class StepEntry:
     """The next ``tokens`` of request ``req_id``; ``want`` lists the places among these
@@ -46,13 +49,18 @@ class StepBatch:
     ctx_len_dev: torch.Tensor        # [R] length of each request after this step
     logit_rows: torch.Tensor         # [K] flat token indices whose logits are wanted
     state_slots: torch.Tensor        # [R] state slot of each request
+    decode_rows: torch.Tensor        # flat indices of tokens that are their request's only token
+    chunk_rows: torch.Tensor         # flat indices of the tokens of requests that bring several
+    chunk_tiles: torch.Tensor        # [n, 3] {request row, first flat token, rows} in tiles of 64
+    max_position: int = 0            # the model's longest context (bounds that do not vary by step)
     block_tables: list[torch.Tensor] = field(default_factory=list)   # per group [R, blocks]
     scratch: dict = field(default_factory=dict)   # per-step values kernels may cache
 
 
 def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
                      tables: Sequence[Sequence[Sequence[int]]], slots: Sequence[int],
-                     act_dtype: torch.dtype, device, min_blocks: int = 1) -> StepBatch:
+                     act_dtype: torch.dtype, device, min_blocks: int = 1,
+                     max_position: int = 0) -> StepBatch:
     """Pack one step.  ``starts[r]`` is the position of entry r's first token,
     ``tables[g][r]`` its block table in group g (already covering the new tokens)."""
     q_lens = [len(e.tokens) for e in entries]
@@ -69,8 +77,17 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
                     f"request {e.req_id!r}: wanted place {w} is outside its {q_lens[i]} tokens")
             rows.append(int(cu[i]) + int(w))
     k = len(rows)
+    dec = [int(cu[i]) for i in range(r) if q_lens[i] == 1]
+    chk = [int(cu[i]) + j for i in range(r) if q_lens[i] > 1 for j in range(q_lens[i])]
+    tiles = []
+    for i in range(r):
+        if q_lens[i] > 1:
+            for lo in range(0, q_lens[i], PREFILL_TILE_ROWS):
+                tiles.append((starts[i] + lo, i, int(cu[i]) + lo, min(PREFILL_TILE_ROWS, q_lens[i] - lo)))
+    tiles.sort(key=lambda x: -x[0])                   # longest contexts first
+    tiles = [x[1:] for x in tiles]
     widths = [max(min_blocks, max((len(tb) for tb in grp), default=0)) for grp in tables]
-    total = 3 * t + (r + 1) + 3 * r + k + sum(r * w for w in widths)
+    total = 4 * t + (r + 1) + 3 * r + k + 3 * len(tiles) + sum(r * w for w in widths)
     host = torch.empty(max(total, 1), dtype=torch.int32,
                        pin_memory=(torch.device(device).type == "cuda"))
     buf = host.numpy()
@@ -90,6 +107,9 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         "tok": put(tok, t), "pos": put(pos, t), "roft": put(roft, t), "cu": put(cu, r + 1),
         "qs": put(np.asarray(starts, dtype=np.int64), r), "ctx": put(np.asarray(ctx), r),
         "slots": put(np.asarray(slots, dtype=np.int64), r), "rows": put(np.asarray(rows), k),
+        "dec": put(np.asarray(dec, dtype=np.int64), len(dec)),
+        "chk": put(np.asarray(chk, dtype=np.int64), len(chk)),
+        "tiles": put(np.asarray(tiles, dtype=np.int64).reshape(-1), 3 * len(tiles)),
     }
     bt_spans = []
     for grp, w in zip(tables, widths):
@@ -109,5 +129,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         max_q_len=max(q_lens, default=0), max_ctx_len=max(ctx, default=0),
         token_ids=view("tok"), positions=view("pos"), req_of_tok=view("roft"), cu_q=view("cu"),
         q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
-        state_slots=view("slots"),
+        state_slots=view("slots"), decode_rows=view("dec"), chunk_rows=view("chk"),
+        chunk_tiles=view("tiles").view(-1, 3),
+        max_position=max_position,
         block_tables=[dev[a:b].view(r, w) for (a, b), w in bt_spans])

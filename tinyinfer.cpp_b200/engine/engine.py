@@ -118,7 +118,8 @@ class Engine:
         tables = [[self.cache.block_table(g, e.req_id) for e in entries]
                   for g in range(len(self.cache.groups))]
         slots = [self.cache.state_slot(e.req_id) for e in entries]
-        batch = build_step_batch(entries, starts, tables, slots, self.dtype, self.device)
+        batch = build_step_batch(entries, starts, tables, slots, self.dtype, self.device,
+                                 max_position=self.plan.max_position)
         logits = self.forward(batch)
         for e in entries:
             self.cache.release_passed(e.req_id)

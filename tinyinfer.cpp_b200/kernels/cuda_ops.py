@@ -68,6 +68,8 @@ class CudaOps:
         self.core = load_library("core")
         self.core.ti_last_error.restype = ctypes.c_char_p
         self._declare()
+        self._bf16 = None
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
         # the entry points that were captured into that graph
@@ -78,15 +80,37 @@ class CudaOps:
         c = self.core
         c.ti_embed.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp]
         c.ti_rmsnorm.argtypes = [_vp, _vp, _vp, _i, _i, _f, _vp, _i, _vp]
-        c.ti_swiglu.argtypes = [_vp, _i, _i, _vp, _i, _vp]
+        c.ti_swiglu.argtypes = [_vp, _i, _i, _i, _vp, _i, _vp]
         c.ti_argmax.argtypes = [_vp, _i, _i, _vp, _vp]
         c.ti_gemm_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]
         c.ti_qk_norm_rope_store.argtypes = [
             _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
             _vp, _i, _vp, _vp]
         c.ti_paged_attention_simple.argtypes = [
-            _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]
+            _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]
         c.ti_sample.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]
+
+    @property
+    def bf16(self):
+        """The tensor-core kernels of the bfloat16 path, built and loaded when first needed."""
+        if self._bf16 is None:
+            b = load_library("bf16")
+            b.ti_last_error.restype = ctypes.c_char_p
+            b.ti_gemm_skinny.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]
+            b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_attn_decode_supported.argtypes = [_i, _i, _i]
+            b.ti_attn_decode.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                         _f, _i, _vp, _vp, _vp, _vp, _vp]
+            b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
+            b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
+            b.ti_attn_prefill_supported.argtypes = [_i, _i]
+            b.ti_attn_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f,
+                                          _vp, _vp, _vp]
+            from ..engine.batch import PREFILL_TILE_ROWS
+            if b.ti_attn_prefill_tile_rows() != PREFILL_TILE_ROWS:
+                raise KernelError("the attention kernel's tile height and the batch builder's differ")
+            self._bf16 = b
+        return self._bf16
 
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
@@ -109,7 +133,18 @@ class CudaOps:
         return w.contiguous()
 
     def pack_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-        return torch.cat([gate, up], dim=0).contiguous()
+        """Gate and up rows as one weight.  When the size allows, in strips of 16 rows: 8 gate
+        rows followed by their 8 up rows, so that a product's epilogue holds both values of
+        an output column and applies SwiGLU without a round trip through memory."""
+        inter, k = gate.shape
+        if gate.dtype == torch.bfloat16 and inter % 8 == 0:
+            packed = torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1)
+            packed = packed.reshape(2 * inter, k).contiguous()
+            packed._ti_interleaved = True
+            return packed
+        packed = torch.cat([gate, up], dim=0).contiguous()
+        packed._ti_interleaved = False
+        return packed
 
     # ---- rowwise -------------------------------------------------------------------------
     def embed(self, table, token_ids, out):
@@ -139,6 +174,22 @@ class CudaOps:
         _need(out.dtype == torch.float32, "linear: out must be float32")
         _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
               "linear: rows must be contiguous")
+        if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if self.bf16.ti_gemm_skinny_supported(m, n, k, a.stride(0), w.stride(0)):
+                self._ok(self.bf16.ti_gemm_skinny(
+                    a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
+                    w.stride(0), out.stride(0), 0, 1 if accumulate else 0, self._stream()),
+                    self.bf16)
+                return
+            mode = 1 if accumulate else 0
+            if (m > 64 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and
+                    out.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
+                        m, n, k, a.stride(0), w.stride(0), out.stride(0), mode)):
+                self._ok(self.bf16.ti_gemm_tcgen05(
+                    a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
+                    w.stride(0), out.stride(0), 0, mode, self.status.data_ptr(), self._stream()),
+                    self.bf16)
+                return
         self._ok(self.core.ti_gemm_simple(
             a.data_ptr(), _code(a, "linear"), w.data_ptr(), _code(w, "linear"), out.data_ptr(),
             m, n, k, a.stride(0), w.stride(0), out.stride(0), int(bool(accumulate)),
@@ -147,9 +198,26 @@ class CudaOps:
     def gate_up_swiglu(self, h, w_gate_up, out):
         inter = out.shape[1]
         _need(w_gate_up.shape[0] == 2 * inter, "gate_up_swiglu: weight must hold gate and up rows")
-        gu = torch.empty((h.shape[0], 2 * inter), dtype=torch.float32, device=h.device)
+        interleaved = bool(getattr(w_gate_up, "_ti_interleaved", False))
+        m, k = h.shape
+        if (interleaved and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                and self.bf16.ti_gemm_skinny_supported(m, 2 * inter, k, h.stride(0),
+                                                       w_gate_up.stride(0))):
+            self._ok(self.bf16.ti_gemm_skinny(
+                h.data_ptr(), w_gate_up.data_ptr(), None, out.data_ptr(), m, 2 * inter, k,
+                h.stride(0), w_gate_up.stride(0), 0, out.stride(0), 2, self._stream()), self.bf16)
+            return
+        if (interleaved and m > 64 and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                and inter % 8 == 0 and out.stride(0) % 8 == 0 and self.bf16.ti_gemm_tcgen05_supported(
+                    m, 2 * inter, k, h.stride(0), w_gate_up.stride(0), 0, 2)):
+            self._ok(self.bf16.ti_gemm_tcgen05(
+                h.data_ptr(), w_gate_up.data_ptr(), None, out.data_ptr(), m, 2 * inter, k,
+                h.stride(0), w_gate_up.stride(0), 0, out.stride(0), 2, self.status.data_ptr(),
+                self._stream()), self.bf16)
+            return
+        gu = torch.empty((m, 2 * inter), dtype=torch.float32, device=h.device)
         self.linear(h, w_gate_up, gu)
-        self._ok(self.core.ti_swiglu(gu.data_ptr(), h.shape[0], inter, out.data_ptr(),
+        self._ok(self.core.ti_swiglu(gu.data_ptr(), m, inter, int(interleaved), out.data_ptr(),
                                      _code(out, "swiglu"), self._stream()))
 
     # ---- attention -----------------------------------------------------------------------
@@ -172,6 +240,17 @@ class CudaOps:
             cache.page_size, int(bool(cache.writes)), t, num_heads, num_kv_heads, head_dim,
             q_out.data_ptr(), _code(q_out, "q"), self.status.data_ptr(), self._stream()))
 
+    def decode_splits(self, rows: int, num_kv_heads: int, max_position: int) -> int:
+        """In how many blocks the keys of a decoding row are cut, per kv head.  It depends on
+        the padded batch size and on the model's longest context only, so that a step cuts
+        the same way whether it runs eagerly or from a graph."""
+        bucket = 1
+        while bucket < rows:
+            bucket *= 2
+        # one-warp blocks, four resident per SM: fill the GPU once, never one block more
+        want = (4 * self.num_sms) // (bucket * num_kv_heads)
+        return max(1, min(want, -(-max_position // 64)))
+
     def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,
                         scale):
         pages, bt = cache.pages, cache.block_table
@@ -179,11 +258,45 @@ class CudaOps:
               "paged_attention: q and out must be contiguous and of one dtype")
         _need(pages.is_contiguous() and tuple(pages.shape[1:]) ==
               (2, num_kv_heads, cache.page_size, head_dim), "paged_attention: page layout")
+        win = int(window or 0)
+        rows, n_rows = None, q.shape[0]
+        n_dec = step.decode_rows.shape[0]
+        if (n_dec and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and
+                self.bf16.ti_attn_decode_supported(head_dim, num_heads // num_kv_heads,
+                                                   cache.page_size)):
+            splits = self.decode_splits(n_dec, num_kv_heads, step.max_position or step.max_ctx_len)
+            part_o = torch.empty((n_dec, num_heads, splits, head_dim), dtype=torch.float32,
+                                 device=q.device)
+            part_ml = torch.empty((n_dec, num_heads, splits, 2), dtype=torch.float32,
+                                  device=q.device)
+            self._ok(self.bf16.ti_attn_decode(
+                q.data_ptr(), step.decode_rows.data_ptr(), n_dec, step.positions.data_ptr(),
+                step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
+                pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
+                float(scale), splits, part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(),
+                self.status.data_ptr(), self._stream()), self.bf16)
+            self.launches += 1
+            rows, n_rows = step.chunk_rows, step.chunk_rows.shape[0]
+            if n_rows == 0:
+                return
+        n_tiles = step.chunk_tiles.shape[0]
+        if (n_tiles and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and
+                self.bf16.ti_attn_prefill_supported(head_dim, cache.page_size)):
+            self._ok(self.bf16.ti_attn_prefill(
+                q.data_ptr(), step.chunk_tiles.data_ptr(), n_tiles, step.positions.data_ptr(),
+                bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size,
+                num_heads, num_kv_heads, head_dim, win, float(scale), out.data_ptr(),
+                self.status.data_ptr(), self._stream()), self.bf16)
+            if rows is not None:          # the single-token rows went through the decode kernel
+                return
+            rows, n_rows = step.decode_rows, n_dec
+            if n_rows == 0:
+                return
         self._ok(self.core.ti_paged_attention_simple(
-            q.data_ptr(), _code(q, "q"), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
-            bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
-            cache.page_size, q.shape[0], num_heads, num_kv_heads, head_dim,
-            int(window or 0), float(scale), out.data_ptr(), self.status.data_ptr(),
+            q.data_ptr(), _code(q, "q"), _ptr(rows), step.positions.data_ptr(),
+            step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
+            _code(pages, "cache"), pages.shape[0], cache.page_size, n_rows, num_heads,
+            num_kv_heads, head_dim, win, float(scale), out.data_ptr(), self.status.data_ptr(),
             self._stream()))
 
     # ---- sampling ------------------------------------------------------------------------
