@@ -357,3 +357,62 @@ extern "C" int ti_attn_decode(const void* q, const int* rows, int num_rows, cons
 #undef CASE
     return ti_fail("attn_decode: head_dim %d", head_dim);
 }
+
+// ---- the variant that allocates nothing (declared and described in attn_decode_noalloc.h) ----
+#include "attn_decode_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+// The partial results of the key splits live here instead of in caller-provided buffers.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TI_DECODE_NOALLOC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+void* g_noalloc_ptr[MAX_DEVICES] = {};        // device address of the array, per device
+std::mutex g_noalloc_mutex;
+
+// In host code the array's name is only a handle: the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+int noalloc_scratch(void** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return ti_fail("attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return ti_fail("attn_decode_noalloc: device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return ti_fail("attn_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = p;
+    }
+    *ptr = g_noalloc_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int ti_attn_decode_noalloc(const void* q, const int* rows, int num_rows,
+                                      const int* positions, const int* req_of_tok,
+                                      const int* block_table, int bt_stride, const void* pages,
+                                      int num_pages, int page_size, int num_heads, int num_kv_heads,
+                                      int head_dim, int window, float scale, int num_splits,
+                                      void* out, int* status, void* stream) {
+    if (num_rows == 0) return 0;
+    TI_REQUIRE(num_rows > 0 && num_heads > 0 && num_splits > 0 && head_dim > 0,
+               "attn_decode_noalloc: sizes must be positive");
+    const unsigned long long slots = (unsigned long long)num_rows * num_heads * num_splits;
+    const unsigned long long need = slots * (unsigned long long)(head_dim + 2) * sizeof(float);
+    TI_REQUIRE(need <= TI_DECODE_NOALLOC_SCRATCH_BYTES,
+               "attn_decode_noalloc: %d rows x %d heads x %d splits x head_dim %d need %llu bytes of "
+               "scratch; the built-in array holds %u",
+               num_rows, num_heads, num_splits, head_dim, need, TI_DECODE_NOALLOC_SCRATCH_BYTES);
+    void* base = nullptr;
+    if (int rc = noalloc_scratch(&base)) return rc;
+    float* part_o = (float*)base;                                   // [slots, head_dim]
+    float* part_ml = part_o + slots * (unsigned long long)head_dim; // [slots, 2]
+    return ti_attn_decode(q, rows, num_rows, positions, req_of_tok, block_table, bt_stride, pages,
+                          num_pages, page_size, num_heads, num_kv_heads, head_dim, window, scale,
+                          num_splits, part_o, part_ml, out, status, stream);
+}
