@@ -1,0 +1,95 @@
+"""The engine's host logic (step function, block tables, windows, generation loop) run through
+the plain PyTorch statement of the kernels, so that it is tested without a GPU.  The product
+itself has no CPU path; the kernel set used here lives under tests/."""
+import pytest
+import torch
+
+import traces
+from plain_qwen3 import load_folder, plain_forward, plain_greedy
+from ref_ops import RefOps
+from tinyinfer_b200 import Engine, LLM, SamplingParams, StepEntry
+from tinyinfer_b200.cache import OutOfPages
+from tinyinfer_b200.kernels import KernelError
+from util import TINY, assert_close_logits, make_model, random_tokens
+
+
+def _requests(name, lengths):
+    return {f"r{i}": random_tokens(TINY[name]["vocab_size"], n, seed=50 + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("name,lengths", [("A", [40, 9, 70, 33, 2]), ("C", [90, 30, 120, 45])])
+@pytest.mark.parametrize("family", ["tail", "portions", "mixed"])
+def test_cuttings_on_the_host_path(tmp_path, name, lengths, family):
+    d = make_model(tmp_path, name)
+    cfg, w = load_folder(d)
+    reqs = _requests(name, lengths)
+    steps = {"tail": traces.tail_decoded, "portions": traces.portions, "mixed": traces.mixed}[family](reqs)
+    eng = Engine(d, dtype="float32", device="cpu", ops=RefOps(), page_size=16,
+                 num_pages=traces.max_live_tokens(steps) // 16, max_requests=4)
+    outputs = {}
+    for s in steps:
+        outputs[s["step"]] = eng.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]])
+        for r in s["end"]:
+            eng.finish(r)
+        eng.cache.check()
+    for r, items in traces.collect(steps, outputs).items():
+        ref = plain_forward(cfg, w, reqs[r])
+        got = torch.stack([row for _, row in items])
+        assert_close_logits(got, ref[[p for p, _ in items]], 2e-5, f"{name} {family} {r}")
+    assert eng.cache.live_requests() == [] and eng.cache.free_pages() == [eng.cache.num_pages] * len(eng.cache.groups)
+
+
+def test_step_refuses_what_it_cannot_run(tmp_path):
+    d = make_model(tmp_path, "A")
+    eng = Engine(d, dtype="float32", device="cpu", ops=RefOps(), page_size=16, num_pages=2, max_requests=2)
+    with pytest.raises(ValueError, match="token id 256"):
+        eng.step([StepEntry("a", [1, 256], [0])])
+    with pytest.raises(IndexError, match="wanted place 3"):
+        eng.step([StepEntry("a", [1, 2, 3], [3])])
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", list(range(40)), [])])
+    assert eng.cache.live_requests() == []            # nothing was kept of the refused step
+    with pytest.raises(ValueError, match="allows 128"):
+        Engine(d, dtype="float32", device="cpu", ops=RefOps(), num_pages=20).step(
+            [StepEntry("b", [1] * 129, [])])
+    assert eng.step([]).shape == (0, 256)
+    with pytest.raises(ValueError, match="dtype"):
+        Engine(d, dtype="float16", device="cpu", ops=RefOps())
+
+
+def test_engine_needs_cuda_kernels_without_injected_ops(tmp_path):
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(KernelError, match="CUDA device only"):
+        Engine(make_model(tmp_path, "A"), dtype="float32")
+
+
+def test_generation_loop_with_preemption_matches_plain_greedy(tmp_path):
+    d = make_model(tmp_path, "B")
+    cfg, w = load_folder(d)
+    prompts = [random_tokens(512, n, seed=n) for n in (1, 9, 33, 64)]
+    # so few pages that running requests are preempted and recomputed
+    llm = LLM(d, dtype="float32", device="cpu", ops=RefOps(), max_seq=128, max_num_seqs=4,
+              max_batched_tokens=48, chunk=16, kv_tokens=128)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=12), log_steps=True)
+    for p, o in zip(prompts, outs):
+        assert o.tokens == plain_greedy(cfg, w, p, 12) and o.finish_reason == "length"
+    assert llm.stats.preemptions >= 1 and sum(o.preemptions for o in outs) == llm.stats.preemptions
+    assert any(len(step) > 1 and any(c > 1 for _, _, c in step) and any(c == 1 for _, _, c in step)
+               for step in llm.stats.step_log), "no step mixed a prompt portion with decoding"
+    llm.engine.cache.check()
+    assert llm.engine.cache.live_requests() == []
+
+
+def test_sampling_does_not_depend_on_the_batch(tmp_path):
+    d = make_model(tmp_path, "B")
+    prompts = [random_tokens(512, n, seed=n) for n in (5, 9, 17)]
+    sp = SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=7, max_tokens=6)
+    together = LLM(d, dtype="float32", device="cpu", ops=RefOps(), max_seq=64, max_num_seqs=4,
+                   max_batched_tokens=64).generate(prompts, sp)
+    chunked = LLM(d, dtype="float32", device="cpu", ops=RefOps(), max_seq=64, max_num_seqs=2,
+                  max_batched_tokens=8, chunk=4).generate(prompts, sp)
+    assert [o.tokens for o in together] == [o.tokens for o in chunked]
+    other_seed = LLM(d, dtype="float32", device="cpu", ops=RefOps(), max_seq=64).generate(
+        prompts, SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=8, max_tokens=6))
+    assert [o.tokens for o in other_seed] != [o.tokens for o in together]

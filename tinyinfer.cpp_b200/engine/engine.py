@@ -114,6 +114,10 @@ class Engine:
             for tok in e.tokens:
                 if not 0 <= int(tok) < vocab:
                     raise ValueError(f"request {e.req_id!r}: token id {tok} is outside [0, {vocab})")
+            for place in e.want:
+                if not 0 <= int(place) < len(e.tokens):
+                    raise IndexError(f"request {e.req_id!r}: wanted place {place} is outside its "
+                                     f"{len(e.tokens)} tokens")
         starts = self.reserve(entries)
         tables = [[self.cache.block_table(g, e.req_id) for e in entries]
                   for g in range(len(self.cache.groups))]
