@@ -37,7 +37,11 @@ class _Bucket:
         b = size
         # layout of the packed integers: tok, pos, ctx, slots, then one table per group
         self.total = 4 * b + groups * b * self.width
-        self.host = torch.empty(self.total, dtype=torch.int32, pin_memory=True)
+        # a ring of pinned staging buffers: one is rewritten only after the copy that read it
+        # has run on the device (the host runs ahead of the device by several steps)
+        self.hosts = [torch.empty(self.total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self.copied = [None] * len(self.hosts)
+        self.turn = 0
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
         d = self.dev
         ar = torch.arange(b, dtype=torch.int32, device=dev)
@@ -61,7 +65,12 @@ class _Bucket:
         cache = engine.cache
         b, w = self.size, self.width
         n = len(entries)
-        buf = self.host.numpy()
+        turn = self.turn
+        self.turn = (turn + 1) % len(self.hosts)
+        if self.copied[turn] is not None:
+            self.copied[turn].synchronize()
+        host = self.hosts[turn]
+        buf = host.numpy()
         buf[:4 * b] = 0
         buf[2 * b:3 * b] = 1                                      # padding rows: one token
         buf[3 * b:4 * b] = cache.max_requests                     # padding rows: spare state slot
@@ -75,7 +84,10 @@ class _Bucket:
             for i, e in enumerate(entries):
                 tb = cache.block_table(g, e.req_id)
                 buf[base + i * w: base + i * w + len(tb)] = tb
-        self.dev.copy_(self.host, non_blocking=True)
+        self.dev.copy_(host, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self.copied[turn] = done
 
 
 class DecodeGraphs:
