@@ -37,12 +37,14 @@ class RefOps:
         inv = torch.rsqrt((src * src).mean(dim=-1, keepdim=True) + eps)
         out.copy_((src * inv * weight.to(F32)).to(out.dtype))
 
-    def linear(self, a, w, out, accumulate=False):
+    def linear(self, a, w, out, accumulate=False, then_norm=None):
         prod = a.to(F32) @ w.to(F32).T
         if accumulate:
             out.add_(prod)
         else:
             out.copy_(prod)
+        if then_norm is not None:                      # (weight, eps, normed output)
+            self.rmsnorm(out, then_norm[0], then_norm[1], then_norm[2])
 
     def gate_up_swiglu(self, h, w_gate_up, out):
         inter = out.shape[1]

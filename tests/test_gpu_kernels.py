@@ -266,3 +266,24 @@ def test_sample_follows_the_distribution(ops):
     freq = torch.bincount(out.long(), minlength=vocab).float() / n
     prob = torch.softmax(base[0], dim=-1)
     assert (freq - prob).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 64])
+@pytest.mark.parametrize("nk", [(1024, 3072), (128, 64), (100, 96)])
+def test_linear_with_fused_norm(ops, m, nk):
+    """The residual update followed, in the same launch, by the RMSNorm of the finished rows."""
+    n, k = nk
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1, scale=0.05)
+    base = _rand((m, n), seed=2)
+    norm_w = 1 + _rand((n,), seed=3, scale=0.1)
+    for fused in (True, True, False):                    # twice fused: the counter must come back to zero
+        ops.fuse_norm_tail = fused
+        out, normed = base.clone(), torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+        ops.linear(a, w, out, accumulate=True, then_norm=(norm_w, 1e-5, normed))
+        ops.fuse_norm_tail = False
+        plain_out = base.clone()
+        ops.linear(a, w, plain_out, accumulate=True)
+        assert torch.equal(out, plain_out)
+        want = torch.empty_like(normed)
+        RefOps().rmsnorm(plain_out, norm_w, 1e-5, want)
+        _close(normed, want, 8e-3, f"fused norm m={m} {nk}")

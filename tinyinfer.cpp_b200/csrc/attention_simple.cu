@@ -29,6 +29,8 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
                           int num_heads, int num_kv_heads, int head_dim,
                           TQ* __restrict__ q_out, int* __restrict__ status) {
     __shared__ float vec[WARPS][MAX_HEAD_DIM];
+    pdl_launch();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int item = blockIdx.y * WARPS + warp;
@@ -196,7 +198,7 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
     dim3 grid(num_tokens, (items + WARPS - 1) / WARPS);
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TQ, TC)                                                                          \
-    qk_norm_rope_store_kernel<TQ, TC><<<grid, WARPS * 32, 0, s>>>(                             \
+    ti_launch_pdl(qk_norm_rope_store_kernel<TQ, TC>, grid, WARPS * 32, 0, s,                   \
         qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
         bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,         \
         head_dim, (TQ*)q_out, status)

@@ -53,6 +53,33 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// out[:] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s, by one warp, over the splits
+// in ascending order.  Loads go to L2: other blocks of the same launch wrote the partial results.
+__device__ __forceinline__ void merge_head(const float* part_o, const float* part_ml, size_t base,
+                                           int num_splits, int head_dim, bf16* out, int lane) {
+    float mmax = -INFINITY;
+    for (int s = lane; s < num_splits; s += 32) mmax = fmaxf(mmax, __ldcg(part_ml + (base + s) * 2));
+    mmax = warp_max(mmax);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane*4 .. lane*4 + 3
+    float total = 0.0f;
+    const int d0 = lane * 4;
+    for (int s = 0; s < num_splits; ++s) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2));
+        if (ml.x == -INFINITY) continue;
+        const float wgt = exp2f(ml.x - mmax);
+        total += ml.y * wgt;
+        if (d0 < head_dim) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * head_dim + d0));
+            acc[0] += v.x * wgt; acc[1] += v.y * wgt; acc[2] += v.z * wgt; acc[3] += v.w * wgt;
+        }
+    }
+    if (d0 < head_dim) {
+        const float inv = 1.0f / total;
+        *reinterpret_cast<__nv_bfloat162*>(out + d0) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(out + d0 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(32)
 attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
@@ -61,6 +88,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
                    const bf16* __restrict__ pages, int num_pages, int page_size,
                    int num_heads, int num_kv_heads, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml,
+                   unsigned* __restrict__ counters, bf16* __restrict__ out,
                    int* __restrict__ status) {
     constexpr int ROW_BYTES = HD * 2 + 16;          // padded: ldmatrix rows fall in distinct banks
     constexpr int CHUNKS = HD / 8;                  // 16-byte chunks per key
@@ -92,19 +120,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
 #pragma unroll
     for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
+    pdl_launch();
     if (my_lo < my_hi) {
-        // queries of the group as the A operand: row r of the tile is head kvh*group + r
-        unsigned qa[KSTEPS][4];
-        const bf16* qbase = q + ((size_t)t * num_heads + (size_t)kvh * group) * HD;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            const int k0 = ks * 16 + tq * 2;
-            qa[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0) : 0u;
-            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0) : 0u;
-            qa[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0 + 8) : 0u;
-            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0 + 8) : 0u;
-        }
-
         auto issue = [&](int tile, int stage) {
             unsigned char* kdst = smem + (size_t)stage * 2 * TILE * ROW_BYTES;
             unsigned char* vdst = kdst + TILE * ROW_BYTES;
@@ -137,8 +154,35 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
             }
         };
 
+        // Keys of earlier steps do not depend on the kernel before this one; the new token's own
+        // key and value (in the tile that holds `pos`) and the queries do.  So the first tiles
+        // are requested before waiting for that kernel.
+        const int new_tile = pos / TILE;
+        int early = 0;
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
+            if (early == s && my_lo + s < my_hi && my_lo + s < new_tile) {
+                issue(my_lo + s, s);
+                cp_async_commit();
+                ++early;
+            }
+        }
+        pdl_wait();
+        // queries of the group as the A operand: row r of the tile is head kvh*group + r
+        unsigned qa[KSTEPS][4];
+        const bf16* qbase = q + ((size_t)t * num_heads + (size_t)kvh * group) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int k0 = ks * 16 + tq * 2;
+            qa[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0) : 0u;
+            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0) : 0u;
+            qa[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0 + 8) : 0u;
+            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0 + 8) : 0u;
+        }
+
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < early) continue;
             if (my_lo + s < my_hi) issue(my_lo + s, s);
             cp_async_commit();
         }
@@ -235,6 +279,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
             __syncwarp();                         // the stage may be refilled
         }
         cp_async_wait<0>();
+    } else {
+        pdl_wait();
     }
     // the sums of a row live in the four lanes of a quad
 #pragma unroll
@@ -257,10 +303,25 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
             part_ml[idx * 2 + 1] = l_run[r];
         }
     }
+    if (counters == nullptr) return;                 // a separate launch merges
+    // The block that finishes last for this (row, kv head) merges the splits of the group's heads.
+    // The counter returns to zero, so the next launch finds it ready.
+    __threadfence();
+    unsigned ticket = 0;
+    unsigned* counter = counters + (size_t)row * num_kv_heads + kvh;
+    if (lane == 0) ticket = atomicAdd(counter, 1u);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket != (unsigned)num_splits - 1) return;
+    __threadfence();
+    if (lane == 0) *counter = 0u;
+    for (int r = 0; r < group; ++r) {
+        const int h = kvh * group + r;
+        merge_head(part_o, part_ml, ((size_t)row * num_heads + h) * num_splits, num_splits, HD,
+                   out + ((size_t)t * num_heads + h) * HD, lane);
+    }
 }
 
-// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s.  One warp per
-// (row, head); the sums run over the splits in ascending order.
+// The merge as a launch of its own (used when no counters are given): one warp per (row, head).
 __global__ void __launch_bounds__(128)
 attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          const int* __restrict__ rows, int num_rows, int num_heads, int num_splits,
@@ -270,37 +331,16 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
     if (item >= num_rows * num_heads) return;
     const int row = item / num_heads, h = item % num_heads;
     const int t = rows ? rows[row] : row;
-    const size_t base = (size_t)item * num_splits;
-    float mmax = -INFINITY;
-    for (int s = lane; s < num_splits; s += 32) mmax = fmaxf(mmax, part_ml[(base + s) * 2]);
-    mmax = warp_max(mmax);
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane*4 .. lane*4 + 3
-    float total = 0.0f;
-    const int d0 = lane * 4;
-    for (int s = 0; s < num_splits; ++s) {
-        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
-        if (ml.x == -INFINITY) continue;
-        const float wgt = exp2f(ml.x - mmax);
-        total += ml.y * wgt;
-        if (d0 < head_dim) {
-            const float4 v = *reinterpret_cast<const float4*>(part_o + (base + s) * head_dim + d0);
-            acc[0] += v.x * wgt; acc[1] += v.y * wgt; acc[2] += v.z * wgt; acc[3] += v.w * wgt;
-        }
-    }
-    if (d0 < head_dim) {
-        const float inv = 1.0f / total;
-        bf16* o = out + ((size_t)t * num_heads + h) * head_dim + d0;
-        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-        *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
-    }
+    merge_head(part_o, part_ml, (size_t)item * num_splits, num_splits, head_dim,
+               out + ((size_t)t * num_heads + h) * head_dim, lane);
 }
 
 template <int HD>
 int launch_decode(const bf16* q, const int* rows, int num_rows, const int* positions,
                   const int* req_of_tok, const int* block_table, int bt_stride, const bf16* pages,
                   int num_pages, int page_size, int num_heads, int num_kv_heads, int window,
-                  float scale, int num_splits, float* part_o, float* part_ml, bf16* out,
-                  int* status, cudaStream_t s) {
+                  float scale, int num_splits, float* part_o, float* part_ml, unsigned* counters,
+                  bf16* out, int* status, cudaStream_t s) {
     constexpr int SMEM = STAGES * 2 * TILE * (HD * 2 + 16);
     static bool configured = false;
     if (!configured) {
@@ -310,11 +350,11 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
         configured = true;
     }
     dim3 grid(num_splits, num_kv_heads, num_rows);
-    attn_decode_kernel<HD><<<grid, 32, SMEM, s>>>(q, rows, positions, req_of_tok, block_table,
-                                                  bt_stride, pages, num_pages, page_size, num_heads,
-                                                  num_kv_heads, window, scale * LOG2E, part_o,
-                                                  part_ml, status);
+    ti_launch_pdl(attn_decode_kernel<HD>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,
+                  block_table, bt_stride, pages, num_pages, page_size, num_heads, num_kv_heads, window,
+                  scale * LOG2E, part_o, part_ml, counters, out, status);
     if (int rc = ti_check_launch("attn_decode")) return rc;
+    if (counters) return 0;
     attn_decode_merge_kernel<<<(num_rows * num_heads + 3) / 4, 128, 0, s>>>(
         part_o, part_ml, rows, num_rows, num_heads, num_splits, HD, out);
     return ti_check_launch("attn_decode_merge");
@@ -329,13 +369,35 @@ extern "C" int ti_attn_decode_supported(int head_dim, int group, int page_size) 
 }
 
 // Scratch the caller provides: part_o [num_rows, num_heads, num_splits, head_dim] float32 and
-// part_ml [num_rows, num_heads, num_splits, 2] float32.
+// part_ml [num_rows, num_heads, num_splits, 2] float32.  `counters` is either null (the splits are
+// then merged by a second launch) or num_rows * num_kv_heads unsigned integers that are zero
+// before the first launch: the last block of a (row, kv head) merges in the same launch and
+// leaves its counter at zero again.
+extern "C" int ti_attn_decode_fused(const void* q, const int* rows, int num_rows, const int* positions,
+                                    const int* req_of_tok, const int* block_table, int bt_stride,
+                                    const void* pages, int num_pages, int page_size, int num_heads,
+                                    int num_kv_heads, int head_dim, int window, float scale,
+                                    int num_splits, float* part_o, float* part_ml,
+                                    unsigned* counters, void* out, int* status, void* stream);
+
 extern "C" int ti_attn_decode(const void* q, const int* rows, int num_rows, const int* positions,
                               const int* req_of_tok, const int* block_table, int bt_stride,
                               const void* pages, int num_pages, int page_size, int num_heads,
                               int num_kv_heads, int head_dim, int window, float scale,
                               int num_splits, float* part_o, float* part_ml, void* out,
                               int* status, void* stream) {
+    return ti_attn_decode_fused(q, rows, num_rows, positions, req_of_tok, block_table, bt_stride,
+                                pages, num_pages, page_size, num_heads, num_kv_heads, head_dim,
+                                window, scale, num_splits, part_o, part_ml, nullptr, out, status,
+                                stream);
+}
+
+extern "C" int ti_attn_decode_fused(const void* q, const int* rows, int num_rows, const int* positions,
+                                    const int* req_of_tok, const int* block_table, int bt_stride,
+                                    const void* pages, int num_pages, int page_size, int num_heads,
+                                    int num_kv_heads, int head_dim, int window, float scale,
+                                    int num_splits, float* part_o, float* part_ml,
+                                    unsigned* counters, void* out, int* status, void* stream) {
     if (num_rows == 0) return 0;
     TI_REQUIRE(num_heads % num_kv_heads == 0, "attn_decode: %d heads over %d kv heads", num_heads,
                num_kv_heads);
@@ -350,7 +412,7 @@ extern "C" int ti_attn_decode(const void* q, const int* rows, int num_rows, cons
         return launch_decode<HD>((const bf16*)q, rows, num_rows, positions, req_of_tok,            \
                                  block_table, bt_stride, (const bf16*)pages, num_pages, page_size, \
                                  num_heads, num_kv_heads, window, scale, num_splits, part_o,       \
-                                 part_ml, (bf16*)out, status, (cudaStream_t)stream)
+                                 part_ml, counters, (bf16*)out, status, (cudaStream_t)stream)
     switch (head_dim) {
         CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     }

@@ -25,6 +25,29 @@ int ti_check_launch(const char* what);             // cudaGetLastError -> 0 or t
         if (!(cond)) return ti_fail(__VA_ARGS__); \
     } while (0)
 
+// Programmatic dependent launch.  A kernel launched through ti_launch_pdl may start while the
+// kernel before it in the stream is still running; it must call pdl_wait() before it reads
+// anything that kernel wrote (what it does before that, such as fetching weights, overlaps
+// with the predecessor).  pdl_launch() lets the next kernel's blocks be scheduled early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t ti_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 

@@ -37,16 +37,20 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT>
+// ROWS = 16: a block owns 16 rows of W.  ROWS = 8: it owns 8 (the upper half of the MMA's A
+// operand is zero), which doubles the number of blocks for narrow outputs.
+template <int NT, int ROWS>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ c,
                    bf16* __restrict__ out_act, int m, int n, int k, int lda, int ldw, int ldc,
-                   int ld_act, int mode) {
+                   int ld_act, int mode, const float* __restrict__ norm_w, float norm_eps,
+                   unsigned* __restrict__ counter) {
     constexpr int MP = NT * 8;                                  // padded token count
-    __shared__ float part[WARPS][STRIP][MP + 1];
+    constexpr int BATCH = 8;                                    // chunks a warp has in flight
+    __shared__ float part[WARPS][ROWS][MP + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int n0 = blockIdx.x * STRIP;
+    const int n0 = blockIdx.x * ROWS;
     // rows past N are read from the last row and never stored
     const bf16* w_lo = w + (size_t)min(n0 + g, n - 1) * ldw + tq * 8;
     const bf16* w_hi = w + (size_t)min(n0 + g + 8, n - 1) * ldw + tq * 8;
@@ -59,21 +63,25 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
 
     const int chunks = k / CHUNK;
-    constexpr int UNROLL = 4;
-    for (int c0 = warp; c0 < chunks; c0 += WARPS * UNROLL) {
-        uint4 wl[UNROLL], wh[UNROLL];
+    pdl_launch();
+    for (int c0 = warp; c0 < chunks; c0 += WARPS * BATCH) {
+        // all loads of the batch first: the product is bound by memory latency, not by arithmetic
+        uint4 wl[BATCH], wh[BATCH];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int u = 0; u < BATCH; ++u) {
             const int ch = c0 + u * WARPS;
             if (ch < chunks) {
                 wl[u] = ld_stream(w_lo + (size_t)ch * CHUNK);
-                wh[u] = ld_stream(w_hi + (size_t)ch * CHUNK);
+                if (ROWS == 16) wh[u] = ld_stream(w_hi + (size_t)ch * CHUNK);
             }
         }
+        // the weights do not depend on the kernel before this one; the activations do
+        if (c0 == warp) pdl_wait();
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int u = 0; u < BATCH; ++u) {
             const int ch = c0 + u * WARPS;
             if (ch >= chunks) break;
+            if (ROWS == 8) wh[u] = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const uint4 x = *reinterpret_cast<const uint4*>(a_row[j] + (size_t)ch * CHUNK);
@@ -87,27 +95,32 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
     for (int j = 0; j < NT; ++j) {
         part[warp][g][j * 8 + tq * 2] = acc[j][0];
         part[warp][g][j * 8 + tq * 2 + 1] = acc[j][1];
-        part[warp][g + 8][j * 8 + tq * 2] = acc[j][2];
-        part[warp][g + 8][j * 8 + tq * 2 + 1] = acc[j][3];
+        if (ROWS == 16) {
+            part[warp][g + 8][j * 8 + tq * 2] = acc[j][2];
+            part[warp][g + 8][j * 8 + tq * 2 + 1] = acc[j][3];
+        }
     }
+    if (chunks <= warp) pdl_wait();                   // a warp without chunks still orders its writes
     __syncthreads();
     if (mode == MODE_SWIGLU) {
-        const int i = threadIdx.x & 7;                          // gate row i, up row i + 8
-        const int col = blockIdx.x * 8 + i;
-        for (int tok = threadIdx.x >> 3; tok < m; tok += WARPS * 4) {
-            float gate = 0.0f, up = 0.0f;
+        if (ROWS == 16) {
+            const int i = threadIdx.x & 7;                      // gate row i, up row i + 8
+            const int col = blockIdx.x * 8 + i;
+            for (int tok = threadIdx.x >> 3; tok < m; tok += WARPS * 4) {
+                float gate = 0.0f, up = 0.0f;
 #pragma unroll
-            for (int wp = 0; wp < WARPS; ++wp) {
-                gate += part[wp][i][tok];
-                up += part[wp][i + 8][tok];
+                for (int wp = 0; wp < WARPS; ++wp) {
+                    gate += part[wp][i][tok];
+                    up += part[wp][(i + 8) % ROWS][tok];
+                }
+                if (n0 + i + 8 < n)
+                    out_act[(size_t)tok * ld_act + col] =
+                        __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
             }
-            if (n0 + i + 8 < n)
-                out_act[(size_t)tok * ld_act + col] =
-                    __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
         }
     } else {
-        const int i = threadIdx.x & 15;
-        for (int tok = threadIdx.x >> 4; tok < m; tok += WARPS * 2) {
+        const int i = threadIdx.x % ROWS;
+        for (int tok = threadIdx.x / ROWS; tok < m; tok += WARPS * 32 / ROWS) {
             float sum = 0.0f;
 #pragma unroll
             for (int wp = 0; wp < WARPS; ++wp) sum += part[wp][i][tok];
@@ -115,6 +128,35 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
                 float* p = c + (size_t)tok * ldc + n0 + i;
                 *p = mode == MODE_ACCUMULATE ? *p + sum : sum;
             }
+        }
+    }
+    if (counter == nullptr) return;
+    // RMSNorm of the finished rows, by the block that finishes last: out_act[t, :] =
+    // bfloat16(c[t, :] * (1 / sqrt(mean(c[t, :]^2) + eps)) * norm_w).  One warp per row; the rows
+    // come from L2, where the other blocks wrote them.
+    __shared__ unsigned ticket;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket = atomicAdd(counter, 1u);
+    __syncthreads();
+    if (ticket != gridDim.x - 1) return;
+    __threadfence();
+    if (threadIdx.x == 0) *counter = 0u;
+    for (int tok = warp; tok < m; tok += WARPS) {
+        const float* row = c + (size_t)tok * ldc;
+        float ss = 0.0f;
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(row + i));
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + norm_eps);
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(row + i));
+            const float4 g4 = *reinterpret_cast<const float4*>(norm_w + i);
+            bf16* o = out_act + (size_t)tok * ld_act + i;
+            *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v.x * inv * g4.x, v.y * inv * g4.y);
+            *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(v.z * inv * g4.z, v.w * inv * g4.w);
         }
     }
 }
@@ -125,10 +167,28 @@ extern "C" int ti_gemm_skinny_supported(int m, int n, int k, int lda, int ldw) {
     return m >= 1 && m <= 64 && n >= 1 && k >= CHUNK && k % CHUNK == 0 && lda % 8 == 0 && ldw % 8 == 0;
 }
 
+extern "C" int ti_gemm_skinny_norm(const void* a, const void* w, float* c, void* out_act, int m,
+                                   int n, int k, int lda, int ldw, int ldc, int ld_act, int mode,
+                                   const float* norm_w, float norm_eps, unsigned* counter,
+                                   void* stream);
+
 // mode 0: c = a w^T; 1: c += a w^T; 2: out_act[m, n/2] = swiglu over strips of 8 gate + 8 up rows.
 extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_act, int m, int n,
                               int k, int lda, int ldw, int ldc, int ld_act, int mode, void* stream) {
+    return ti_gemm_skinny_norm(a, w, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, nullptr, 0.0f,
+                               nullptr, stream);
+}
+
+// As ti_gemm_skinny in mode 0 or 1, followed in the same launch by the RMSNorm of the finished
+// rows: out_act[m, n] = bfloat16(rmsnorm(c) * norm_w).  `counter` is one unsigned integer that is
+// zero before the first launch; the launch leaves it at zero.  Needs n % 4 == 0.
+extern "C" int ti_gemm_skinny_norm(const void* a, const void* w, float* c, void* out_act, int m,
+                                   int n, int k, int lda, int ldw, int ldc, int ld_act, int mode,
+                                   const float* norm_w, float norm_eps, unsigned* counter,
+                                   void* stream) {
     if (m == 0 || n == 0) return 0;
+    TI_REQUIRE(counter == nullptr || (mode != MODE_SWIGLU && n % 4 == 0 && ldc % 4 == 0 && ld_act % 4 == 0),
+               "gemm_skinny: the fused norm needs N, ldc and the output stride to be multiples of 4");
     TI_REQUIRE(ti_gemm_skinny_supported(m, n, k, lda, ldw),
                "gemm_skinny: M=%d (1..64), K=%d (multiple of 32) or row strides %d, %d (multiples of 8) "
                "are not supported", m, k, lda, ldw);
@@ -136,15 +196,21 @@ extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_
                "gemm_skinny: operands must be 16-byte aligned");
     TI_REQUIRE(mode != MODE_SWIGLU || n % 16 == 0, "gemm_skinny: SwiGLU needs N %% 16 == 0, got %d", n);
     cudaStream_t s = (cudaStream_t)stream;
-    const unsigned grid = (unsigned)((n + STRIP - 1) / STRIP);
-#define LAUNCH(NT)                                                                              \
-    gemm_skinny_kernel<NT><<<grid, WARPS * 32, 0, s>>>((const bf16*)a, (const bf16*)w, c,       \
-                                                       (bf16*)out_act, m, n, k, lda, ldw, ldc,  \
-                                                       ld_act, mode)
-    if (m <= 8) LAUNCH(1);
-    else if (m <= 16) LAUNCH(2);
-    else if (m <= 32) LAUNCH(4);
-    else LAUNCH(8);
+    // narrow outputs get blocks of 8 rows, so that at least about 128 blocks share the reading
+    const bool narrow = mode != MODE_SWIGLU && (n + STRIP - 1) / STRIP < 128;
+#define LAUNCH(NT)                                                                                  \
+    if (narrow)                                                                                     \
+        ti_launch_pdl(gemm_skinny_kernel<NT, 8>, (unsigned)((n + 7) / 8), WARPS * 32, 0, s,         \
+                      (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, lda, ldw, ldc,    \
+                      ld_act, mode, norm_w, norm_eps, counter);                                     \
+    else                                                                                            \
+        ti_launch_pdl(gemm_skinny_kernel<NT, 16>, (unsigned)((n + STRIP - 1) / STRIP), WARPS * 32,  \
+                      0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, lda, ldw,   \
+                      ldc, ld_act, mode, norm_w, norm_eps, counter)
+    if (m <= 8) { LAUNCH(1); }
+    else if (m <= 16) { LAUNCH(2); }
+    else if (m <= 32) { LAUNCH(4); }
+    else { LAUNCH(8); }
 #undef LAUNCH
     return ti_check_launch("gemm_skinny");
 }

@@ -8,6 +8,8 @@ namespace {
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              int hidden, float* __restrict__ out) {
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const TW* row = table + (size_t)tokens[t] * hidden;
     float* o = out + (size_t)t * hidden;
@@ -20,6 +22,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows, float eps, int n,
                                TO* __restrict__ out) {
     __shared__ float scratch[32];
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * n;
     TO* o = out + (size_t)r * n;
@@ -90,9 +94,9 @@ extern "C" int ti_embed(const void* table, int table_dtype, const int* tokens, i
     if (num_tokens == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == TI_BF16)
-        embed_kernel<bf16><<<num_tokens, 256, 0, s>>>((const bf16*)table, tokens, hidden, out);
+        ti_launch_pdl(embed_kernel<bf16>, num_tokens, 256, 0, s, (const bf16*)table, tokens, hidden, out);
     else if (table_dtype == TI_F32)
-        embed_kernel<float><<<num_tokens, 256, 0, s>>>((const float*)table, tokens, hidden, out);
+        ti_launch_pdl(embed_kernel<float>, num_tokens, 256, 0, s, (const float*)table, tokens, hidden, out);
     else
         return ti_fail("embed: table dtype code %d is not float32 or bfloat16", table_dtype);
     return ti_check_launch("embed");
@@ -104,9 +108,9 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = n >= 1024 ? 256 : 128;
     if (out_dtype == TI_BF16)
-        rmsnorm_kernel<bf16><<<num_rows, threads, 0, s>>>(x, weight, rows, eps, n, (bf16*)out);
+        ti_launch_pdl(rmsnorm_kernel<bf16>, num_rows, threads, 0, s, x, weight, rows, eps, n, (bf16*)out);
     else if (out_dtype == TI_F32)
-        rmsnorm_kernel<float><<<num_rows, threads, 0, s>>>(x, weight, rows, eps, n, (float*)out);
+        ti_launch_pdl(rmsnorm_kernel<float>, num_rows, threads, 0, s, x, weight, rows, eps, n, (float*)out);
     else
         return ti_fail("rmsnorm: output dtype code %d is not float32 or bfloat16", out_dtype);
     return ti_check_launch("rmsnorm");

@@ -69,6 +69,11 @@ class CudaOps:
         self.core.ti_last_error.restype = ctypes.c_char_p
         self._declare()
         self._bf16 = None
+        self._counters = None
+        self._gemm_counter = None
+        # Computing the following RMSNorm in the product's last block saves a launch but was
+        # measured slower than the norm's own launch (the tail runs on one SM), so it is off.
+        self.fuse_norm_tail = False
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -97,10 +102,12 @@ class CudaOps:
             b = load_library("bf16")
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_gemm_skinny.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]
+            b.ti_gemm_skinny_norm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
+                                              _f, _vp, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
             b.ti_attn_decode_supported.argtypes = [_i, _i, _i]
-            b.ti_attn_decode.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                         _f, _i, _vp, _vp, _vp, _vp, _vp]
+            b.ti_attn_decode_fused.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i,
+                                               _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
             b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
             b.ti_attn_prefill_supported.argtypes = [_i, _i]
@@ -167,7 +174,19 @@ class CudaOps:
                                       x.shape[1], float(eps), out.data_ptr(),
                                       _code(out, "rmsnorm"), self._stream()))
 
-    def linear(self, a, w, out, accumulate=False):
+    def linear(self, a, w, out, accumulate=False, then_norm=None):
+        """out (+)= a @ w.T.  ``then_norm=(weight, eps, normed)`` also writes
+        ``normed = rmsnorm(out) * weight``, in the same launch where the kernel can."""
+        if then_norm is not None:
+            norm_w, eps, normed = then_norm
+            if self._linear(a, w, out, accumulate, then_norm):
+                return
+            self.rmsnorm(out, norm_w, eps, normed)
+            return
+        self._linear(a, w, out, accumulate, None)
+
+    def _linear(self, a, w, out, accumulate, then_norm) -> bool:
+        """Runs the product; True if it also computed the norm asked for."""
         m, k = a.shape
         n = w.shape[0]
         _need(w.shape[1] == k and tuple(out.shape) == (m, n), "linear: shapes do not agree")
@@ -176,11 +195,23 @@ class CudaOps:
               "linear: rows must be contiguous")
         if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
             if self.bf16.ti_gemm_skinny_supported(m, n, k, a.stride(0), w.stride(0)):
+                fuse = (self.fuse_norm_tail and then_norm is not None and then_norm[2].dtype == torch.bfloat16
+                        and n % 4 == 0 and out.stride(0) % 4 == 0 and then_norm[2].stride(0) % 4 == 0)
+                if fuse:
+                    if self._gemm_counter is None:
+                        self._gemm_counter = torch.zeros(1, dtype=torch.int32, device=a.device)
+                    norm_w, eps, normed = then_norm
+                    self._ok(self.bf16.ti_gemm_skinny_norm(
+                        a.data_ptr(), w.data_ptr(), out.data_ptr(), normed.data_ptr(), m, n, k,
+                        a.stride(0), w.stride(0), out.stride(0), normed.stride(0),
+                        1 if accumulate else 0, norm_w.data_ptr(), float(eps),
+                        self._gemm_counter.data_ptr(), self._stream()), self.bf16)
+                    return True
                 self._ok(self.bf16.ti_gemm_skinny(
                     a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
                     w.stride(0), out.stride(0), 0, 1 if accumulate else 0, self._stream()),
                     self.bf16)
-                return
+                return False
             mode = 1 if accumulate else 0
             if (m > 64 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and
                     out.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
@@ -189,11 +220,12 @@ class CudaOps:
                     a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
                     w.stride(0), out.stride(0), 0, mode, self.status.data_ptr(), self._stream()),
                     self.bf16)
-                return
+                return False
         self._ok(self.core.ti_gemm_simple(
             a.data_ptr(), _code(a, "linear"), w.data_ptr(), _code(w, "linear"), out.data_ptr(),
             m, n, k, a.stride(0), w.stride(0), out.stride(0), int(bool(accumulate)),
             self._stream()))
+        return False
 
     def gate_up_swiglu(self, h, w_gate_up, out):
         inter = out.shape[1]
@@ -269,13 +301,17 @@ class CudaOps:
                                  device=q.device)
             part_ml = torch.empty((n_dec, num_heads, splits, 2), dtype=torch.float32,
                                   device=q.device)
-            self._ok(self.bf16.ti_attn_decode(
+            if self._counters is None or self._counters.numel() < n_dec * num_kv_heads:
+                # zero once; every launch leaves its counters at zero again
+                self._counters = torch.zeros(max(4096, n_dec * num_kv_heads), dtype=torch.int32,
+                                             device=q.device)
+            self._ok(self.bf16.ti_attn_decode_fused(
                 q.data_ptr(), step.decode_rows.data_ptr(), n_dec, step.positions.data_ptr(),
                 step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
                 pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
-                float(scale), splits, part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(),
-                self.status.data_ptr(), self._stream()), self.bf16)
-            self.launches += 1
+                float(scale), splits, part_o.data_ptr(), part_ml.data_ptr(),
+                self._counters.data_ptr(), out.data_ptr(), self.status.data_ptr(),
+                self._stream()), self.bf16)
             rows, n_rows = step.chunk_rows, step.chunk_rows.shape[0]
             if n_rows == 0:
                 return

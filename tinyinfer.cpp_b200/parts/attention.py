@@ -22,6 +22,7 @@ from .base import (MATRIX, NORM_WEIGHT, PagedKVSpec, Part, WeightSpec, as_float3
 
 class Attention(Part):
     category = "mixer"
+    fuses_norm = True        # forward(..., then_norm=norm) returns norm(residual) from its last launch
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: float, position: PartSpec, window: Optional[int] = None,
@@ -66,7 +67,7 @@ class Attention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, ops, h, residual, step, cache):
+    def forward(self, ops, h, residual, step, cache, then_norm=None):
         t = h.shape[0]
         dev = h.device
         qkv = torch.empty((t, self.nq + 2 * self.nk), dtype=torch.float32, device=dev)
@@ -78,7 +79,13 @@ class Attention(Part):
         out = torch.empty((t, self.nq), dtype=h.dtype, device=dev)
         ops.paged_attention(q, step, cache, out, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.window, self.scale)
-        ops.linear(out, self.w_o, residual, accumulate=True)
+        if then_norm is None:
+            ops.linear(out, self.w_o, residual, accumulate=True)
+            return None
+        normed = torch.empty((t, self.hidden_size), dtype=h.dtype, device=dev)
+        ops.linear(out, self.w_o, residual, accumulate=True,
+                   then_norm=(then_norm.weight, then_norm.eps, normed))
+        return normed
 
 
 register_part("mixer", "attention", Attention)

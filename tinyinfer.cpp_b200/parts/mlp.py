@@ -13,6 +13,7 @@ from .base import MATRIX, Part, WeightSpec, register_part
 
 class SwiGLU(Part):
     category = "ffn"
+    fuses_norm = True        # forward(..., then_norm=norm) returns norm(residual) from its last launch
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = int(hidden_size)
@@ -34,10 +35,16 @@ class SwiGLU(Part):
         self.w_gate_up = ops.pack_gate_up(g, u)
         self.w_down = ops.pack_linear(tensors["down_proj.weight"])
 
-    def forward(self, ops, h, residual, step):
+    def forward(self, ops, h, residual, step, then_norm=None):
         y = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
         ops.gate_up_swiglu(h, self.w_gate_up, y)
-        ops.linear(y, self.w_down, residual, accumulate=True)
+        if then_norm is None:
+            ops.linear(y, self.w_down, residual, accumulate=True)
+            return None
+        normed = torch.empty((h.shape[0], self.hidden_size), dtype=h.dtype, device=h.device)
+        ops.linear(y, self.w_down, residual, accumulate=True,
+                   then_norm=(then_norm.weight, then_norm.eps, normed))
+        return normed
 
 
 register_part("ffn", "swiglu", SwiGLU)
