@@ -93,6 +93,94 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
     }
 }
 
+// The same work for head sizes up to 64 * VEC with head_dim / 2 a multiple of VEC: a lane keeps
+// VEC consecutive elements of each half of the vector in registers (the rotation pairs element
+// k with k + head_dim / 2, so a lane owns whole pairs); no shared memory.
+template <typename TQ, typename TC, int VEC>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
+                              const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                              float eps, const float* __restrict__ inv_freq,
+                              const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                              const int* __restrict__ block_table, int bt_stride,
+                              TC* __restrict__ pages, int num_pages, int page_size, int write_kv,
+                              int num_heads, int num_kv_heads, int head_dim, int items_per_warp,
+                              TQ* __restrict__ q_out, int* __restrict__ status) {
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int nq = num_heads * head_dim, nk = num_kv_heads * head_dim;
+    const int pos = positions[t];
+    // with many tokens a warp takes several vectors in turn, so that blocks are not tiny
+    for (int turn = 0; turn < items_per_warp; ++turn) {
+    const int item = (blockIdx.y * items_per_warp + turn) * WARPS + warp;
+    if (item >= num_heads + 2 * num_kv_heads) return;
+    int kind, head;
+    if (item < num_heads) { kind = 0; head = item; }
+    else if (item < num_heads + num_kv_heads) { kind = 1; head = item - num_heads; }
+    else { kind = 2; head = item - num_heads - num_kv_heads; }
+    if (kind != 0 && !write_kv) continue;
+    const float* src = qkv + (size_t)t * qkv_stride +
+                       (kind == 0 ? head * head_dim : kind == 1 ? nq + head * head_dim
+                                                                : nq + nk + head * head_dim);
+    TC* dst = nullptr;
+    if (kind != 0) {
+        const int r = req_of_tok[t];
+        const int page = block_table[(size_t)r * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+            continue;
+        }
+        dst = pages + ((((size_t)page * 2 + (kind - 1)) * num_kv_heads + head) * page_size +
+                       pos % page_size) * head_dim;
+    }
+    const int k0 = lane * VEC;
+    const bool active = k0 < half;
+    float lo[VEC], hi[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        lo[i] = active ? src[k0 + i] : 0.0f;
+        hi[i] = active ? src[half + k0 + i] : 0.0f;
+    }
+    if (kind == 2) {
+        if (active) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                dst[k0 + i] = from_f32<TC>(lo[i]);
+                dst[half + k0 + i] = from_f32<TC>(hi[i]);
+            }
+        }
+        continue;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) { ss = fmaf(lo[i], lo[i], ss); ss = fmaf(hi[i], hi[i], ss); }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+    if (!active) continue;
+    const float* w = kind == 0 ? q_weight : k_weight;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const float x0 = lo[i] * inv * w[k0 + i];
+        const float x1 = hi[i] * inv * w[half + k0 + i];
+        float sn, cs;
+        sincosf((float)pos * inv_freq[k0 + i], &sn, &cs);
+        const float y0 = x0 * cs - x1 * sn;
+        const float y1 = x0 * sn + x1 * cs;
+        if (kind == 0) {
+            TQ* q = q_out + (size_t)t * nq + head * head_dim;
+            q[k0 + i] = from_f32<TQ>(y0);
+            q[half + k0 + i] = from_f32<TQ>(y1);
+        } else {
+            dst[k0 + i] = from_f32<TC>(y0);
+            dst[half + k0 + i] = from_f32<TC>(y1);
+        }
+    }
+    }
+}
+
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_simple_kernel(const TQ* __restrict__ q, const int* __restrict__ rows,
@@ -197,11 +285,26 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
     const int items = num_heads + 2 * num_kv_heads;
     dim3 grid(num_tokens, (items + WARPS - 1) / WARPS);
     cudaStream_t s = (cudaStream_t)stream;
+    const int half = head_dim / 2;
+    const int ipw = num_tokens >= 512 ? (items + WARPS - 1) / WARPS : 1;      // items per warp
+    dim3 vgrid(num_tokens, (items + WARPS * ipw - 1) / (WARPS * ipw));
+    const int vec = (half % 4 == 0 && half > 64) ? 4 : (half % 2 == 0 && half <= 64) ? 2 : 0;
 #define CALL(TQ, TC)                                                                          \
-    ti_launch_pdl(qk_norm_rope_store_kernel<TQ, TC>, grid, WARPS * 32, 0, s,                   \
-        qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
-        bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,         \
-        head_dim, (TQ*)q_out, status)
+    if (vec == 2)                                                                             \
+        ti_launch_pdl(qk_norm_rope_store_vec_kernel<TQ, TC, 2>, vgrid, WARPS * 32, 0, s,       \
+            qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
+            bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
+            head_dim, ipw, (TQ*)q_out, status);                                                \
+    else if (vec == 4)                                                                        \
+        ti_launch_pdl(qk_norm_rope_store_vec_kernel<TQ, TC, 4>, vgrid, WARPS * 32, 0, s,       \
+            qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
+            bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
+            head_dim, ipw, (TQ*)q_out, status);                                                \
+    else                                                                                      \
+        ti_launch_pdl(qk_norm_rope_store_kernel<TQ, TC>, grid, WARPS * 32, 0, s,               \
+            qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
+            bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
+            head_dim, (TQ*)q_out, status)
     TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
 #undef CALL
     return ti_check_launch("qk_norm_rope_store");

@@ -50,7 +50,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // tiles[i] = {request row, first flat token, number of query rows (<= 64)}
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, HD > 64 ? 3 : 4)
 attn_prefill_kernel(const bf16* __restrict__ q, const int* __restrict__ tiles,
                     const int* __restrict__ positions, const int* __restrict__ block_table,
                     int bt_stride, const bf16* __restrict__ pages, int num_pages, int page_size,

@@ -1,12 +1,14 @@
 // Matrix product on the 5th-generation tensor cores: C[M,N] (+)= A[M,K] * W[N,K]^T, bfloat16
 // operands, float32 accumulation in tensor memory.  This is the prefill product (M > 64).
 //
-// One block computes one 128 x 128 tile of C.  Warp 0 feeds a ring of shared-memory stages
-// with TMA tile loads (64 elements of K = one 128-byte swizzled row per matrix row); warp 1
-// issues tcgen05.mma (128 x 128 x 16, both operands K-major from shared memory, accumulator
-// in TMEM) and hands each stage back with tcgen05.commit; warps 2-5 wait for the last
-// commit, read the accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes = rows that
-// its position in the warpgroup allows) and run the epilogue: store, accumulate into C (the
+// The kernel is persistent: one block per SM walks over 128 x BN tiles of C (BN = 256, or 128
+// when the output is too narrow to give every SM a wide tile).  Warp 0 feeds a ring of
+// shared-memory stages with TMA tile loads (64 elements of K = one 128-byte swizzled row per
+// matrix row); warp 1 issues tcgen05.mma (128 x BN x 16, both operands K-major from shared
+// memory) into one of two accumulators in TMEM and hands each stage back with tcgen05.commit;
+// warps 2-5 read a finished accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes = rows
+// that its position in the warpgroup allows) and run the epilogue while the next tile's
+// products already fill the other accumulator.  Epilogues: store, accumulate into C (the
 // residual stream), or SwiGLU over 8 gate + 8 up columns into bfloat16.  Rows and columns past
 // M, N and K are zero-filled by TMA on the way in and skipped on the way out.
 //
@@ -19,13 +21,16 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16;
-constexpr int STAGES = 6;
-constexpr int STAGE_A = BM * BK * 2, STAGE_B = BN * BK * 2;
-constexpr int SMEM_BYTES = STAGES * (STAGE_A + STAGE_B) + 1024 /* alignment */ + 256 /* barriers */;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr unsigned TMEM_COLS = 128;
 constexpr long long WAIT_LIMIT = 1LL << 31;          // cycles; about a second
+
+template <int BN> struct Tile {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int STAGE_A = BM * BK * 2, STAGE_B = BN * BK * 2;
+    static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr unsigned TMEM_COLS = 2 * BN;     // two accumulators
+};
 
 enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2 };
 enum { TI_ERR_TIMEOUT = 2 };
@@ -39,6 +44,9 @@ __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
                  "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 // Waits until the barrier's phase with the given parity has completed; gives up after WAIT_LIMIT cycles.
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
@@ -98,32 +106,37 @@ __device__ __forceinline__ void tmem_load32(unsigned taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     float* __restrict__ c, bf16* __restrict__ out_act, int m, int n, int k, int ldc,
                     int ld_act, int mode, int* __restrict__ status) {
+    using T = Tile<BN>;
+    constexpr int STAGES = T::STAGES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* stage_a = smem;
-    unsigned char* stage_b = smem + STAGES * STAGE_A;
-    unsigned long long* bars = (unsigned long long*)(smem + STAGES * (STAGE_A + STAGE_B));
-    unsigned long long* full = bars;                 // [STAGES] TMA -> MMA
-    unsigned long long* empty = bars + STAGES;       // [STAGES] MMA -> TMA
-    unsigned long long* acc_ready = bars + 2 * STAGES;
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 1);
+    unsigned char* stage_b = smem + STAGES * T::STAGE_A;
+    unsigned long long* bars = (unsigned long long*)(smem + STAGES * (T::STAGE_A + T::STAGE_B));
+    unsigned long long* full = bars;                     // [STAGES] TMA -> MMA
+    unsigned long long* empty = bars + STAGES;           // [STAGES] MMA -> TMA
+    unsigned long long* acc_full = bars + 2 * STAGES;    // [2] MMA -> epilogue
+    unsigned long long* acc_empty = bars + 2 * STAGES + 2;   // [2] epilogue -> MMA
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const int num_kb = (k + BK - 1) / BK;
+    const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"(T::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -131,16 +144,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
 
+    // tiles in order of m fastest, so that blocks running together share few panels of W
     bool ok = true;
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1);
-                if (!ok) break;
-                mbar_expect_tx(&full[s], STAGE_A + STAGE_B);
-                tma_load_2d(stage_a + s * STAGE_A, &map_a, &full[s], kb * BK, m0);
-                tma_load_2d(stage_b + s * STAGE_B, &map_w, &full[s], kb * BK, n0);
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[s], T::STAGE_A + T::STAGE_B);
+                    tma_load_2d(stage_a + s * T::STAGE_A, &map_a, &full[s], kb * BK, m0);
+                    tma_load_2d(stage_b + s * T::STAGE_B, &map_w, &full[s], kb * BK, n0);
+                }
             }
         }
     } else if (warp == 1) {
@@ -148,36 +166,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // bf16 x bf16 -> f32, both K-major, N at bit 17 (/8), M at bit 24 (/16)
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
                                    ((unsigned)(BM >> 4) << 24);
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(&full[s], (kb / STAGES) & 1);
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1);   // the epilogue has read it
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned long long da = umma_desc(stage_a + s * STAGE_A);
-                const unsigned long long db = umma_desc(stage_b + s * STAGE_B);
+                const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned long long da = umma_desc(stage_a + s * T::STAGE_A);
+                    const unsigned long long db = umma_desc(stage_b + s * T::STAGE_B);
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                    // 16 elements of K = 32 bytes further inside the swizzled row
-                    umma_bf16(tmem_base, da + (unsigned long long)(kk * UMMA_K * 2 >> 4),
-                              db + (unsigned long long)(kk * UMMA_K * 2 >> 4), idesc,
-                              (kb | kk) != 0);
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // 16 elements of K = 32 bytes further inside the swizzled row
+                        umma_bf16(tmem_acc, da + (unsigned long long)(kk * UMMA_K * 2 >> 4),
+                                  db + (unsigned long long)(kk * UMMA_K * 2 >> 4), idesc, (kb | kk) != 0);
+                    }
+                    umma_commit(&empty[s]);           // the stage is free once these MMAs have read it
                 }
-                umma_commit(&empty[s]);               // the stage is free once these MMAs have read it
+                umma_commit(&acc_full[buf]);          // the tile's accumulator is complete
             }
-            umma_commit(acc_ready);                   // all MMAs done: the accumulator is complete
         }
     } else {
         const int quarter = warp & 3;                 // the TMEM lanes this warp may read
-        ok = mbar_wait(acc_ready, 0);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const int row = m0 + quarter * 32 + lane;
-        if (ok) {
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 float v[32];
-                tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
-                if (row >= m) continue;
+                tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c0), v);
                 const int col = n0 + c0;
+                if (row >= m || col >= n) continue;
                 if (mode == MODE_SWIGLU) {
                     // columns: 8 gate, their 8 up, 8 gate, their 8 up
 #pragma unroll
@@ -209,6 +238,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            // all of this warp's reads of the accumulator are done: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     if (!ok) atomicCAS(status, 0, TI_ERR_TIMEOUT);
@@ -217,7 +250,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
-                     ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+                     ::"r"(tmem_base), "r"(T::TMEM_COLS) : "memory");
     }
 }
 
@@ -238,13 +271,13 @@ EncodeTiled encode_fn() {
     return fn;
 }
 
-// rows x cols bfloat16, row-major with `ld` elements between rows; tiles of 128 rows x 64 columns
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld) {
+// rows x cols bfloat16, row-major with `ld` elements between rows; tiles of box_rows x 64 columns
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
     EncodeTiled fn = encode_fn();
     if (!fn) return ti_fail("gemm_tcgen05: the driver lacks cuTensorMapEncodeTiled");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {BK, 128};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                     elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -273,19 +306,33 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     TI_REQUIRE(mode == MODE_SWIGLU ? ((uintptr_t)out_act % 16 == 0 && ld_act % 8 == 0)
                                    : (uintptr_t)c % 16 == 0,
                "gemm_tcgen05: the output must be 16-byte aligned");
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int tiles_m = (m + BM - 1) / BM;
+    // wide tiles when they still give every SM one; else twice as many narrow ones
+    const bool wide = tiles_m * ((n + 255) / 256) >= sms;
+    CUtensorMap map_a, map_w;
+    if (int rc = make_map(&map_a, a, m, k, lda, BM)) return rc;
+    if (int rc = make_map(&map_w, w, n, k, ldw, wide ? 256 : 128)) return rc;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Tile<128>::SMEM);
         if (e != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }
-    CUtensorMap map_a, map_w;
-    if (int rc = make_map(&map_a, a, m, k, lda)) return rc;
-    if (int rc = make_map(&map_w, w, n, k, ldw)) return rc;
-    dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
-    TI_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d rows exceed the grid limit", m);
-    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
-        map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    if (wide) {
+        const int tiles = tiles_m * ((n + 255) / 256);
+        gemm_tcgen05_kernel<256><<<tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM, (cudaStream_t)stream>>>(
+            map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    } else {
+        const int tiles = tiles_m * ((n + 127) / 128);
+        gemm_tcgen05_kernel<128><<<tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM, (cudaStream_t)stream>>>(
+            map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    }
     return ti_check_launch("gemm_tcgen05");
 }

@@ -37,6 +37,42 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * inv * w[i]);
 }
 
+// The same norm with one warp per row and 16-byte accesses, for row lengths that are multiples
+// of 4: no shared memory, no block barrier; the second pass reads the row from L1.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                    const int* __restrict__ rows, float eps, int n, int num_rows,
+                    TO* __restrict__ out) {
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= num_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const int n4 = n >> 2;
+    float ss = 0.0f;
+    for (int i = lane; i < n4; i += 32) {
+        const float4 v = xr[i];
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+    TO* o = out + (size_t)r * n;
+    for (int i = lane; i < n4; i += 32) {
+        const float4 v = xr[i], g = w4[i];
+        if constexpr (sizeof(TO) == 2) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(v.x * inv * g.x, v.y * inv * g.y);
+            __nv_bfloat162 b = __floats2bfloat162_rn(v.z * inv * g.z, v.w * inv * g.w);
+            uint2 pk = make_uint2(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b));
+            *reinterpret_cast<uint2*>(o + 4 * i) = pk;
+        } else {
+            *reinterpret_cast<float4*>(o + 4 * i) =
+                make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+        }
+    }
+}
+
 // y[t, j] = silu(gate_j) * up_j, silu(g) = g / (1 + exp(-g)).  Stacked layout: gate_j = gu[t, j],
 // up_j = gu[t, inter + j].  Interleaved layout (groups of 8 gate columns followed by their 8 up
 // columns): gate_j = gu[t, 16 (j / 8) + j % 8], up_j eight columns further.
@@ -106,6 +142,16 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
                           int n, float eps, void* out, int out_dtype, void* stream) {
     if (num_rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (n % 4 == 0 && num_rows >= 64 && (out_dtype == TI_BF16 || out_dtype == TI_F32) &&
+        (uintptr_t)x % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        // many rows: a warp per row.  (Few rows keep a block per row: more threads per row.)
+        const unsigned grid = (unsigned)((num_rows + 7) / 8);
+        if (out_dtype == TI_BF16)
+            ti_launch_pdl(rmsnorm_warp_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
+        else
+            ti_launch_pdl(rmsnorm_warp_kernel<float>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (float*)out);
+        return ti_check_launch("rmsnorm");
+    }
     const int threads = n >= 1024 ? 256 : 128;
     if (out_dtype == TI_BF16)
         ti_launch_pdl(rmsnorm_kernel<bf16>, num_rows, threads, 0, s, x, weight, rows, eps, n, (bf16*)out);
