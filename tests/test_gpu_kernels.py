@@ -146,17 +146,19 @@ def _paged_case(num_heads, num_kv, hd, page_size, ctx_lens, q_lens, dtype, seed=
     for i, b in enumerate(blocks):
         bt[i, :b] = torch.tensor([next(it) for _ in range(b)], dtype=torch.int32)
     pages = _rand((num_pages, 2, num_kv, page_size, hd), dtype, seed=seed + 1)
-    positions, req_of_tok, dec, chk, tiles = [], [], [], [], []
+    positions, req_of_tok, dec, chk, tiles, tiles_big = [], [], [], [], [], []
     for i, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
         if ql > 1:
             tiles += [[i, len(positions) + lo, min(64, ql - lo)] for lo in range(0, ql, 64)]
+            tiles_big += [[i, len(positions) + lo, min(128, ql - lo)] for lo in range(0, ql, 128)]
         for j in range(ql):
             (dec if ql == 1 else chk).append(len(positions))
             positions.append(c - ql + j)
             req_of_tok.append(i)
     ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), decode_rows=ti(dec),
-                           chunk_rows=ti(chk), chunk_tiles=ti(tiles).view(-1, 3), max_position=max(ctx_lens), max_ctx_len=max(ctx_lens))
+                           chunk_rows=ti(chk), chunk_tiles=ti(tiles).view(-1, 3),
+                           chunk_tiles_big=ti(tiles_big).view(-1, 3), max_position=max(ctx_lens), max_ctx_len=max(ctx_lens))
     cache = SimpleNamespace(pages=pages, block_table=bt.to(DEV), page_size=page_size, writes=True)
     q = _rand((len(positions), num_heads * hd), dtype, seed=seed + 2)
     return step, cache, q
@@ -179,6 +181,29 @@ def test_paged_attention(ops, dtype, geom, window):
     RefOps().paged_attention(q, step, cache, ref, heads, kv, hd, window, scale)
     ops.check_status()
     _close(out, ref, 2e-5 if dtype == torch.float32 else 1.5e-2, f"attention {geom} window={window}")
+
+
+@pytest.mark.parametrize("geom", [(16, 8, 128, 16), (4, 1, 128, 32), (6, 6, 128, 16)])
+@pytest.mark.parametrize("window", [None, 1, 200])
+def test_prompt_attention_on_tcgen05_matches_the_mma_kernel_and_the_plain_statement(ops, geom, window):
+    """Head size 128 takes the tcgen05 kernel: long and short portions, earlier context, ragged ends."""
+    heads, kv, hd, ps = geom
+    ctx = [700, 128, 129, 1, 300, 1000, 257, 64]
+    qls = [131, 128, 129, 1, 2, 1000, 129, 33]
+    step, cache, q = _paged_case(heads, kv, hd, ps, ctx, qls, torch.bfloat16, seed=3)
+    scale = 1.0 / math.sqrt(hd)
+    got, ref, mma = torch.zeros_like(q), torch.zeros_like(q), torch.zeros_like(q)
+    assert ops.use_tc_attention
+    ops.paged_attention(q, step, cache, got, heads, kv, hd, window, scale)
+    ops.check_status()
+    ops.use_tc_attention = False
+    try:
+        ops.paged_attention(q, step, cache, mma, heads, kv, hd, window, scale)
+    finally:
+        ops.use_tc_attention = True
+    RefOps().paged_attention(q, step, cache, ref, heads, kv, hd, window, scale)
+    _close(mma, ref, 1.5e-2, f"mma attention {geom} window={window}")
+    _close(got, ref, 1.5e-2, f"tcgen05 attention {geom} window={window}")
 
 
 def test_decode_attention_finds_a_far_key(ops):

@@ -106,13 +106,18 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
                               TC* __restrict__ pages, int num_pages, int page_size, int write_kv,
                               int num_heads, int num_kv_heads, int head_dim, int items_per_warp,
                               TQ* __restrict__ q_out, int* __restrict__ status) {
+    __shared__ float cs_tab[MAX_HEAD_DIM / 2], sn_tab[MAX_HEAD_DIM / 2];
     pdl_launch();
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int half = head_dim >> 1;
     const int nq = num_heads * head_dim, nk = num_kv_heads * head_dim;
     const int pos = positions[t];
+    // the rotation of a token is the same for all its heads: its sines and cosines once per block
+    for (int k = threadIdx.x; k < half; k += WARPS * 32)
+        sincosf((float)pos * inv_freq[k], &sn_tab[k], &cs_tab[k]);
+    pdl_wait();
+    __syncthreads();
     // with many tokens a warp takes several vectors in turn, so that blocks are not tiny
     for (int turn = 0; turn < items_per_warp; ++turn) {
     const int item = (blockIdx.y * items_per_warp + turn) * WARPS + warp;
@@ -165,8 +170,7 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
     for (int i = 0; i < VEC; ++i) {
         const float x0 = lo[i] * inv * w[k0 + i];
         const float x1 = hi[i] * inv * w[half + k0 + i];
-        float sn, cs;
-        sincosf((float)pos * inv_freq[k0 + i], &sn, &cs);
+        const float sn = sn_tab[k0 + i], cs = cs_tab[k0 + i];
         const float y0 = x0 * cs - x1 * sn;
         const float y1 = x0 * sn + x1 * cs;
         if (kind == 0) {

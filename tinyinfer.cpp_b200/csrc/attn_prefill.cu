@@ -64,10 +64,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, const int* __restrict__ tiles,
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int h = blockIdx.y;
+    // heads run fastest in the grid, tiles are sorted by length: blocks start longest first
+    const int h = blockIdx.x, tile_id = blockIdx.y;
     const int kvh = h / (num_heads / num_kv_heads);
-    const int req = tiles[blockIdx.x * 3], tok0 = tiles[blockIdx.x * 3 + 1];
-    const int nrows = tiles[blockIdx.x * 3 + 2];
+    const int req = tiles[tile_id * 3], tok0 = tiles[tile_id * 3 + 1];
+    const int nrows = tiles[tile_id * 3 + 2];
     const int* table = block_table + (size_t)req * bt_stride;
     const size_t kv_stride = (size_t)num_kv_heads * page_size * HD;
 
@@ -260,7 +261,7 @@ int launch_prefill(const bf16* q, const int* tiles, int num_tiles, const int* po
         if (e != cudaSuccess) return ti_fail("attn_prefill: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(num_tiles, num_heads);
+    dim3 grid(num_heads, num_tiles);
     attn_prefill_kernel<HD><<<grid, WARPS * 32, SMEM, s>>>(q, tiles, positions, block_table, bt_stride,
                                                           pages, num_pages, page_size, num_heads,
                                                           num_kv_heads, window, scale * LOG2E, out,
@@ -290,7 +291,7 @@ extern "C" int ti_attn_prefill(const void* q, const int* tiles, int num_tiles, c
     TI_REQUIRE(ti_attn_prefill_supported(head_dim, page_size),
                "attn_prefill: head_dim %d (multiple of 16 up to 128) or page size %d (multiple of 16) "
                "is not supported", head_dim, page_size);
-    TI_REQUIRE(num_heads <= 65535, "attn_prefill: %d heads exceed the grid limit", num_heads);
+    TI_REQUIRE(num_tiles <= 65535, "attn_prefill: %d tiles exceed the grid limit", num_tiles);
 #define CASE(HD)                                                                                     \
     case HD:                                                                                         \
         return launch_prefill<HD>((const bf16*)q, tiles, num_tiles, positions, block_table, bt_stride, \

@@ -15,15 +15,14 @@
 // The k order of the accumulation is fixed (ascending blocks of 64, 16 at a time), so an
 // output element does not depend on M or on the tile around it.  Every wait on an mbarrier
 // is bounded: on a timeout the block records status 2, frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace {
 
+using namespace sm100;
+
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr long long WAIT_LIMIT = 1LL << 31;          // cycles; about a second
 
 template <int BN> struct Tile {
     static constexpr int STAGES = BN == 256 ? 4 : 6;
@@ -34,77 +33,6 @@ template <int BN> struct Tile {
 
 enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2 };
 enum { TI_ERR_TIMEOUT = 2 };
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
-                 "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Waits until the barrier's phase with the given parity has completed; gives up after WAIT_LIMIT cycles.
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    const long long start = clock64();
-    for (;;) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if (clock64() - start > WAIT_LIMIT) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-// K-major operand in 128-byte swizzled rows: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc(const void* p) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_u32(p) & 0x3FFFF) >> 4);           // start address
-    d |= (unsigned long long)1 << 16;                                  // leading byte offset (unused)
-    d |= (unsigned long long)(1024 >> 4) << 32;                        // stride byte offset
-    d |= (unsigned long long)1 << 46;                                  // descriptor version
-    d |= (unsigned long long)2 << 61;                                  // 128-byte swizzle
-    return d;
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da,
-                                          unsigned long long db, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(void* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
-                 ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -135,9 +63,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"(T::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        tmem_alloc(tmem_slot, T::TMEM_COLS);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -249,41 +175,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
-                     ::"r"(tmem_base), "r"(T::TMEM_COLS) : "memory");
+        tmem_dealloc(tmem_base, T::TMEM_COLS);
     }
-}
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-// rows x cols bfloat16, row-major with `ld` elements between rows; tiles of box_rows x 64 columns
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
-    EncodeTiled fn = encode_fn();
-    if (!fn) return ti_fail("gemm_tcgen05: the driver lacks cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                    elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return ti_fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
-    return 0;
 }
 
 }  // namespace
@@ -313,8 +206,8 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     // wide tiles when they still give every SM one; else twice as many narrow ones
     const bool wide = tiles_m * ((n + 255) / 256) >= sms;
     CUtensorMap map_a, map_w;
-    if (int rc = make_map(&map_a, a, m, k, lda, BM)) return rc;
-    if (int rc = make_map(&map_w, w, n, k, ldw, wide ? 256 : 128)) return rc;
+    if (int rc = make_map_bf16(&map_a, a, m, k, lda, BM, "gemm_tcgen05")) return rc;
+    if (int rc = make_map_bf16(&map_w, w, n, k, ldw, wide ? 256 : 128, "gemm_tcgen05")) return rc;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,

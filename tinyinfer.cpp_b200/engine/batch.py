@@ -16,7 +16,8 @@ import numpy as np
 import torch
 
 
-PREFILL_TILE_ROWS = 64     # query rows per block of the prompt-portion attention kernel
+PREFILL_TILE_ROWS = 64     # query rows per block of the prompt-portion attention kernel (mma.sync)
+PREFILL_TILE_ROWS_BIG = 128    # the same for the tcgen05 kernel
 
 
 @dataclass(frozen=True)
@@ -52,6 +53,7 @@ class StepBatch:
     decode_rows: torch.Tensor        # flat indices of tokens that are their request's only token
     chunk_rows: torch.Tensor         # flat indices of the tokens of requests that bring several
     chunk_tiles: torch.Tensor        # [n, 3] {request row, first flat token, rows} in tiles of 64
+    chunk_tiles_big: torch.Tensor    # the same in tiles of 128
     max_position: int = 0            # the model's longest context (bounds that do not vary by step)
     block_tables: list[torch.Tensor] = field(default_factory=list)   # per group [R, blocks]
     scratch: dict = field(default_factory=dict)   # per-step values kernels may cache
@@ -79,15 +81,19 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
     k = len(rows)
     dec = [int(cu[i]) for i in range(r) if q_lens[i] == 1]
     chk = [int(cu[i]) + j for i in range(r) if q_lens[i] > 1 for j in range(q_lens[i])]
-    tiles = []
-    for i in range(r):
-        if q_lens[i] > 1:
-            for lo in range(0, q_lens[i], PREFILL_TILE_ROWS):
-                tiles.append((starts[i] + lo, i, int(cu[i]) + lo, min(PREFILL_TILE_ROWS, q_lens[i] - lo)))
-    tiles.sort(key=lambda x: -x[0])                   # longest contexts first
-    tiles = [x[1:] for x in tiles]
+    def tile_list(rows_per_tile):
+        found = []
+        for i in range(r):
+            if q_lens[i] > 1:
+                for lo in range(0, q_lens[i], rows_per_tile):
+                    found.append((starts[i] + lo, i, int(cu[i]) + lo, min(rows_per_tile, q_lens[i] - lo)))
+        found.sort(key=lambda x: -x[0])               # longest contexts first
+        return [x[1:] for x in found]
+
+    tiles = tile_list(PREFILL_TILE_ROWS)
+    tiles_big = tile_list(PREFILL_TILE_ROWS_BIG)
     widths = [max(min_blocks, max((len(tb) for tb in grp), default=0)) for grp in tables]
-    total = 4 * t + (r + 1) + 3 * r + k + 3 * len(tiles) + sum(r * w for w in widths)
+    total = 4 * t + (r + 1) + 3 * r + k + 3 * len(tiles) + 3 * len(tiles_big) + sum(r * w for w in widths)
     host = torch.empty(max(total, 1), dtype=torch.int32,
                        pin_memory=(torch.device(device).type == "cuda"))
     buf = host.numpy()
@@ -110,6 +116,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         "dec": put(np.asarray(dec, dtype=np.int64), len(dec)),
         "chk": put(np.asarray(chk, dtype=np.int64), len(chk)),
         "tiles": put(np.asarray(tiles, dtype=np.int64).reshape(-1), 3 * len(tiles)),
+        "tiles_big": put(np.asarray(tiles_big, dtype=np.int64).reshape(-1), 3 * len(tiles_big)),
     }
     bt_spans = []
     for grp, w in zip(tables, widths):
@@ -130,6 +137,6 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         token_ids=view("tok"), positions=view("pos"), req_of_tok=view("roft"), cu_q=view("cu"),
         q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
         state_slots=view("slots"), decode_rows=view("dec"), chunk_rows=view("chk"),
-        chunk_tiles=view("tiles").view(-1, 3),
+        chunk_tiles=view("tiles").view(-1, 3), chunk_tiles_big=view("tiles_big").view(-1, 3),
         max_position=max_position,
         block_tables=[dev[a:b].view(r, w) for (a, b), w in bt_spans])

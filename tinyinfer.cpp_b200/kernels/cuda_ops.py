@@ -74,6 +74,7 @@ class CudaOps:
         # Computing the following RMSNorm in the product's last block saves a launch but was
         # measured slower than the norm's own launch (the tail runs on one SM), so it is off.
         self.fuse_norm_tail = False
+        self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -113,8 +114,12 @@ class CudaOps:
             b.ti_attn_prefill_supported.argtypes = [_i, _i]
             b.ti_attn_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f,
                                           _vp, _vp, _vp]
-            from ..engine.batch import PREFILL_TILE_ROWS
-            if b.ti_attn_prefill_tile_rows() != PREFILL_TILE_ROWS:
+            b.ti_attn_prefill_tc_supported.argtypes = [_i, _i, _i, _i]
+            b.ti_attn_prefill_tc.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                             _f, _vp, _vp, _vp]
+            from ..engine.batch import PREFILL_TILE_ROWS, PREFILL_TILE_ROWS_BIG
+            if (b.ti_attn_prefill_tile_rows() != PREFILL_TILE_ROWS or
+                    b.ti_attn_prefill_tc_tile_rows() != PREFILL_TILE_ROWS_BIG):
                 raise KernelError("the attention kernel's tile height and the batch builder's differ")
             self._bf16 = b
         return self._bf16
@@ -318,11 +323,20 @@ class CudaOps:
         n_tiles = step.chunk_tiles.shape[0]
         if (n_tiles and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and
                 self.bf16.ti_attn_prefill_supported(head_dim, cache.page_size)):
-            self._ok(self.bf16.ti_attn_prefill(
-                q.data_ptr(), step.chunk_tiles.data_ptr(), n_tiles, step.positions.data_ptr(),
-                bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size,
-                num_heads, num_kv_heads, head_dim, win, float(scale), out.data_ptr(),
-                self.status.data_ptr(), self._stream()), self.bf16)
+            big = getattr(step, "chunk_tiles_big", None)
+            if (self.use_tc_attention and big is not None and self.bf16.ti_attn_prefill_tc_supported(
+                    head_dim, cache.page_size, num_heads, num_kv_heads)):
+                self._ok(self.bf16.ti_attn_prefill_tc(
+                    q.data_ptr(), q.shape[0], big.data_ptr(), big.shape[0],
+                    step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
+                    pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
+                    float(scale), out.data_ptr(), self.status.data_ptr(), self._stream()), self.bf16)
+            else:
+                self._ok(self.bf16.ti_attn_prefill(
+                    q.data_ptr(), step.chunk_tiles.data_ptr(), n_tiles, step.positions.data_ptr(),
+                    bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size,
+                    num_heads, num_kv_heads, head_dim, win, float(scale), out.data_ptr(),
+                    self.status.data_ptr(), self._stream()), self.bf16)
             if rows is not None:          # the single-token rows went through the decode kernel
                 return
             rows, n_rows = step.decode_rows, n_dec
