@@ -184,6 +184,77 @@ def build_plan(cfg: Qwen3Config) -> ModelPlan:
                "head": "lm_head."})
 
 
+def config_from_gguf(meta: Mapping[str, Any], shapes: Mapping[str, tuple]) -> dict[str, Any]:
+    """The config.json dictionary that a GGUF file's metadata stands for.  Keys as the reference
+    reads them (src/model.cpp:32-41); the vocabulary falls back to the embedding's row count
+    (src/model.cpp:48-52); the head is tied iff the file has no ``output.weight``."""
+    def need(key):
+        if key not in meta:
+            raise ConfigError(f"GGUF metadata lacks '{key}'")
+        return meta[key]
+
+    vocab = meta.get("qwen3.vocab_size") or (shapes.get("token_embd.weight") or (0,))[0]
+    cfg = {
+        "architectures": [Qwen3Config.ARCHITECTURE],
+        "num_hidden_layers": need("qwen3.block_count"),
+        "hidden_size": need("qwen3.embedding_length"),
+        "intermediate_size": need("qwen3.feed_forward_length"),
+        "num_attention_heads": need("qwen3.attention.head_count"),
+        "num_key_value_heads": need("qwen3.attention.head_count_kv"),
+        "head_dim": need("qwen3.attention.key_length"),
+        "vocab_size": vocab,
+        "rope_theta": meta.get("qwen3.rope.freq_base", 1.0e6),
+        "rms_norm_eps": meta.get("qwen3.attention.layer_norm_rms_epsilon", 1.0e-6),
+        "max_position_embeddings": need("qwen3.context_length"),
+        "tie_word_embeddings": "output.weight" not in shapes,
+    }
+    eos = meta.get("tokenizer.ggml.eos_token_id")
+    if eos is not None and 0 <= eos < vocab:
+        cfg["eos_token_id"] = eos
+    return cfg
+
+
+_GGUF_LAYER = {
+    "input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "ffn_norm.weight",
+    "self_attn.q_proj.weight": "attn_q.weight", "self_attn.k_proj.weight": "attn_k.weight",
+    "self_attn.v_proj.weight": "attn_v.weight", "self_attn.o_proj.weight": "attn_output.weight",
+    "self_attn.q_norm.weight": "attn_q_norm.weight", "self_attn.k_norm.weight": "attn_k_norm.weight",
+    "mlp.gate_proj.weight": "ffn_gate.weight", "mlp.up_proj.weight": "ffn_up.weight",
+    "mlp.down_proj.weight": "ffn_down.weight",
+}
+_GGUF_GLOBAL = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+                "lm_head.weight": "output.weight"}
+
+
+def gguf_tensor_name(name: str) -> str:
+    """GGUF name of a checkpoint tensor (names as the reference loads them, src/model.cpp:120-149)."""
+    if name in _GGUF_GLOBAL:
+        return _GGUF_GLOBAL[name]
+    parts = name.split(".", 3)                       # model.layers.<i>.<rest>
+    if len(parts) == 4 and parts[:2] == ["model", "layers"] and parts[3] in _GGUF_LAYER:
+        return f"blk.{parts[2]}.{_GGUF_LAYER[parts[3]]}"
+    raise KeyError(name)
+
+
+def gguf_metadata(cfg: Qwen3Config) -> dict[str, Any]:
+    """The GGUF metadata that reads back as ``cfg`` (windowed layers have no GGUF keys here)."""
+    if cfg.sliding_window is not None:
+        raise ConfigError("windowed layers cannot be written to GGUF metadata")
+    meta = {
+        "general.architecture": "qwen3", "qwen3.block_count": cfg.num_hidden_layers,
+        "qwen3.embedding_length": cfg.hidden_size, "qwen3.feed_forward_length": cfg.intermediate_size,
+        "qwen3.attention.head_count": cfg.num_attention_heads,
+        "qwen3.attention.head_count_kv": cfg.num_key_value_heads,
+        "qwen3.attention.key_length": cfg.head_dim, "qwen3.vocab_size": cfg.vocab_size,
+        "qwen3.rope.freq_base": float(cfg.rope_theta),
+        "qwen3.attention.layer_norm_rms_epsilon": float(cfg.rms_norm_eps),
+        "qwen3.context_length": cfg.max_position_embeddings,
+    }
+    if cfg.eos_token_ids:
+        meta["tokenizer.ggml.eos_token_id"] = cfg.eos_token_ids[0]
+    return meta
+
+
 register_architecture(Architecture(
     name=Qwen3Config.ARCHITECTURE, from_dict=Qwen3Config.from_dict, build_plan=build_plan,
-    aliases=("qwen3",)))
+    aliases=("qwen3",), config_from_gguf=config_from_gguf, gguf_tensor_name=gguf_tensor_name))

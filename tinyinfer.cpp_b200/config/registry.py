@@ -24,6 +24,10 @@ class Architecture:
     from_dict: Callable[[Mapping[str, Any]], Any]      # config.json dict -> typed configuration
     build_plan: Callable[[Any], ModelPlan]             # typed configuration -> plan
     aliases: tuple[str, ...] = ()
+    # GGUF support, if the architecture has it: metadata (and tensor shapes) -> config.json
+    # dictionary, and the GGUF name of a checkpoint tensor name
+    config_from_gguf: Any = None
+    gguf_tensor_name: Any = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

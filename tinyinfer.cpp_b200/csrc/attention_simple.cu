@@ -118,70 +118,80 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
         sincosf((float)pos * inv_freq[k], &sn_tab[k], &cs_tab[k]);
     pdl_wait();
     __syncthreads();
-    // with many tokens a warp takes several vectors in turn, so that blocks are not tiny
-    for (int turn = 0; turn < items_per_warp; ++turn) {
-    const int item = (blockIdx.y * items_per_warp + turn) * WARPS + warp;
-    if (item >= num_heads + 2 * num_kv_heads) return;
-    int kind, head;
-    if (item < num_heads) { kind = 0; head = item; }
-    else if (item < num_heads + num_kv_heads) { kind = 1; head = item - num_heads; }
-    else { kind = 2; head = item - num_heads - num_kv_heads; }
-    if (kind != 0 && !write_kv) continue;
-    const float* src = qkv + (size_t)t * qkv_stride +
-                       (kind == 0 ? head * head_dim : kind == 1 ? nq + head * head_dim
-                                                                : nq + nk + head * head_dim);
-    TC* dst = nullptr;
-    if (kind != 0) {
-        const int r = req_of_tok[t];
-        const int page = block_table[(size_t)r * bt_stride + pos / page_size];
-        if (page < 0 || page >= num_pages) {
-            if (lane == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
-            continue;
-        }
-        dst = pages + ((((size_t)page * 2 + (kind - 1)) * num_kv_heads + head) * page_size +
-                       pos % page_size) * head_dim;
-    }
+    // With many tokens a warp takes up to MAX_TURNS vectors, so that blocks are not tiny; all of
+    // their loads are issued before any of them is used.
+    constexpr int MAX_TURNS = 8;
+    const int items = num_heads + 2 * num_kv_heads;
     const int k0 = lane * VEC;
     const bool active = k0 < half;
-    float lo[VEC], hi[VEC];
+    float lo[MAX_TURNS][VEC], hi[MAX_TURNS][VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        lo[i] = active ? src[k0 + i] : 0.0f;
-        hi[i] = active ? src[half + k0 + i] : 0.0f;
+    for (int turn = 0; turn < MAX_TURNS; ++turn) {
+        const int item = (blockIdx.y * items_per_warp + turn) * WARPS + warp;
+        const bool live = turn < items_per_warp && item < items && active;
+        const float* src = qkv + (size_t)t * qkv_stride + (size_t)(live ? item : 0) * head_dim;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            lo[turn][i] = live ? src[k0 + i] : 0.0f;
+            hi[turn][i] = live ? src[half + k0 + i] : 0.0f;
+        }
     }
-    if (kind == 2) {
-        if (active) {
+    int page = -1;
+    if (write_kv) {
+        page = block_table[(size_t)req_of_tok[t] * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+            page = -1;
+        }
+    }
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                dst[k0 + i] = from_f32<TC>(lo[i]);
-                dst[half + k0 + i] = from_f32<TC>(hi[i]);
+    for (int turn = 0; turn < MAX_TURNS; ++turn) {
+        const int item = (blockIdx.y * items_per_warp + turn) * WARPS + warp;
+        if (turn >= items_per_warp || item >= items) break;
+        // the vectors of a token lie one after the other: query heads, key heads, value heads
+        const int kind = item < num_heads ? 0 : item < num_heads + num_kv_heads ? 1 : 2;
+        const int head = kind == 0 ? item : kind == 1 ? item - num_heads : item - num_heads - num_kv_heads;
+        if (kind != 0 && page < 0) continue;
+        TC* dst = nullptr;
+        if (kind != 0)
+            dst = pages + ((((size_t)page * 2 + (kind - 1)) * num_kv_heads + head) * page_size +
+                           pos % page_size) * head_dim;
+        if (kind == 2) {
+            if (active) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    dst[k0 + i] = from_f32<TC>(lo[turn][i]);
+                    dst[half + k0 + i] = from_f32<TC>(hi[turn][i]);
+                }
+            }
+            continue;
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            ss = fmaf(lo[turn][i], lo[turn][i], ss);
+            ss = fmaf(hi[turn][i], hi[turn][i], ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+        if (!active) continue;
+        const float* w = kind == 0 ? q_weight : k_weight;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const float x0 = lo[turn][i] * inv * w[k0 + i];
+            const float x1 = hi[turn][i] * inv * w[half + k0 + i];
+            const float sn = sn_tab[k0 + i], cs = cs_tab[k0 + i];
+            const float y0 = x0 * cs - x1 * sn;
+            const float y1 = x0 * sn + x1 * cs;
+            if (kind == 0) {
+                TQ* q = q_out + (size_t)t * nq + head * head_dim;
+                q[k0 + i] = from_f32<TQ>(y0);
+                q[half + k0 + i] = from_f32<TQ>(y1);
+            } else {
+                dst[k0 + i] = from_f32<TC>(y0);
+                dst[half + k0 + i] = from_f32<TC>(y1);
             }
         }
-        continue;
-    }
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) { ss = fmaf(lo[i], lo[i], ss); ss = fmaf(hi[i], hi[i], ss); }
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
-    if (!active) continue;
-    const float* w = kind == 0 ? q_weight : k_weight;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        const float x0 = lo[i] * inv * w[k0 + i];
-        const float x1 = hi[i] * inv * w[half + k0 + i];
-        const float sn = sn_tab[k0 + i], cs = cs_tab[k0 + i];
-        const float y0 = x0 * cs - x1 * sn;
-        const float y1 = x0 * sn + x1 * cs;
-        if (kind == 0) {
-            TQ* q = q_out + (size_t)t * nq + head * head_dim;
-            q[k0 + i] = from_f32<TQ>(y0);
-            q[half + k0 + i] = from_f32<TQ>(y1);
-        } else {
-            dst[k0 + i] = from_f32<TC>(y0);
-            dst[half + k0 + i] = from_f32<TC>(y1);
-        }
-    }
     }
 }
 
@@ -290,7 +300,8 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
     dim3 grid(num_tokens, (items + WARPS - 1) / WARPS);
     cudaStream_t s = (cudaStream_t)stream;
     const int half = head_dim / 2;
-    const int ipw = num_tokens >= 512 ? (items + WARPS - 1) / WARPS : 1;      // items per warp
+    int ipw = num_tokens >= 512 ? (items + WARPS - 1) / WARPS : 1;            // vectors per warp
+    if (ipw > 8) ipw = 8;
     dim3 vgrid(num_tokens, (items + WARPS * ipw - 1) / (WARPS * ipw));
     const int vec = (half % 4 == 0 && half > 64) ? 4 : (half % 2 == 0 && half <= 64) ? 2 : 0;
 #define CALL(TQ, TC)                                                                          \

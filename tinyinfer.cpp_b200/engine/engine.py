@@ -8,6 +8,7 @@ this call.  The reference's counterpart is ``Inference::forward``
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Hashable, Mapping, Optional, Sequence
 
 import torch
@@ -15,7 +16,7 @@ import torch
 from ..cache import CacheManager, OutOfPages
 from ..config.registry import architecture_of, load_config
 from ..parts.model import CausalLM
-from ..weights.loader import load_model_weights
+from ..weights.loader import load_gguf, load_model_weights, load_model_weights_gguf
 from ..weights.random_init import random_tensor
 from .batch import StepBatch, StepEntry, build_step_batch
 
@@ -37,7 +38,7 @@ def parse_dtype(dtype) -> torch.dtype:
 class Engine:
     """A loaded model with its cache.
 
-    model_dir    folder with ``config.json`` and ``model.safetensors``; or
+    model_dir    folder with ``config.json`` and ``model.safetensors``, or a ``.gguf`` file; or
     config+seed  a ``config.json`` dictionary and a seed: random weights made on the device.
     dtype        ``bfloat16``: the kernels and precisions of serving (bfloat16 activations and
                  cache, float32 residual stream, norms, softmax); ``float32``: everything in
@@ -57,7 +58,12 @@ class Engine:
             from ..kernels import cuda_ops
             ops = cuda_ops(self.device)
         self.ops = ops
-        if model_dir is not None:
+        gguf_file = None
+        if model_dir is not None and os.path.isfile(model_dir):
+            # a file instead of a folder: a GGUF model (the reference's own format)
+            gguf_file, arch, gguf_cfg = load_gguf(model_dir)
+            typed = arch.from_dict(gguf_cfg)
+        elif model_dir is not None:
             arch, typed = load_config(model_dir)
         elif config is not None:
             arch = architecture_of(config)
@@ -67,7 +73,12 @@ class Engine:
         self.config = typed
         self.plan = arch.build_plan(typed)
         self.model = CausalLM(self.plan)
-        if model_dir is not None:
+        if gguf_file is not None:
+            try:
+                load_model_weights_gguf(self.model, gguf_file, arch, self.device, ops)
+            finally:
+                gguf_file.close()
+        elif model_dir is not None:
             load_model_weights(self.model, model_dir, self.device, ops)
         else:
             if seed is None:

@@ -71,5 +71,34 @@ def load_model_weights(model, model_dir: str, device, ops) -> None:
             f.close()
 
 
-__all__ = ["SafetensorsError", "WeightsError", "check_tensors", "load_model_weights",
+def load_gguf(path: str):
+    """Open a GGUF file; returns ``(file, architecture, config.json dictionary)``."""
+    from ..config.registry import ConfigError, get_architecture
+    from .gguf import GgufFile
+    f = GgufFile(path)
+    name = f.metadata.get("general.architecture")
+    if not isinstance(name, str):
+        raise ConfigError(f"{path}: GGUF metadata lacks 'general.architecture'")
+    arch = get_architecture(name)
+    if arch.config_from_gguf is None:
+        raise ConfigError(f"architecture {name!r} has no GGUF support")
+    cfg = arch.config_from_gguf(f.metadata, {n: f.shape(n) for n in f.names()})
+    return f, arch, cfg
+
+
+def load_model_weights_gguf(model, gguf_file, arch, device, ops) -> None:
+    """As ``load_model_weights``, from an open GGUF file; names in errors are the file's own."""
+    expected = model.expected_tensors()
+    to_gguf = {name: arch.gguf_tensor_name(name) for name in expected}
+    check_tensors(gguf_file.path, {to_gguf[n]: spec for n, spec in expected.items()},
+                  {n: gguf_file.shape(n) for n in gguf_file.names()})
+
+    def fetch(name: str) -> torch.Tensor:
+        t = gguf_file.get(to_gguf[name])
+        return t.to(device=device, dtype=storage_dtype(t.dtype), copy=True)
+
+    model.load_weights(fetch, ops)
+
+
+__all__ = ["SafetensorsError", "load_gguf", "load_model_weights_gguf", "WeightsError", "check_tensors", "load_model_weights",
            "storage_dtype"]
