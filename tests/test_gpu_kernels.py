@@ -249,9 +249,10 @@ def test_qk_norm_rope_store(ops, dtype, geom):
     ops.check_status()
 
 
-def test_argmax_first_maximum_wins(ops):
-    logits = _rand((5, 151936))
-    logits[1, 77] = logits[1, 150000] = 50.0
+@pytest.mark.parametrize("vocab", [151936, 1009, 16384])
+def test_argmax_first_maximum_wins(ops, vocab):
+    logits = _rand((5, vocab))
+    logits[1, 77] = logits[1, vocab - 9] = 50.0
     logits[2, :] = 0.0
     out = torch.empty(5, dtype=torch.int32, device=DEV)
     ops.argmax(logits, out)

@@ -19,6 +19,7 @@ namespace {
 
 constexpr int TILE = 32;       // keys per tile
 constexpr int STAGES = 3;
+constexpr int MAX_SPLITS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -48,6 +49,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {           // 2^x, 2 ulp, 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -55,29 +61,52 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // out[:] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s, by one warp, over the splits
 // in ascending order.  Loads go to L2: other blocks of the same launch wrote the partial results.
+// First the weights of all splits (lanes in parallel, kept in `wbuf`, MAX_SPLITS floats of shared
+// memory), then the weighted sum with several loads in flight.
 __device__ __forceinline__ void merge_head(const float* part_o, const float* part_ml, size_t base,
-                                           int num_splits, int head_dim, bf16* out, int lane) {
+                                           int num_splits, int head_dim, bf16* out, int lane,
+                                           float* wbuf) {
     float mmax = -INFINITY;
     for (int s = lane; s < num_splits; s += 32) mmax = fmaxf(mmax, __ldcg(part_ml + (base + s) * 2));
     mmax = warp_max(mmax);
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane*4 .. lane*4 + 3
     float total = 0.0f;
-    const int d0 = lane * 4;
-    for (int s = 0; s < num_splits; ++s) {
+    for (int s = lane; s < num_splits; s += 32) {
         const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2));
-        if (ml.x == -INFINITY) continue;
-        const float wgt = exp2f(ml.x - mmax);
-        total += ml.y * wgt;
-        if (d0 < head_dim) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * head_dim + d0));
-            acc[0] += v.x * wgt; acc[1] += v.y * wgt; acc[2] += v.z * wgt; acc[3] += v.w * wgt;
-        }
+        const float wgt = ml.x == -INFINITY ? 0.0f : exp2f(ml.x - mmax);
+        wbuf[s] = wgt;
+        total += ml.y * wgt;                                  // lanes hold disjoint splits
     }
+    // a fixed order of the additions: lane partial sums, then the shuffle tree
+    total = warp_sum(total);
+    __syncwarp();
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane*4 .. lane*4 + 3
+    const int d0 = lane * 4;
     if (d0 < head_dim) {
+        const float* src = part_o + base * head_dim + d0;
+        int s = 0;
+        for (; s + 4 <= num_splits; s += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s + u) * head_dim));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float wgt = wbuf[s + u];
+                acc[0] = fmaf(v[u].x, wgt, acc[0]); acc[1] = fmaf(v[u].y, wgt, acc[1]);
+                acc[2] = fmaf(v[u].z, wgt, acc[2]); acc[3] = fmaf(v[u].w, wgt, acc[3]);
+            }
+        }
+        for (; s < num_splits; ++s) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * head_dim));
+            const float wgt = wbuf[s];
+            acc[0] = fmaf(v.x, wgt, acc[0]); acc[1] = fmaf(v.y, wgt, acc[1]);
+            acc[2] = fmaf(v.z, wgt, acc[2]); acc[3] = fmaf(v.w, wgt, acc[3]);
+        }
         const float inv = 1.0f / total;
         *reinterpret_cast<__nv_bfloat162*>(out + d0) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
         *reinterpret_cast<__nv_bfloat162*>(out + d0 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
     }
+    __syncwarp();                                             // wbuf may be reused for the next head
 }
 
 template <int HD>
@@ -234,7 +263,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                alpha[r] = m_new == -INFINITY ? 1.0f : exp2f(m_run[r] - m_new);
+                alpha[r] = m_new == -INFINITY ? 1.0f : fast_exp2(m_run[r] - m_new);
                 m_run[r] = m_new;
             }
             // a tile always holds at least one visible key, so the running maxima are finite
@@ -243,7 +272,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
             for (int j = 0; j < 4; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p = exp2f(s_acc[j][e] - m_run[e >> 1]);
+                    const float p = fast_exp2(s_acc[j][e] - m_run[e >> 1]);
                     s_acc[j][e] = p;
                     sum[e >> 1] += p;
                 }
@@ -317,7 +346,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
     for (int r = 0; r < group; ++r) {
         const int h = kvh * group + r;
         merge_head(part_o, part_ml, ((size_t)row * num_heads + h) * num_splits, num_splits, HD,
-                   out + ((size_t)t * num_heads + h) * HD, lane);
+                   out + ((size_t)t * num_heads + h) * HD, lane, reinterpret_cast<float*>(smem));
     }
 }
 
@@ -326,13 +355,14 @@ __global__ void __launch_bounds__(128)
 attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          const int* __restrict__ rows, int num_rows, int num_heads, int num_splits,
                          int head_dim, bf16* __restrict__ out) {
+    __shared__ float wbuf[4][MAX_SPLITS];
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (item >= num_rows * num_heads) return;
     const int row = item / num_heads, h = item % num_heads;
     const int t = rows ? rows[row] : row;
     merge_head(part_o, part_ml, (size_t)item * num_splits, num_splits, head_dim,
-               out + ((size_t)t * num_heads + h) * head_dim, lane);
+               out + ((size_t)t * num_heads + h) * head_dim, lane, wbuf[threadIdx.x >> 5]);
 }
 
 template <int HD>
@@ -361,6 +391,13 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
 }
 
 }  // namespace
+
+// How many of the kernel's one-warp blocks fit on an SM (by shared memory), for sizing the grid.
+extern "C" int ti_attn_decode_blocks_per_sm(int head_dim) {
+    const int smem = STAGES * 2 * TILE * (head_dim * 2 + 16) + 1024;
+    const int fit = (227 * 1024) / smem;
+    return fit > 16 ? 16 : fit;
+}
 
 // 1 if (head_dim, heads per kv head, page_size) can run on this kernel, else 0.
 extern "C" int ti_attn_decode_supported(int head_dim, int group, int page_size) {
@@ -405,8 +442,8 @@ extern "C" int ti_attn_decode_fused(const void* q, const int* rows, int num_rows
                "attn_decode: head_dim %d (multiple of 16 up to 128), %d heads per kv head (up to 16) "
                "or page size %d (multiple of 16) is not supported",
                head_dim, num_heads / num_kv_heads, page_size);
-    TI_REQUIRE(num_splits >= 1 && num_rows <= 65535 && num_kv_heads <= 65535,
-               "attn_decode: grid out of range");
+    TI_REQUIRE(num_splits >= 1 && num_splits <= MAX_SPLITS && num_rows <= 65535 && num_kv_heads <= 65535,
+               "attn_decode: grid out of range (at most %d splits)", MAX_SPLITS);
 #define CASE(HD)                                                                                   \
     case HD:                                                                                       \
         return launch_decode<HD>((const bf16*)q, rows, num_rows, positions, req_of_tok,            \

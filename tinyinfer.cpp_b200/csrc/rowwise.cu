@@ -123,7 +123,73 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* 
     }
 }
 
+// Argmax in two steps for wide rows: blocks take slices of a row and leave their best (value,
+// index); one more small launch picks among the slices.  Ties still go to the lowest index.
+constexpr int ARGMAX_SLICES = 64;
+
+__global__ void __launch_bounds__(256)
+argmax_slice_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ part_v,
+                    int* __restrict__ part_i) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const int per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int lo = slice * per, hi = min(vocab, lo + per);
+    const float* x = logits + (size_t)row * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += 256) keep_best(x[i], i, bv, bi);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        keep_best(ov, oi, bv, bi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) keep_best(sv[w], si[w], bv, bi);
+        part_v[row * ARGMAX_SLICES + slice] = bv;
+        part_i[row * ARGMAX_SLICES + slice] = bi;
+    }
+}
+
+__global__ void __launch_bounds__(ARGMAX_SLICES)
+argmax_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                   int* __restrict__ out) {
+    __shared__ float sv[2];
+    __shared__ int si[2];
+    const int row = blockIdx.x;
+    float bv = part_v[row * ARGMAX_SLICES + threadIdx.x];
+    int bi = part_i[row * ARGMAX_SLICES + threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        keep_best(ov, oi, bv, bi);
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        keep_best(sv[1], si[1], bv, bi);
+        out[row] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
 }  // namespace
+
+// Scratch for the two-step argmax: rows * 64 floats and rows * 64 ints.
+extern "C" int ti_argmax_sliced(const float* logits, int rows, int vocab, float* part_v, int* part_i,
+                                int* out, void* stream) {
+    if (rows == 0) return 0;
+    TI_REQUIRE(vocab > 0 && rows <= 65535, "argmax: %d rows of %d", rows, vocab);
+    cudaStream_t s = (cudaStream_t)stream;
+    argmax_slice_kernel<<<dim3(ARGMAX_SLICES, rows), 256, 0, s>>>(logits, vocab, part_v, part_i);
+    if (int rc = ti_check_launch("argmax")) return rc;
+    argmax_pick_kernel<<<rows, ARGMAX_SLICES, 0, s>>>(part_v, part_i, out);
+    return ti_check_launch("argmax");
+}
 
 extern "C" int ti_embed(const void* table, int table_dtype, const int* tokens, int num_tokens,
                         int hidden, float* out, void* stream) {

@@ -88,6 +88,7 @@ class CudaOps:
         c.ti_rmsnorm.argtypes = [_vp, _vp, _vp, _i, _i, _f, _vp, _i, _vp]
         c.ti_swiglu.argtypes = [_vp, _i, _i, _i, _vp, _i, _vp]
         c.ti_argmax.argtypes = [_vp, _i, _i, _vp, _vp]
+        c.ti_argmax_sliced.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _vp]
         c.ti_gemm_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]
         c.ti_qk_norm_rope_store.argtypes = [
             _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
@@ -107,6 +108,7 @@ class CudaOps:
                                               _f, _vp, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
             b.ti_attn_decode_supported.argtypes = [_i, _i, _i]
+            b.ti_attn_decode_blocks_per_sm.argtypes = [_i]
             b.ti_attn_decode_fused.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i,
                                                _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
             b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
@@ -277,16 +279,16 @@ class CudaOps:
             cache.page_size, int(bool(cache.writes)), t, num_heads, num_kv_heads, head_dim,
             q_out.data_ptr(), _code(q_out, "q"), self.status.data_ptr(), self._stream()))
 
-    def decode_splits(self, rows: int, num_kv_heads: int, max_position: int) -> int:
+    def decode_splits(self, rows: int, num_kv_heads: int, max_position: int, head_dim: int = 128) -> int:
         """In how many blocks the keys of a decoding row are cut, per kv head.  It depends on
         the padded batch size and on the model's longest context only, so that a step cuts
         the same way whether it runs eagerly or from a graph."""
         bucket = 1
         while bucket < rows:
             bucket *= 2
-        # one-warp blocks, four resident per SM: fill the GPU once, never one block more
-        want = (4 * self.num_sms) // (bucket * num_kv_heads)
-        return max(1, min(want, -(-max_position // 64)))
+        # one-warp blocks, as many per SM as shared memory allows: fill the GPU once, never more
+        want = (self.bf16.ti_attn_decode_blocks_per_sm(head_dim) * self.num_sms) // (bucket * num_kv_heads)
+        return max(1, min(want, -(-max_position // 64), 256))
 
     def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,
                         scale):
@@ -301,7 +303,7 @@ class CudaOps:
         if (n_dec and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and
                 self.bf16.ti_attn_decode_supported(head_dim, num_heads // num_kv_heads,
                                                    cache.page_size)):
-            splits = self.decode_splits(n_dec, num_kv_heads, step.max_position or step.max_ctx_len)
+            splits = self.decode_splits(n_dec, num_kv_heads, step.max_position or step.max_ctx_len, head_dim)
             part_o = torch.empty((n_dec, num_heads, splits, head_dim), dtype=torch.float32,
                                  device=q.device)
             part_ml = torch.empty((n_dec, num_heads, splits, 2), dtype=torch.float32,
@@ -353,8 +355,14 @@ class CudaOps:
     def argmax(self, logits, out):
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "argmax: float32 logits")
         _need(out.dtype == torch.int32 and out.shape[0] == logits.shape[0], "argmax: int32 out")
-        self._ok(self.core.ti_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1],
-                                     out.data_ptr(), self._stream()))
+        rows, vocab = logits.shape
+        if vocab >= 16384:                 # wide rows: many blocks per row, then one pick
+            part_v = torch.empty((rows, 64), dtype=torch.float32, device=logits.device)
+            part_i = torch.empty((rows, 64), dtype=torch.int32, device=logits.device)
+            self._ok(self.core.ti_argmax_sliced(logits.data_ptr(), rows, vocab, part_v.data_ptr(),
+                                                part_i.data_ptr(), out.data_ptr(), self._stream()))
+            return
+        self._ok(self.core.ti_argmax(logits.data_ptr(), rows, vocab, out.data_ptr(), self._stream()))
 
     def sample(self, logits, temperature, top_k, top_p, uniform, out):
         rows = logits.shape[0]
