@@ -225,6 +225,54 @@ def measure_prefill(engine, tokens, reps, torch):
     return statistics.median(times)
 
 
+def measure_chains(engine, batch, torch):
+    """Each decode product alone: a CUDA graph of 56 dependent launches with distinct weights,
+    timed with CUDA events; microseconds per launch."""
+    ops, dev, bf = engine.ops, engine.device, torch.bfloat16
+    cfg = engine.config
+    h, inter = cfg.hidden_size, cfg.intermediate_size
+    nq = cfg.num_attention_heads * cfg.head_dim
+    nqkv = nq + 2 * cfg.num_key_value_heads * cfg.head_dim
+
+    def rnd(*shape):
+        return torch.randn(*shape, device=dev).to(bf)
+
+    x, xb, o, y = torch.randn(batch, h, device=dev), rnd(batch, h), rnd(batch, nq), rnd(batch, inter)
+    qkv = torch.empty(batch, nqkv, device=dev)
+    yo = torch.empty(batch, inter, device=dev, dtype=bf)
+    xn = torch.empty(batch, h, device=dev, dtype=bf)
+    norm_w = torch.ones(h, device=dev)
+    n = 56
+    wq, wo = [rnd(nqkv, h) for _ in range(n)], [rnd(h, nq) for _ in range(n)]
+    wg = [ops.pack_gate_up(rnd(inter, h), rnd(inter, h)) for _ in range(n)]
+    wd = [rnd(h, inter) for _ in range(n)]
+    cases = {
+        "qkv": lambda: [ops.linear(xb, w, qkv) for w in wq],
+        "o_accumulate": lambda: [ops.linear(o, w, x, accumulate=True) for w in wo],
+        "gate_up_swiglu": lambda: [ops.gate_up_swiglu(xb, w, yo) for w in wg],
+        "down_accumulate": lambda: [ops.linear(y, w, x, accumulate=True) for w in wd],
+        "rmsnorm": lambda: [ops.rmsnorm(x, norm_w, 1e-6, xn) for _ in range(n)],
+    }
+    out = {}
+    for name, fn in cases.items():
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        for _ in range(3):
+            graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(20):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        out[name] = round(start.elapsed_time(stop) / 20 / n * 1e3, 2)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -235,7 +283,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "chains"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
 
@@ -268,6 +316,10 @@ def main() -> int:
         (ms, _, launches), _ = measure_decode(engine, args.batch, args.context, args.steps, warmup, torch)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context,
                           "ms_per_step": round(ms, 4), "gpu_launches": launches}))
+        return 0
+    if args.only == "chains":
+        print(json.dumps({"only": "chains", "batch": args.batch, "us_per_launch":
+                          measure_chains(engine, args.batch, torch)}))
         return 0
     if args.only == "prefill":
         pf_ms = measure_prefill(engine, 2048, max(1, args.steps), torch)
