@@ -89,6 +89,34 @@ def test_graph_replay_equals_eager_bit_for_bit(tmp_path_factory, dtype):
     assert torch.equal(results[0], results[1]), "graph replay and eager steps differ"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_step_graphs_equal_eager_bit_for_bit(tmp_path_factory, dtype):
+    """Steps of a shape seen before are replayed from CUDA graphs: prompt portions of the same
+    sizes for different requests at different positions, and mixed steps, give the same bits."""
+    from tinyinfer_b200 import StepEntry
+    d = make_model(tmp_path_factory.getbasetemp(), "D")
+    vocab = TINY["D"]["vocab_size"]
+    toks = {r: random_tokens(vocab, 400, seed=i) for i, r in enumerate("abcd")}
+    results = []
+    for graphs in (False, True):
+        eng = _engine(d, dtype, max_tokens=2048, step_graphs=graphs)
+        out = []
+        done = {r: 0 for r in toks}
+        def portion(r, n, want):
+            e = StepEntry(r, toks[r][done[r]:done[r] + n], want)
+            done[r] += n
+            return e
+        for rnd in range(4):
+            for r in "abcd":                                   # the same shape 16 times
+                out.append(eng.step([portion(r, 70, [0, 69])]).clone())
+            out.append(eng.step([portion("a", 1, [0]), portion("b", 20, [19]), portion("c", 2, [1])]).clone())
+        if graphs:
+            assert len(eng._step_graphs.graphs) == 2 and eng.ops.launches > 0
+        results.append(torch.cat(out))
+        eng.ops.check_status()
+    assert torch.equal(results[0], results[1]), "replayed steps differ from eager steps"
+
+
 @pytest.mark.parametrize("graph", [False, True])
 def test_greedy_generation_through_the_entry_point(tmp_path_factory, graph):
     from tinyinfer_b200 import LLM, SamplingParams

@@ -117,6 +117,37 @@ def test_linear_many_rows_bf16(ops, m, nk):
         assert torch.equal(part, full[m - 70:])
 
 
+@pytest.mark.parametrize("shape", [(2048, 4096, 1024), (1100, 5000, 520), (2048, 6144, 136), (4096, 2560, 64)])
+def test_linear_on_pairs_of_sms(ops, shape):
+    """Outputs with many 256 x 256 tiles run on pairs of SMs (tcgen05 cta_group::2): same bits as
+    the one-SM kernel, right against float64."""
+    m, n, k = shape
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1)
+    base = _rand((m, n), seed=2)
+    assert ops._tc_gemm(m, n) is ops.bf16.ti_gemm_tcgen05_2sm
+    for acc in (False, True):
+        out = base.clone()
+        ops.linear(a, w, out, accumulate=acc)
+        ops.check_status()
+        ops.use_2sm_gemm = False
+        try:
+            one = base.clone()
+            ops.linear(a, w, one, accumulate=acc)
+        finally:
+            ops.use_2sm_gemm = True
+        assert torch.equal(out, one), "pair kernel and one-SM kernel differ"
+        _close(out, a.double() @ w.double().T + (base.double() if acc else 0), _sum_rtol(k),
+               f"pairs {shape} acc={acc}")
+    gate, up = _rand((n // 2, k), torch.bfloat16, seed=3, scale=0.2), _rand((n // 2, k), torch.bfloat16, seed=4, scale=0.2)
+    y = torch.empty((m, n // 2), dtype=torch.bfloat16, device=DEV)
+    ref = torch.empty_like(y)
+    ops.gate_up_swiglu(a, ops.pack_gate_up(gate, up), y)
+    r = RefOps()
+    r.gate_up_swiglu(a, r.pack_gate_up(gate, up), ref)
+    _close(y, ref, 8e-3, f"pairs swiglu {shape}")
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [1, 8, 40, 64, 100])
 @pytest.mark.parametrize("hk", [(128, 320), (1024, 3072), (80, 176), (64, 24)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

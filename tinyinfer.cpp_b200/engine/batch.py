@@ -10,7 +10,7 @@ sequence (src/main.cpp:211-219,269-274).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, Sequence
+from typing import Hashable, Optional, Sequence
 
 import numpy as np
 import torch
@@ -55,6 +55,7 @@ class StepBatch:
     chunk_tiles: torch.Tensor        # [n, 3] {request row, first flat token, rows} in tiles of 64
     chunk_tiles_big: torch.Tensor    # the same in tiles of 128
     max_position: int = 0            # the model's longest context (bounds that do not vary by step)
+    packed_size: int = 0             # int32 values in the packed device buffer
     block_tables: list[torch.Tensor] = field(default_factory=list)   # per group [R, blocks]
     scratch: dict = field(default_factory=dict)   # per-step values kernels may cache
 
@@ -62,9 +63,14 @@ class StepBatch:
 def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
                      tables: Sequence[Sequence[Sequence[int]]], slots: Sequence[int],
                      act_dtype: torch.dtype, device, min_blocks: int = 1,
-                     max_position: int = 0) -> StepBatch:
+                     max_position: int = 0, dev_buffer: Optional[torch.Tensor] = None) -> StepBatch:
     """Pack one step.  ``starts[r]`` is the position of entry r's first token,
-    ``tables[g][r]`` its block table in group g (already covering the new tokens)."""
+    ``tables[g][r]`` its block table in group g (already covering the new tokens).
+
+    The packed layout depends only on the entries' token counts and wanted places once
+    ``min_blocks`` fixes the block tables' width.  ``dev_buffer`` (int32, at least
+    ``packed_size`` long) receives the integers instead of a fresh device tensor, so that a
+    captured graph finds a later step of the same shape at the same addresses."""
     q_lens = [len(e.tokens) for e in entries]
     r = len(entries)
     t = sum(q_lens)
@@ -124,7 +130,11 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         for i, tb in enumerate(grp):
             arr[i, :len(tb)] = tb
         bt_spans.append((put(arr.reshape(-1), r * w), w))
-    dev = host.to(device, non_blocking=True)
+    if dev_buffer is None:
+        dev = host.to(device, non_blocking=True)
+    else:
+        dev = dev_buffer[:host.shape[0]]
+        dev.copy_(host, non_blocking=True)
 
     def view(name):
         a, b = spans[name]
@@ -138,5 +148,5 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
         state_slots=view("slots"), decode_rows=view("dec"), chunk_rows=view("chk"),
         chunk_tiles=view("tiles").view(-1, 3), chunk_tiles_big=view("tiles_big").view(-1, 3),
-        max_position=max_position,
+        max_position=max_position, packed_size=host.shape[0],
         block_tables=[dev[a:b].view(r, w) for (a, b), w in bt_spans])

@@ -46,12 +46,15 @@ class Engine:
     max_tokens   how many tokens the cache holds over all live requests (each request's
                  count rounded up to whole pages); or ``num_pages`` directly.
     ops          the kernel set; by default the CUDA kernels, which must be available.
+    step_graphs  replay steps of a shape seen before from CUDA graphs (``step`` then returns a
+                 logits tensor that the next step of the same shape reuses).
     """
 
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[Mapping[str, Any]] = None,
                  seed: Optional[int] = None, dtype="bfloat16", device="cuda:0",
                  page_size: int = 16, max_tokens: Optional[int] = None,
-                 num_pages: Optional[int] = None, max_requests: int = 64, ops=None):
+                 num_pages: Optional[int] = None, max_requests: int = 64, ops=None,
+                 step_graphs: bool = False):
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         if ops is None:
@@ -97,6 +100,10 @@ class Engine:
                                   kv_dtype=self.dtype, device=self.device)
         self.last_batch: Optional[StepBatch] = None
         self._graphs = None
+        self._step_graphs = None
+        if step_graphs:
+            from .graphs import StepGraphs
+            self._step_graphs = StepGraphs(self)
 
     # ---- requests ------------------------------------------------------------------------
     def add_request(self, req_id: Hashable) -> None:
@@ -133,12 +140,16 @@ class Engine:
         tables = [[self.cache.block_table(g, e.req_id) for e in entries]
                   for g in range(len(self.cache.groups))]
         slots = [self.cache.state_slot(e.req_id) for e in entries]
-        batch = build_step_batch(entries, starts, tables, slots, self.dtype, self.device,
-                                 max_position=self.plan.max_position)
-        logits = self.forward(batch)
+        logits = None
+        if self._step_graphs is not None:
+            logits = self._step_graphs.run(entries, starts, tables, slots)
+        if logits is None:
+            batch = build_step_batch(entries, starts, tables, slots, self.dtype, self.device,
+                                     max_position=self.plan.max_position)
+            logits = self.forward(batch)
+            self.last_batch = batch
         for e in entries:
             self.cache.release_passed(e.req_id)
-        self.last_batch = batch
         return logits
 
     def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:

@@ -52,7 +52,7 @@ class LLM:
             kv_tokens = max_num_seqs * max_seq
         self.engine = Engine(model_dir, config=config, seed=seed, dtype=dtype, device=device,
                              page_size=page_size, num_pages=-(-kv_tokens // page_size),
-                             max_requests=max_num_seqs, ops=ops)
+                             max_requests=max_num_seqs, ops=ops, step_graphs=cuda_graph)
         self.max_seq = min(max_seq, self.engine.plan.max_position)
         self.max_num_seqs = max_num_seqs
         self.max_batched_tokens = max_batched_tokens

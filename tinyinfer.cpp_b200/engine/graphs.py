@@ -17,7 +17,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
-from .batch import StepBatch, StepEntry
+from .batch import StepBatch, StepEntry, build_step_batch
 
 
 def bucket_of(n: int) -> int:
@@ -120,3 +120,56 @@ class DecodeGraphs:
         if hasattr(eng.ops, "launches"):
             eng.ops.launches += bk.launches
         return bk.logits[:len(entries)]
+
+
+class StepGraphs:
+    """CUDA-graph replay of whole steps of any shape (prompt portions, mixed batches).
+
+    A step's launches depend only on its entries' token counts and wanted places: positions,
+    block tables and everything else are data in one packed device buffer.  A shape that has
+    been seen before is captured (after running eagerly once more); later steps of that shape
+    copy their integers into the graph's buffer and replay it, which removes the host's work of
+    launching some hundreds of kernels.  The least recently used graphs are dropped beyond
+    ``capacity``.  The logits tensor of a shape is reused by its next replay.
+    """
+
+    def __init__(self, engine, capacity: int = 8):
+        from collections import Counter, OrderedDict
+        self.engine = engine
+        self.capacity = capacity
+        self.graphs: "OrderedDict[tuple, dict]" = OrderedDict()
+        self.seen: Counter = Counter()
+        self.width = -(-engine.plan.max_position // engine.cache.page_size)
+
+    def run(self, entries, starts, tables, slots):
+        """Logits of the step, or None if the step should run eagerly (a shape seen for the first time)."""
+        eng = self.engine
+        key = (tuple(len(e.tokens) for e in entries), tuple(tuple(e.want) for e in entries))
+        ent = self.graphs.get(key)
+        build = dict(act_dtype=eng.dtype, device=eng.device, min_blocks=self.width,
+                     max_position=eng.plan.max_position)
+        if ent is not None:
+            self.graphs.move_to_end(key)
+            build_step_batch(entries, starts, tables, slots, dev_buffer=ent["buffer"], **build)
+            ent["graph"].replay()
+            if hasattr(eng.ops, "launches"):
+                eng.ops.launches += ent["launches"]
+            return ent["logits"]
+        self.seen[key] += 1
+        if self.seen[key] < 2:
+            return None
+        probe = build_step_batch(entries, starts, tables, slots, **build)
+        buffer = torch.zeros(probe.packed_size, dtype=torch.int32, device=eng.device)
+        batch = build_step_batch(entries, starts, tables, slots, dev_buffer=buffer, **build)
+        batch.scratch["graph"] = True
+        logits = eng.forward(batch)                    # this step, eagerly
+        torch.cuda.synchronize(eng.device)
+        graph = torch.cuda.CUDAGraph()
+        before = getattr(eng.ops, "launches", 0)
+        with torch.cuda.graph(graph):
+            static_logits = eng.forward(batch)
+        self.graphs[key] = {"graph": graph, "buffer": buffer, "logits": static_logits,
+                            "launches": getattr(eng.ops, "launches", 0) - before}
+        while len(self.graphs) > self.capacity:
+            self.graphs.popitem(last=False)
+        return logits

@@ -68,6 +68,7 @@ class CudaOps:
         self.core = load_library("core")
         self.core.ti_last_error.restype = ctypes.c_char_p
         self._declare()
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._bf16 = None
         self._counters = None
         self._gemm_counter = None
@@ -75,6 +76,7 @@ class CudaOps:
         # measured slower than the norm's own launch (the tail runs on one SM), so it is off.
         self.fuse_norm_tail = False
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
+        self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -113,6 +115,7 @@ class CudaOps:
                                                _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
             b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
+            b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             b.ti_attn_prefill_supported.argtypes = [_i, _i]
             b.ti_attn_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f,
                                           _vp, _vp, _vp]
@@ -127,7 +130,7 @@ class CudaOps:
         return self._bf16
 
     def _stream(self) -> int:
-        return torch.cuda.current_stream(self.device).cuda_stream
+        return torch._C._cuda_getCurrentRawStream(self._device_index)
 
     def _ok(self, rc: int, lib=None) -> None:
         self.launches += 1
@@ -140,6 +143,13 @@ class CudaOps:
         if code:
             self.status.zero_()
             raise KernelError(f"a kernel reported device status {code} (1: page id outside the pool)")
+
+    def _tc_gemm(self, m: int, n: int):
+        """The tcgen05 product to use: on pairs of SMs when every pair gets a 256 x 256 tile."""
+        tiles = -(-m // 256) * -(-n // 256)
+        if self.use_2sm_gemm and tiles >= self.num_sms // 2:
+            return self.bf16.ti_gemm_tcgen05_2sm
+        return self.bf16.ti_gemm_tcgen05
 
     # ---- weights -------------------------------------------------------------------------
     def pack_linear(self, w: torch.Tensor) -> torch.Tensor:
@@ -223,7 +233,7 @@ class CudaOps:
             if (m > 64 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and
                     out.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                         m, n, k, a.stride(0), w.stride(0), out.stride(0), mode)):
-                self._ok(self.bf16.ti_gemm_tcgen05(
+                self._ok(self._tc_gemm(m, n)(
                     a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
                     w.stride(0), out.stride(0), 0, mode, self.status.data_ptr(), self._stream()),
                     self.bf16)
@@ -249,7 +259,7 @@ class CudaOps:
         if (interleaved and m > 64 and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
                 and inter % 8 == 0 and out.stride(0) % 8 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                     m, 2 * inter, k, h.stride(0), w_gate_up.stride(0), 0, 2)):
-            self._ok(self.bf16.ti_gemm_tcgen05(
+            self._ok(self._tc_gemm(m, 2 * inter)(
                 h.data_ptr(), w_gate_up.data_ptr(), None, out.data_ptr(), m, 2 * inter, k,
                 h.stride(0), w_gate_up.stride(0), 0, out.stride(0), 2, self.status.data_ptr(),
                 self._stream()), self.bf16)
