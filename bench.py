@@ -48,6 +48,13 @@ QWEN3_0_6B = dict(
     num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
     vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
     max_position_embeddings=4096)
+# the other two shapes of the reference's architecture that BASELINE.json names (untied heads)
+QWEN3_8B = dict(QWEN3_0_6B, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=8, intermediate_size=12288, tie_word_embeddings=False)
+QWEN3_32B = dict(QWEN3_0_6B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                 num_key_value_heads=8, intermediate_size=25600, tie_word_embeddings=False)
+SHAPES = {"0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "8b": ("Qwen3-8B shape", QWEN3_8B),
+          "32b": ("Qwen3-32B shape", QWEN3_32B)}
 PAGE = 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -282,6 +289,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
+    ap.add_argument("--shape", choices=list(SHAPES), default="0.6b", help="layer sizes of the model")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill", "chains"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
@@ -301,7 +309,8 @@ def main() -> int:
     import torch
     from tinyinfer_b200 import Engine
 
-    cfg = dict(QWEN3_0_6B)
+    shape_name, shape_cfg = SHAPES[args.shape]
+    cfg = dict(shape_cfg)
     cfg["max_position_embeddings"] = max(args.context, 2048)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
@@ -343,17 +352,17 @@ def main() -> int:
 
     value = args.batch / (ms * 1e-3)
     line = {
-        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-0.6B shape)",
+        "metric": f"decode tok/s at batch {args.batch}, context {args.context} ({shape_name})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights, random token ids, random keys and values",
         "config": {
-            "model": "Qwen3-0.6B shape", "layers": cfg["num_hidden_layers"],
+            "model": shape_name, "layers": cfg["num_hidden_layers"],
             "layers_full": full_layers, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
-            "vocab": cfg["vocab_size"], "tied": True, "global_batch": args.batch,
+            "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"], "global_batch": args.batch,
             "seq_len": args.context, "page_size": PAGE, "parallelism": "single GPU",
             "cuda_graph": True, "l2": "working set > L2, no flush", "peaks": pk_kind,
         },

@@ -86,7 +86,8 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
             rows.append(int(cu[i]) + int(w))
     k = len(rows)
     dec = [int(cu[i]) for i in range(r) if q_lens[i] == 1]
-    chk = [int(cu[i]) + j for i in range(r) if q_lens[i] > 1 for j in range(q_lens[i])]
+    chk_parts = [np.arange(cu[i], cu[i + 1]) for i in range(r) if q_lens[i] > 1]
+    chk = np.concatenate(chk_parts) if chk_parts else np.zeros(0, dtype=np.int64)
     def tile_list(rows_per_tile):
         found = []
         for i in range(r):
@@ -112,7 +113,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         o += n
         return span
 
-    tok = np.fromiter((int(x) for e in entries for x in e.tokens), dtype=np.int64, count=t)
+    tok = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]) if t else np.zeros(0, dtype=np.int64)
     pos = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, q_lens)]) if t else tok
     roft = np.repeat(np.arange(r), q_lens)
     spans = {
@@ -120,7 +121,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         "qs": put(np.asarray(starts, dtype=np.int64), r), "ctx": put(np.asarray(ctx), r),
         "slots": put(np.asarray(slots, dtype=np.int64), r), "rows": put(np.asarray(rows), k),
         "dec": put(np.asarray(dec, dtype=np.int64), len(dec)),
-        "chk": put(np.asarray(chk, dtype=np.int64), len(chk)),
+        "chk": put(chk, len(chk)),
         "tiles": put(np.asarray(tiles, dtype=np.int64).reshape(-1), 3 * len(tiles)),
         "tiles_big": put(np.asarray(tiles_big, dtype=np.int64).reshape(-1), 3 * len(tiles_big)),
     }

@@ -11,6 +11,7 @@ from __future__ import annotations
 import os
 from typing import Any, Hashable, Mapping, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages
@@ -129,9 +130,10 @@ class Engine:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
         vocab = self.plan.vocab_size
         for e in entries:
-            for tok in e.tokens:
-                if not 0 <= int(tok) < vocab:
-                    raise ValueError(f"request {e.req_id!r}: token id {tok} is outside [0, {vocab})")
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            if ids.size and (ids.min() < 0 or ids.max() >= vocab):
+                bad = int(ids[(ids < 0) | (ids >= vocab)][0])
+                raise ValueError(f"request {e.req_id!r}: token id {bad} is outside [0, {vocab})")
             for place in e.want:
                 if not 0 <= int(place) < len(e.tokens):
                     raise IndexError(f"request {e.req_id!r}: wanted place {place} is outside its "
