@@ -43,6 +43,30 @@ def test_long_decoding(tmp_path_factory, name, dtype):
     eng.ops.check_status()
 
 
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_decoding_with_every_few_rows_product_on_the_split_k_kernel(tmp_path_factory, name):
+    """The engine's small weights never reach the split-K tcgen05 product by themselves; forced
+    onto it, prompts in portions, decoding and a mixed batch still match the plain implementation."""
+    from tinyinfer_b200 import StepEntry
+    d = make_model(tmp_path_factory.getbasetemp(), name)
+    cfg, w = load_folder(d)
+    toks = random_tokens(cfg["vocab_size"], 90, seed=4)
+    other = random_tokens(cfg["vocab_size"], 40, seed=5)
+    ref = plain_forward(cfg, w, toks, emulate_bf16=True)
+    ref_other = plain_forward(cfg, w, other, emulate_bf16=True)
+    eng = _engine(d, "bfloat16")
+    eng.ops.few_tc_min_bytes = 0
+    before = eng.ops.launches
+    rows = [eng.step([StepEntry("a", toks[:30], list(range(30)))]).cpu()]
+    both = eng.step([StepEntry("a", toks[30:50], list(range(20))), StepEntry("b", other, list(range(40)))]).cpu()
+    rows.append(both[:20])
+    rows += [eng.step([StepEntry("a", [t], [0])]).cpu() for t in toks[50:]]
+    assert_close_logits(torch.cat(rows), ref, BF16_RTOL, f"{name} on the split-K product")
+    assert_close_logits(both[20:], ref_other, BF16_RTOL, f"{name} second request on the split-K product")
+    assert eng.ops.launches > before
+    eng.ops.check_status()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(tmp_path_factory, dtype):
     from tinyinfer_b200 import StepEntry

@@ -95,6 +95,64 @@ def test_linear_few_rows_bf16(ops, m, nk):
     assert torch.equal(alone[0], full[m - 1])
 
 
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 33, 64])
+@pytest.mark.parametrize("nk", [(48, 64), (100, 96), (1000, 520), (4096, 1024), (1024, 3072), (331, 128),
+                                (6144, 2048), (20000, 256)])
+def test_linear_few_rows_on_tcgen05(ops, m, nk):
+    """The few-rows product for large weights (W as the MMA's 128-row side, K split over blocks,
+    the last block of a tile adds the partial sums), forced here at every size."""
+    n, k = nk
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1)
+    base = _rand((m, n), seed=2)
+    keep = ops.few_tc_min_bytes
+    ops.few_tc_min_bytes = 0
+    try:
+        before = ops.launches
+        for acc in (False, True):
+            out = base.clone()
+            assert ops._few_tc(a, w, out, None, 1 if acc else 0)
+            ops.check_status()
+            want = a.double() @ w.double().T + (base.double() if acc else 0)
+            _close(out, want, _sum_rtol(k), f"few rows on tcgen05 m={m} n={n} k={k} acc={acc}")
+        assert ops.launches == before + 2
+        # a row's result does not depend on how many rows there are, nor on the rows beside it
+        alone = torch.empty((1, n), device=DEV)
+        ops.linear(a[m - 1:m], w, alone)
+        full = torch.empty((m, n), device=DEV)
+        ops.linear(a, w, full)
+        assert torch.equal(alone[0], full[m - 1])
+        if n % 16 == 0:
+            gate, up = w[:n // 2] * 0.2, w[n // 2:] * 0.2
+            y = torch.zeros((m, n // 2), dtype=torch.bfloat16, device=DEV)
+            ref = torch.empty_like(y)
+            ops.gate_up_swiglu(a, ops.pack_gate_up(gate.contiguous(), up.contiguous()), y)
+            r = RefOps()
+            r.gate_up_swiglu(a, r.pack_gate_up(gate, up), ref)
+            _close(y, ref, 8e-3, f"few rows on tcgen05, swiglu m={m} {nk}")
+        ops.check_status()
+    finally:
+        ops.few_tc_min_bytes = keep
+
+
+def test_large_weights_go_to_the_split_k_kernel(ops):
+    """The dispatch: at least 32 MiB of weights and at most 64 rows."""
+    w = _rand((4096, 4096), torch.bfloat16, seed=1, scale=0.05)
+    a = _rand((8, 4096), torch.bfloat16)
+    out = torch.empty((8, 4096), device=DEV)
+    ops.linear(a, w, out)
+    _close(out, a.double() @ w.double().T, _sum_rtol(4096), "4096 x 4096 at 8 rows")
+    keep = ops.few_tc_min_bytes
+    try:
+        ops.few_tc_min_bytes = None
+        other = torch.empty_like(out)
+        ops.linear(a, w, other)
+        assert not torch.equal(out, other), "both runs took the same kernel"
+        _close(other, out, _sum_rtol(4096), "the two few-rows kernels")
+    finally:
+        ops.few_tc_min_bytes = keep
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [65, 128, 129, 300, 1000])
 @pytest.mark.parametrize("nk", [(128, 64), (136, 72), (4096, 1024), (1024, 3072), (1000, 520), (331, 128)])
 def test_linear_many_rows_bf16(ops, m, nk):

@@ -73,6 +73,58 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
     }
 }
 
+// The same norm with one block per row for few rows whose length is a multiple of 4 and at most
+// 16 * THREADS: a thread keeps its up to four 16-byte pieces of the row in registers, so the row
+// is read once and all loads are in flight together; the weights are fetched before the wait on
+// the previous kernel.
+template <typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                   float eps, int n, TO* __restrict__ out) {
+    __shared__ float scratch[32];
+    pdl_launch();
+    const int n4 = n >> 2;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4 g[4], v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * THREADS;
+        if (i < n4) g[j] = w4[i];
+    }
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * THREADS;
+        if (i < n4) v[j] = xr[i];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (threadIdx.x + j * THREADS < n4) {
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+    TO* o = out + (size_t)r * n;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * THREADS;
+        if (i >= n4) continue;
+        const float4 y = make_float4(v[j].x * inv * g[j].x, v[j].y * inv * g[j].y, v[j].z * inv * g[j].z,
+                                     v[j].w * inv * g[j].w);
+        if constexpr (sizeof(TO) == 2) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(y.x, y.y), b = __floats2bfloat162_rn(y.z, y.w);
+            *reinterpret_cast<uint2*>(o + 4 * i) =
+                make_uint2(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b));
+        } else {
+            *reinterpret_cast<float4*>(o + 4 * i) = y;
+        }
+    }
+}
+
 // y[t, j] = silu(gate_j) * up_j, silu(g) = g / (1 + exp(-g)).  Stacked layout: gate_j = gu[t, j],
 // up_j = gu[t, inter + j].  Interleaved layout (groups of 8 gate columns followed by their 8 up
 // columns): gate_j = gu[t, 16 (j / 8) + j % 8], up_j eight columns further.
@@ -216,6 +268,20 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
             ti_launch_pdl(rmsnorm_warp_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
         else
             ti_launch_pdl(rmsnorm_warp_kernel<float>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (float*)out);
+        return ti_check_launch("rmsnorm");
+    }
+    if (n % 4 == 0 && n <= 16 * 1024 && (out_dtype == TI_BF16 || out_dtype == TI_F32) &&
+        (uintptr_t)x % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        // few rows: a block per row that keeps the row in registers
+        const bool small = n <= 16 * 256;
+        if (out_dtype == TI_BF16 && small)
+            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256>, num_rows, 256, 0, s, x, weight, rows, eps, n, (bf16*)out);
+        else if (out_dtype == TI_BF16)
+            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 1024>, num_rows, 1024, 0, s, x, weight, rows, eps, n, (bf16*)out);
+        else if (small)
+            ti_launch_pdl(rmsnorm_vec_kernel<float, 256>, num_rows, 256, 0, s, x, weight, rows, eps, n, (float*)out);
+        else
+            ti_launch_pdl(rmsnorm_vec_kernel<float, 1024>, num_rows, 1024, 0, s, x, weight, rows, eps, n, (float*)out);
         return ti_check_launch("rmsnorm");
     }
     const int threads = n >= 1024 ? 256 : 128;

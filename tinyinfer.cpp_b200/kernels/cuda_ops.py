@@ -77,6 +77,11 @@ class CudaOps:
         self.fuse_norm_tail = False
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
+        # few-rows products on tcgen05 with K split over blocks: for weights of at least this many
+        # bytes (None: never), below which the direct-to-register kernel's shorter chain wins
+        # (measured: 4096 x 4096 is even at 16 rows, larger weights gain 15-50 %)
+        self.few_tc_min_bytes = 1 << 25
+        self._few_tickets = None
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -109,6 +114,11 @@ class CudaOps:
             b.ti_gemm_skinny_norm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
                                               _f, _vp, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_gemm_tcgen05_few_supported.argtypes = [_i, _i, _i, _i, _i, _i]
+            b.ti_gemm_tcgen05_few_scratch.argtypes = [_i, _i, _i, ctypes.POINTER(ctypes.c_longlong),
+                                                      ctypes.POINTER(ctypes.c_int)]
+            b.ti_gemm_tcgen05_few.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp,
+                                              _vp, _vp]
             b.ti_attn_decode_supported.argtypes = [_i, _i, _i]
             b.ti_attn_decode_blocks_per_sm.argtypes = [_i]
             b.ti_attn_decode_fused.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i,
@@ -150,6 +160,25 @@ class CudaOps:
         if self.use_2sm_gemm and tiles >= self.num_sms // 2:
             return self.bf16.ti_gemm_tcgen05_2sm
         return self.bf16.ti_gemm_tcgen05
+
+    def _few_tc(self, a, w, c, out_act, mode) -> bool:
+        """Runs the split-K tcgen05 product for few rows if it applies to these operands."""
+        m, k = a.shape
+        n = w.shape[0]
+        if (self.few_tc_min_bytes is None or m > 64 or n * k * 2 < self.few_tc_min_bytes
+                or a.data_ptr() % 16 or w.data_ptr() % 16
+                or not self.bf16.ti_gemm_tcgen05_few_supported(m, n, k, a.stride(0), w.stride(0), mode)):
+            return False
+        ws_floats, tickets = ctypes.c_longlong(0), ctypes.c_int(0)
+        self.bf16.ti_gemm_tcgen05_few_scratch(m, n, k, ctypes.byref(ws_floats), ctypes.byref(tickets))
+        if self._few_tickets is None or self._few_tickets.numel() < tickets.value:
+            self._few_tickets = torch.zeros(max(4096, tickets.value), dtype=torch.int32, device=a.device)
+        ws = torch.empty(ws_floats.value, dtype=torch.float32, device=a.device) if ws_floats.value else None
+        self._ok(self.bf16.ti_gemm_tcgen05_few(
+            a.data_ptr(), w.data_ptr(), _ptr(c), _ptr(out_act), m, n, k, a.stride(0), w.stride(0),
+            c.stride(0) if c is not None else 0, out_act.stride(0) if out_act is not None else 0, mode,
+            _ptr(ws), self._few_tickets.data_ptr(), self.status.data_ptr(), self._stream()), self.bf16)
+        return True
 
     # ---- weights -------------------------------------------------------------------------
     def pack_linear(self, w: torch.Tensor) -> torch.Tensor:
@@ -211,6 +240,8 @@ class CudaOps:
         _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
               "linear: rows must be contiguous")
         if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if self._few_tc(a, w, out, None, 1 if accumulate else 0):
+                return False
             if self.bf16.ti_gemm_skinny_supported(m, n, k, a.stride(0), w.stride(0)):
                 fuse = (self.fuse_norm_tail and then_norm is not None and then_norm[2].dtype == torch.bfloat16
                         and n % 4 == 0 and out.stride(0) % 4 == 0 and then_norm[2].stride(0) % 4 == 0)
@@ -249,6 +280,9 @@ class CudaOps:
         _need(w_gate_up.shape[0] == 2 * inter, "gate_up_swiglu: weight must hold gate and up rows")
         interleaved = bool(getattr(w_gate_up, "_ti_interleaved", False))
         m, k = h.shape
+        if (interleaved and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                and self._few_tc(h, w_gate_up, None, out, 2)):
+            return
         if (interleaved and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
                 and self.bf16.ti_gemm_skinny_supported(m, 2 * inter, k, h.stride(0),
                                                        w_gate_up.stride(0))):
