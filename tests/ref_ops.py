@@ -37,16 +37,26 @@ class RefOps:
         inv = torch.rsqrt((src * src).mean(dim=-1, keepdim=True) + eps)
         out.copy_((src * inv * weight.to(F32)).to(out.dtype))
 
-    def linear(self, a, w, out, accumulate=False, then_norm=None):
+    def _normed(self, pre_norm):
+        x, weight, eps, dtype = pre_norm
+        a = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
+        self.rmsnorm(x, weight, eps, a)
+        return a
+
+    def linear(self, a, w, out, accumulate=False, pre_norm=None):
+        if pre_norm is not None:                       # (x, weight, eps, dtype): a = norm(x)
+            assert a is None
+            a = self._normed(pre_norm)
         prod = a.to(F32) @ w.to(F32).T
         if accumulate:
             out.add_(prod)
         else:
             out.copy_(prod)
-        if then_norm is not None:                      # (weight, eps, normed output)
-            self.rmsnorm(out, then_norm[0], then_norm[1], then_norm[2])
 
-    def gate_up_swiglu(self, h, w_gate_up, out):
+    def gate_up_swiglu(self, h, w_gate_up, out, pre_norm=None):
+        if pre_norm is not None:
+            assert h is None
+            h = self._normed(pre_norm)
         inter = out.shape[1]
         gu = h.to(F32) @ w_gate_up.to(F32).T
         gate, up = gu[:, :inter], gu[:, inter:]

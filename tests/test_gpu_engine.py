@@ -55,12 +55,16 @@ def test_decoding_with_every_few_rows_product_on_the_split_k_kernel(tmp_path_fac
     ref = plain_forward(cfg, w, toks, emulate_bf16=True)
     ref_other = plain_forward(cfg, w, other, emulate_bf16=True)
     eng = _engine(d, "bfloat16")
+    keep = eng.ops.few_tc_min_bytes                  # the kernel set is shared by every engine of the device
     eng.ops.few_tc_min_bytes = 0
     before = eng.ops.launches
-    rows = [eng.step([StepEntry("a", toks[:30], list(range(30)))]).cpu()]
-    both = eng.step([StepEntry("a", toks[30:50], list(range(20))), StepEntry("b", other, list(range(40)))]).cpu()
-    rows.append(both[:20])
-    rows += [eng.step([StepEntry("a", [t], [0])]).cpu() for t in toks[50:]]
+    try:
+        rows = [eng.step([StepEntry("a", toks[:30], list(range(30)))]).cpu()]
+        both = eng.step([StepEntry("a", toks[30:50], list(range(20))), StepEntry("b", other, list(range(40)))]).cpu()
+        rows.append(both[:20])
+        rows += [eng.step([StepEntry("a", [t], [0])]).cpu() for t in toks[50:]]
+    finally:
+        eng.ops.few_tc_min_bytes = keep
     assert_close_logits(torch.cat(rows), ref, BF16_RTOL, f"{name} on the split-K product")
     assert_close_logits(both[20:], ref_other, BF16_RTOL, f"{name} second request on the split-K product")
     assert eng.ops.launches > before

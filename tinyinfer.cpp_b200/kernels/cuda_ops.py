@@ -13,6 +13,8 @@ embed(table, token_ids, out)                 out[t] = float32(table[token_ids[t]
 rmsnorm(x, weight, eps, out, rows=None)      out[r] = norm(x[rows[r]] or x[r]), rounded to out.dtype
 linear(a, w, out, accumulate=False)          out (+)= a @ w.T in float32
 gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
+    both take pre_norm=(x, weight, eps, dtype) instead of their first operand (None): the operand
+    is then rmsnorm(x) * weight rounded to dtype, made inside the product's launch where it can be
 qk_norm_rope_store(...)                      q/k head norm, rotation, k/v into pages, q out
 paged_attention(...)                         causal attention over the pages of each token's request
 argmax(logits, out) / sample(...)            next token per row
@@ -71,12 +73,9 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._bf16 = None
         self._counters = None
-        self._gemm_counter = None
-        # Computing the following RMSNorm in the product's last block saves a launch but was
-        # measured slower than the norm's own launch (the tail runs on one SM), so it is off.
-        self.fuse_norm_tail = False
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
+        self.fuse_pre_norm = True         # the few-rows product normalises its own input rows
         # few-rows products on tcgen05 with K split over blocks: for weights of at least this many
         # bytes (None: never), below which the direct-to-register kernel's shorter chain wins
         # (measured: 4096 x 4096 is even at 16 rows, larger weights gain 15-50 %)
@@ -111,9 +110,10 @@ class CudaOps:
             b = load_library("bf16")
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_gemm_skinny.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]
-            b.ti_gemm_skinny_norm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
-                                              _f, _vp, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_gemm_skinny_prenorm_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_gemm_skinny_prenorm.argtypes = [_vp, _i, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                                 _i, _vp]
             b.ti_gemm_tcgen05_few_supported.argtypes = [_i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_few_scratch.argtypes = [_i, _i, _i, ctypes.POINTER(ctypes.c_longlong),
                                                       ctypes.POINTER(ctypes.c_int)]
@@ -220,19 +220,36 @@ class CudaOps:
                                       x.shape[1], float(eps), out.data_ptr(),
                                       _code(out, "rmsnorm"), self._stream()))
 
-    def linear(self, a, w, out, accumulate=False, then_norm=None):
-        """out (+)= a @ w.T.  ``then_norm=(weight, eps, normed)`` also writes
-        ``normed = rmsnorm(out) * weight``, in the same launch where the kernel can."""
-        if then_norm is not None:
-            norm_w, eps, normed = then_norm
-            if self._linear(a, w, out, accumulate, then_norm):
-                return
-            self.rmsnorm(out, norm_w, eps, normed)
-            return
-        self._linear(a, w, out, accumulate, None)
+    def _pre_normed(self, pre_norm, w, n, c, out_act, mode) -> Optional[torch.Tensor]:
+        """Runs the few-rows product on rmsnorm(x) inside one launch if it applies (returns
+        None); else returns the normed rows for the caller to multiply."""
+        x, norm_w, eps, dtype = pre_norm
+        m, k = x.shape
+        _need(x.dtype == torch.float32 and x.stride(1) == 1, "pre_norm: x must be float32 rows")
+        _need(norm_w.dtype == torch.float32 and norm_w.shape[0] == k, "pre_norm: weight must be float32 [K]")
+        if (self.fuse_pre_norm and dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.stride(1) == 1
+                and (self.few_tc_min_bytes is None or n * k * 2 < self.few_tc_min_bytes)
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and norm_w.data_ptr() % 16 == 0
+                and self.bf16.ti_gemm_skinny_prenorm_supported(m, n, k, x.stride(0), w.stride(0))):
+            self._ok(self.bf16.ti_gemm_skinny_prenorm(
+                x.data_ptr(), x.stride(0), norm_w.data_ptr(), float(eps), w.data_ptr(), _ptr(c),
+                _ptr(out_act), m, n, k, w.stride(0), c.stride(0) if c is not None else 0,
+                out_act.stride(0) if out_act is not None else 0, mode, self._stream()), self.bf16)
+            return None
+        a = torch.empty((m, k), dtype=dtype, device=x.device)
+        self.rmsnorm(x.contiguous(), norm_w, eps, a)
+        return a
 
-    def _linear(self, a, w, out, accumulate, then_norm) -> bool:
-        """Runs the product; True if it also computed the norm asked for."""
+    def linear(self, a, w, out, accumulate=False, pre_norm=None):
+        """out (+)= a @ w.T.  ``pre_norm=(x, weight, eps, dtype)`` with ``a=None``:
+        a = rmsnorm(x) * weight in dtype."""
+        if pre_norm is not None:
+            _need(a is None, "linear: give either a or pre_norm")
+            _need(w.shape[1] == pre_norm[0].shape[1] and tuple(out.shape) == (pre_norm[0].shape[0], w.shape[0])
+                  and out.dtype == torch.float32 and out.stride(1) == 1, "linear: shapes do not agree")
+            a = self._pre_normed(pre_norm, w, w.shape[0], out, None, 1 if accumulate else 0)
+            if a is None:
+                return
         m, k = a.shape
         n = w.shape[0]
         _need(w.shape[1] == k and tuple(out.shape) == (m, n), "linear: shapes do not agree")
@@ -240,27 +257,14 @@ class CudaOps:
         _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
               "linear: rows must be contiguous")
         if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-            if self._few_tc(a, w, out, None, 1 if accumulate else 0):
-                return False
+            mode = 1 if accumulate else 0
+            if self._few_tc(a, w, out, None, mode):
+                return
             if self.bf16.ti_gemm_skinny_supported(m, n, k, a.stride(0), w.stride(0)):
-                fuse = (self.fuse_norm_tail and then_norm is not None and then_norm[2].dtype == torch.bfloat16
-                        and n % 4 == 0 and out.stride(0) % 4 == 0 and then_norm[2].stride(0) % 4 == 0)
-                if fuse:
-                    if self._gemm_counter is None:
-                        self._gemm_counter = torch.zeros(1, dtype=torch.int32, device=a.device)
-                    norm_w, eps, normed = then_norm
-                    self._ok(self.bf16.ti_gemm_skinny_norm(
-                        a.data_ptr(), w.data_ptr(), out.data_ptr(), normed.data_ptr(), m, n, k,
-                        a.stride(0), w.stride(0), out.stride(0), normed.stride(0),
-                        1 if accumulate else 0, norm_w.data_ptr(), float(eps),
-                        self._gemm_counter.data_ptr(), self._stream()), self.bf16)
-                    return True
                 self._ok(self.bf16.ti_gemm_skinny(
                     a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
-                    w.stride(0), out.stride(0), 0, 1 if accumulate else 0, self._stream()),
-                    self.bf16)
-                return False
-            mode = 1 if accumulate else 0
+                    w.stride(0), out.stride(0), 0, mode, self._stream()), self.bf16)
+                return
             if (m > 64 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and
                     out.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                         m, n, k, a.stride(0), w.stride(0), out.stride(0), mode)):
@@ -268,17 +272,28 @@ class CudaOps:
                     a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
                     w.stride(0), out.stride(0), 0, mode, self.status.data_ptr(), self._stream()),
                     self.bf16)
-                return False
+                return
         self._ok(self.core.ti_gemm_simple(
             a.data_ptr(), _code(a, "linear"), w.data_ptr(), _code(w, "linear"), out.data_ptr(),
             m, n, k, a.stride(0), w.stride(0), out.stride(0), int(bool(accumulate)),
             self._stream()))
-        return False
 
-    def gate_up_swiglu(self, h, w_gate_up, out):
+    def gate_up_swiglu(self, h, w_gate_up, out, pre_norm=None):
         inter = out.shape[1]
         _need(w_gate_up.shape[0] == 2 * inter, "gate_up_swiglu: weight must hold gate and up rows")
         interleaved = bool(getattr(w_gate_up, "_ti_interleaved", False))
+        if pre_norm is not None:
+            _need(h is None, "gate_up_swiglu: give either h or pre_norm")
+            _need(w_gate_up.shape[1] == pre_norm[0].shape[1] and out.shape[0] == pre_norm[0].shape[0],
+                  "gate_up_swiglu: shapes do not agree")
+            if interleaved and out.dtype == torch.bfloat16 and out.stride(1) == 1:
+                h = self._pre_normed(pre_norm, w_gate_up, 2 * inter, None, out, 2)
+                if h is None:
+                    return
+            else:
+                x, norm_w, eps, dtype = pre_norm
+                h = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
+                self.rmsnorm(x, norm_w, eps, h)
         m, k = h.shape
         if (interleaved and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
                 and self._few_tc(h, w_gate_up, None, out, 2)):

@@ -22,7 +22,7 @@ from .base import (MATRIX, NORM_WEIGHT, PagedKVSpec, Part, WeightSpec, as_float3
 
 class Attention(Part):
     category = "mixer"
-    fuses_norm = True        # forward(..., then_norm=norm) returns norm(residual) from its last launch
+    takes_norm = True        # forward(ops, None, residual, ..., pre_norm=norm) norms the residual itself
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: float, position: PartSpec, window: Optional[int] = None,
@@ -67,25 +67,25 @@ class Attention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, ops, h, residual, step, cache, then_norm=None):
-        t = h.shape[0]
-        dev = h.device
+    def forward(self, ops, h, residual, step, cache, pre_norm=None):
+        """``h`` is the normed residual, or None with ``pre_norm`` the RMSNorm part to apply to
+        ``residual`` inside the first product."""
+        t = residual.shape[0]
+        dev = residual.device
+        act = step.act_dtype if h is None else h.dtype
         qkv = torch.empty((t, self.nq + 2 * self.nk), dtype=torch.float32, device=dev)
-        ops.linear(h, self.w_qkv, qkv)
-        q = torch.empty((t, self.nq), dtype=h.dtype, device=dev)
+        if h is None:
+            ops.linear(None, self.w_qkv, qkv, pre_norm=(residual, pre_norm.weight, pre_norm.eps, act))
+        else:
+            ops.linear(h, self.w_qkv, qkv)
+        q = torch.empty((t, self.nq), dtype=act, device=dev)
         ops.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.eps,
                                self.position.table(dev), step, cache, q,
                                self.num_heads, self.num_kv_heads, self.head_dim)
-        out = torch.empty((t, self.nq), dtype=h.dtype, device=dev)
+        out = torch.empty((t, self.nq), dtype=act, device=dev)
         ops.paged_attention(q, step, cache, out, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.window, self.scale)
-        if then_norm is None:
-            ops.linear(out, self.w_o, residual, accumulate=True)
-            return None
-        normed = torch.empty((t, self.hidden_size), dtype=h.dtype, device=dev)
-        ops.linear(out, self.w_o, residual, accumulate=True,
-                   then_norm=(then_norm.weight, then_norm.eps, normed))
-        return normed
+        ops.linear(out, self.w_o, residual, accumulate=True)
 
 
 register_part("mixer", "attention", Attention)

@@ -14,12 +14,10 @@ position  ``table(device)``: what the mixer's kernels need to rotate a head at a
 mixer     ``cache_spec()``: what it keeps per request (``PagedKVSpec``, ``FixedStateSpec`` or
           None); ``forward(ops, h, residual, step, cache)``: adds its output to ``residual``.
 ffn       ``forward(ops, h, residual, step)``: adds its output to ``residual``.
-          Optional for both: a class attribute ``fuses_norm = True`` and a keyword
-          ``then_norm=<RMSNorm part>``; the part then returns ``norm(residual)``, computed by
-          its last launch, and the block skips the norm's own launch.
-block     arrangement of the four parts of a layer: ``forward(ops, x, step, cache)``; with
-          ``chains_norm = True`` also ``h=`` (the normed input, if already there) and
-          ``next_norm=`` (the norm after the block, whose result it may return).
+          Optional for both: a class attribute ``takes_norm = True`` and a keyword
+          ``pre_norm=<RMSNorm part>``; the block then passes ``h=None`` and the part applies
+          the norm to ``residual`` itself, inside its first product's launch.
+block     arrangement of the four parts of a layer: ``forward(ops, x, step, cache)``.
 embedding ``forward(ops, token_ids, out)``;  head ``forward(ops, h) -> logits``.
 
 ``h`` is the normed activation in the engine's activation dtype (bfloat16 or

@@ -11,31 +11,23 @@ from .base import Part, register_part
 
 class PreNormBlock(Part):
     category = "block"
-    chains_norm = True       # forward takes the normed input ``h`` and may return the next block's
 
     def __init__(self, mixer, ffn, mixer_norm, ffn_norm):
         self.mixer, self.ffn = mixer, ffn
         self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
 
-    def forward(self, ops, x, step, cache, h=None, next_norm=None):
-        """``h``: norm1(x) if the block before already computed it.  ``next_norm``: the norm that
-        follows this block; if the feed-forward can compute it in its last launch, its result is
-        returned (else None).  A mixer or feed-forward that sets ``fuses_norm`` accepts
-        ``then_norm=<RMSNorm part>`` and returns the normed residual."""
-        if h is None:
-            h = self.mixer_norm.forward(ops, x, step.act_dtype)
-        h2 = None
-        if getattr(self.mixer, "fuses_norm", False) and getattr(self.ffn_norm, "is_rmsnorm", False):
-            h2 = self.mixer.forward(ops, h, x, step, cache, then_norm=self.ffn_norm)
+    def forward(self, ops, x, step, cache):
+        """A mixer or feed-forward that sets ``takes_norm`` gets ``h=None, pre_norm=<the RMSNorm
+        part>`` and applies the norm to the residual inside its first product; any other gets
+        the normed residual."""
+        if getattr(self.mixer, "takes_norm", False) and getattr(self.mixer_norm, "is_rmsnorm", False):
+            self.mixer.forward(ops, None, x, step, cache, pre_norm=self.mixer_norm)
         else:
-            self.mixer.forward(ops, h, x, step, cache)
-        if h2 is None:
-            h2 = self.ffn_norm.forward(ops, x, step.act_dtype)
-        if (next_norm is not None and getattr(self.ffn, "fuses_norm", False)
-                and getattr(next_norm, "is_rmsnorm", False)):
-            return self.ffn.forward(ops, h2, x, step, then_norm=next_norm)
-        self.ffn.forward(ops, h2, x, step)
-        return None
+            self.mixer.forward(ops, self.mixer_norm.forward(ops, x, step.act_dtype), x, step, cache)
+        if getattr(self.ffn, "takes_norm", False) and getattr(self.ffn_norm, "is_rmsnorm", False):
+            self.ffn.forward(ops, None, x, step, pre_norm=self.ffn_norm)
+        else:
+            self.ffn.forward(ops, self.ffn_norm.forward(ops, x, step.act_dtype), x, step)
 
 
 register_part("block", "prenorm", PreNormBlock)

@@ -74,18 +74,9 @@ class CausalLM:
         x = torch.empty((step.num_tokens, self.plan.hidden_size), dtype=torch.float32,
                         device=step.token_ids.device)
         self.embedding.forward(ops, step.token_ids, x)
-        schedule = self.plan.schedule
-        h = None                       # norm of x for the next block, when the last one made it
-        for i, entry in enumerate(schedule):
+        for entry in self.plan.schedule:
             cache = cache_views[(entry.cache_slot, entry.writes_cache)]
-            block = self.blocks[entry.layer]
-            if getattr(block, "chains_norm", False):
-                nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
-                next_norm = getattr(nxt, "mixer_norm", None) if getattr(nxt, "chains_norm", False) else None
-                h = block.forward(ops, x, step, cache, h=h, next_norm=next_norm)
-            else:
-                block.forward(ops, x, step, cache)
-                h = None
+            self.blocks[entry.layer].forward(ops, x, step, cache)
         if step.num_logit_rows == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=x.device)
         h = self.final_norm.forward_rows(ops, x, step.logit_rows, step.act_dtype)
