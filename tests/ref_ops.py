@@ -92,6 +92,13 @@ class RefOps:
             cache.pages[page, 0, :, pos % ps, :] = k.to(cache.pages.dtype)
             cache.pages[page, 1, :, pos % ps, :] = v.to(cache.pages.dtype)
 
+    def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+                       num_heads, num_kv_heads, head_dim, pre_norm=None):
+        qkv = torch.empty((q_out.shape[0], w_qkv.shape[0]), dtype=F32, device=q_out.device)
+        self.linear(h, w_qkv, qkv, pre_norm=pre_norm)
+        self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+                                num_heads, num_kv_heads, head_dim)
+
     def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,
                         scale):
         t = q.shape[0]

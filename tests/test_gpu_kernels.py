@@ -247,7 +247,8 @@ def _paged_case(num_heads, num_kv, hd, page_size, ctx_lens, q_lens, dtype, seed=
     ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), decode_rows=ti(dec),
                            chunk_rows=ti(chk), chunk_tiles=ti(tiles).view(-1, 3),
-                           chunk_tiles_big=ti(tiles_big).view(-1, 3), max_position=max(ctx_lens), max_ctx_len=max(ctx_lens))
+                           chunk_tiles_big=ti(tiles_big).view(-1, 3), max_position=max(ctx_lens), max_ctx_len=max(ctx_lens),
+                           scratch={})
     cache = SimpleNamespace(pages=pages, block_table=bt.to(DEV), page_size=page_size, writes=True)
     q = _rand((len(positions), num_heads * hd), dtype, seed=seed + 2)
     return step, cache, q
@@ -336,6 +337,52 @@ def test_qk_norm_rope_store(ops, dtype, geom):
     _close(q_out, q_ref, tol, "rotated queries")
     _close(cache.pages, ref_cache.pages, tol, "pages after the store")
     ops.check_status()
+
+
+@pytest.mark.parametrize("geom", [(16, 8, 1024, [2048], [2048]), (5, 1, 136, [300, 77, 500], [150, 70, 333]),
+                                  (3, 3, 64, [90], [65]), (16, 8, 1024, [700, 64, 100], [700, 1, 100])])
+@pytest.mark.parametrize("writes", [True, False])
+def test_qkv_product_with_norm_rotation_and_store_in_its_epilogue(ops, geom, writes):
+    """Prompt portions with head size 128: the tcgen05 QKV product whose epilogue norms, rotates
+    and stores each head (on one SM or on pairs, by size) against the separate kernels."""
+    heads, kv, k, ctx, qls = geom
+    hd, ps = 128, 16
+    step, cache, _ = _paged_case(heads, kv, hd, ps, ctx, qls, torch.bfloat16)
+    cache.writes = writes
+    t = step.positions.shape[0]
+    h = _rand((t, k), torch.bfloat16, seed=7)
+    w = _rand(((heads + 2 * kv) * hd, k), torch.bfloat16, seed=8, scale=2.0 / math.sqrt(k))
+    qw, kw = 1 + _rand((hd,), seed=4, scale=0.1), 1 + _rand((hd,), seed=5, scale=0.1)
+    inv_freq = torch.pow(torch.tensor(1e6, dtype=torch.float64),
+                         -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(DEV)
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.pages = cache.pages.clone()
+    untouched = cache.pages.clone()
+    q_out = torch.zeros((t, heads * hd), dtype=torch.bfloat16, device=DEV)
+    q_ref = torch.empty_like(q_out)
+    before = ops.launches
+    ops.qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, cache, q_out, heads, kv, hd)
+    assert ops.launches - before == 2                    # the rotation table of the step, the product
+    ops.qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, cache, q_out, heads, kv, hd)
+    assert ops.launches - before == 3                    # the next layer finds the table
+    ops.check_status()
+    RefOps().qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, ref_cache, q_ref, heads, kv, hd)
+    _close(q_out, q_ref, 8e-3, "rotated queries")
+    _close(cache.pages, ref_cache.pages, 8e-3, "pages after the store")
+    if not writes:
+        assert torch.equal(cache.pages, untouched)
+    # unfused on this device: the same numbers up to the order of the norm's sum
+    keep = ops.fuse_qkv_epilogue
+    ops.fuse_qkv_epilogue = False
+    try:
+        q_two = torch.empty_like(q_out)
+        two = SimpleNamespace(**vars(cache))
+        two.pages = untouched.clone()
+        ops.qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, two, q_two, heads, kv, hd)
+    finally:
+        ops.fuse_qkv_epilogue = keep
+    _close(q_out, q_two, 8e-3, "fused against separate kernels")
+    assert (q_out != q_two).float().mean().item() < 0.02
 
 
 @pytest.mark.parametrize("vocab", [151936, 1009, 16384])

@@ -9,13 +9,14 @@
 // warps 2-5 read a finished accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes = rows
 // that its position in the warpgroup allows) and run the epilogue while the next tile's
 // products already fill the other accumulator.  Epilogues: store, accumulate into C (the
-// residual stream), or SwiGLU over 8 gate + 8 up columns into bfloat16.  Rows and columns past
+// residual stream), SwiGLU over 8 gate + 8 up columns into bfloat16, or (BN = 256) the QKV
+// epilogue of qkv_epilogue.cuh: head norm, rotation and the store into the paged cache.  Rows and columns past
 // M, N and K are zero-filled by TMA on the way in and skipped on the way out.
 //
 // The k order of the accumulation is fixed (ascending blocks of 64, 16 at a time), so an
 // output element does not depend on M or on the tile around it.  Every wait on an mbarrier
 // is bounded: on a timeout the block records status 2, frees its tensor memory and returns.
-#include "sm100.cuh"
+#include "qkv_epilogue.cuh"
 
 namespace {
 
@@ -31,7 +32,7 @@ template <int BN> struct Tile {
     static constexpr unsigned TMEM_COLS = 2 * BN;     // two accumulators
 };
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2, MODE_QKV = 3 };
 enum { TI_ERR_TIMEOUT = 2 };
 
 // silu(g) * u = g * u / (1 + e^-g) with the fast exponential and reciprocal (relative error about
@@ -43,8 +44,9 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    float* __restrict__ c, bf16* __restrict__ out_act, int m, int n, int k, int ldc,
-                    int ld_act, int mode, int* __restrict__ status) {
+                    const __grid_constant__ qkv::Epilogue qkv_e, float* __restrict__ c,
+                    bf16* __restrict__ out_act, int m, int n, int k, int ldc, int ld_act, int mode,
+                    int* __restrict__ status) {
     using T = Tile<BN>;
     constexpr int STAGES = T::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -134,8 +136,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
+            if constexpr (BN == 256) {
+                if (mode == MODE_QKV) {
+                    // this thread's 128 columns are one head of its token (BN / 2 == head size)
+                    const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
+                    qkv::head(qkv_e, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + col_half * (BN / 2)),
+                              row, item, row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+                }
+            }
 #pragma unroll 1
-            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
+            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2) && mode != MODE_QKV; c0 += 32) {
                 float v[32];
                 tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c0), v);
                 const int col = n0 + c0;
@@ -185,6 +195,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// table[t] = {cos(pos_t * inv_freq[0 .. half)), sin(...)}: the rotation of every token of a step.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  int num_tokens, int half, float* __restrict__ table) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_tokens * half) return;
+    const int t = i / half, k = i % half;
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[k], &sn, &cs);
+    table[(size_t)t * 2 * half + k] = cs;
+    table[(size_t)t * 2 * half + half + k] = sn;
+}
+
+int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c, void* out_act, int m, int n,
+                 int k, int lda, int ldw, int ldc, int ld_act, int mode, bool wide, int* status, void* stream) {
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int tiles_m = (m + BM - 1) / BM;
+    CUtensorMap map_a, map_w;
+    if (int rc = make_map_bf16(&map_a, a, m, k, lda, BM, "gemm_tcgen05")) return rc;
+    if (int rc = make_map_bf16(&map_w, w, n, k, ldw, wide ? 256 : 128, "gemm_tcgen05")) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::SMEM);
+        if (e2 == cudaSuccess)
+            e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<128>::SMEM);
+        if (e2 != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e2));
+        configured = true;
+    }
+    if (wide) {
+        const int tiles = tiles_m * ((n + 255) / 256);
+        gemm_tcgen05_kernel<256><<<tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM, (cudaStream_t)stream>>>(
+            map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    } else {
+        const int tiles = tiles_m * ((n + 127) / 128);
+        gemm_tcgen05_kernel<128><<<tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM, (cudaStream_t)stream>>>(
+            map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    }
+    return ti_check_launch("gemm_tcgen05");
+}
+
 }  // namespace
 
 extern "C" int ti_gemm_tcgen05_supported(int m, int n, int k, int lda, int ldw, int ldc, int mode) {
@@ -198,6 +251,7 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
                                int k, int lda, int ldw, int ldc, int ld_act, int mode, int* status,
                                void* stream) {
     if (m == 0 || n == 0) return 0;
+    TI_REQUIRE(mode >= MODE_STORE && mode <= MODE_SWIGLU, "gemm_tcgen05: mode %d", mode);
     TI_REQUIRE(ti_gemm_tcgen05_supported(m, n, k, lda, ldw, ldc, mode),
                "gemm_tcgen05: K=%d and the row strides %d, %d must be multiples of 8, N=%d a multiple "
                "of 4 (16 with SwiGLU)", k, lda, ldw, n);
@@ -208,30 +262,37 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const int tiles_m = (m + BM - 1) / BM;
     // wide tiles when they still give every SM one; else twice as many narrow ones
-    const bool wide = tiles_m * ((n + 255) / 256) >= sms;
-    CUtensorMap map_a, map_w;
-    if (int rc = make_map_bf16(&map_a, a, m, k, lda, BM, "gemm_tcgen05")) return rc;
-    if (int rc = make_map_bf16(&map_w, w, n, k, ldw, wide ? 256 : 128, "gemm_tcgen05")) return rc;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::SMEM);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Tile<128>::SMEM);
-        if (e != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    if (wide) {
-        const int tiles = tiles_m * ((n + 255) / 256);
-        gemm_tcgen05_kernel<256><<<tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM, (cudaStream_t)stream>>>(
-            map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
-    } else {
-        const int tiles = tiles_m * ((n + 127) / 128);
-        gemm_tcgen05_kernel<128><<<tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM, (cudaStream_t)stream>>>(
-            map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
-    }
-    return ti_check_launch("gemm_tcgen05");
+    const bool wide = ((m + BM - 1) / BM) * ((n + 255) / 256) >= sms;
+    return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, wide, status, stream);
+}
+
+// The QKV product of a prompt portion with the epilogue of qkv_epilogue.cuh (head size 128), on
+// 128 x 256 tiles: w is [(heads + 2 kv_heads) * 128, k]; nothing but q_out and the pages is written.
+extern "C" int ti_gemm_tcgen05_qkv(const void* a, const void* w, int m, int k, int lda, int ldw,
+                                   const float* q_weight, const float* k_weight, float eps,
+                                   const float* table, const int* positions, const int* req_of_tok,
+                                   const int* block_table, int bt_stride, void* pages, int num_pages,
+                                   int page_size, int write_kv, int num_heads, int num_kv_heads,
+                                   void* q_out, int* status, void* stream) {
+    if (m == 0) return 0;
+    const int n = (num_heads + 2 * num_kv_heads) * qkv::HEAD_DIM;
+    TI_REQUIRE(k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tcgen05_qkv: K=%d and the row strides %d, %d must be multiples of 8", k, lda, ldw);
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+               (uintptr_t)pages % 16 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)q_weight % 16 == 0 &&
+               (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned");
+    const qkv::Epilogue e{q_weight, k_weight, eps, table, positions, req_of_tok, block_table, bt_stride,
+                          (bf16*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, (bf16*)q_out};
+    return launch_tiles(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, true, status, stream);
+}
+
+// table [num_tokens][2][half] float32: cosines then sines of positions[t] * inv_freq[k].
+extern "C" int ti_rope_table(const int* positions, const float* inv_freq, int num_tokens, int half,
+                             float* table, void* stream) {
+    if (num_tokens == 0 || half == 0) return 0;
+    const int total = num_tokens * half;
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, num_tokens,
+                                                                             half, table);
+    return ti_check_launch("rope_table");
 }

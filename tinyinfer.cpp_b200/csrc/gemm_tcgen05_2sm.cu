@@ -6,7 +6,8 @@
 // crosses from L2 to an SM; the one-SM kernel is bound by that path.  The leader (rank 0) issues
 // tcgen05.mma.cta_group::2 (256 x 256 x 16): the tensor cores of both SMs read both blocks' shared
 // memory at the same offsets, and each SM accumulates its 128 rows x 256 columns in its own tensor
-// memory.  Both blocks run the same epilogue on their own rows (store, accumulate, or SwiGLU).
+// memory.  Both blocks run the same epilogue on their own rows (store, accumulate, SwiGLU, or the
+// QKV epilogue of qkv_epilogue.cuh: head norm, rotation and the store into the paged cache).
 //
 // Barriers: a stage's "full" barrier lives in the leader and counts the bytes of both blocks' TMA
 // loads (loads of the peer name the leader's barrier); "empty" and "accumulator full" are signalled
@@ -14,7 +15,7 @@
 // is multicast); "accumulator empty" collects arrivals of both blocks' epilogue warps at the
 // leader.  Every wait is bounded; on a timeout the block records status 2 and both blocks leave
 // through the cluster barrier at the end, freeing their tensor memory.
-#include "sm100.cuh"
+#include "qkv_epilogue.cuh"
 
 namespace {
 
@@ -34,7 +35,7 @@ template <int BN> struct Pair {
     static constexpr unsigned TMEM_COLS = 2 * BN;
 };
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2, MODE_QKV = 3 };
 enum { TI_ERR_TIMEOUT = 2 };
 
 // silu(g) * u = g * u / (1 + e^-g) with the fast exponential and reciprocal (relative error about
@@ -88,8 +89,9 @@ __device__ __forceinline__ void umma_commit_pair(void* bar) {
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        float* __restrict__ c, bf16* __restrict__ out_act, int m, int n, int k, int ldc,
-                        int ld_act, int mode, int* __restrict__ status) {
+                        const __grid_constant__ qkv::Epilogue qkv_e, float* __restrict__ c,
+                        bf16* __restrict__ out_act, int m, int n, int k, int ldc, int ld_act, int mode,
+                        int* __restrict__ status) {
     constexpr int STAGES = Pair<BN>::STAGES, STAGE_B = Pair<BN>::STAGE_B;
     constexpr unsigned TMEM_COLS = Pair<BN>::TMEM_COLS;
     extern __shared__ unsigned char smem_raw[];
@@ -182,8 +184,14 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             if (!ok) break;
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
+            if (mode == MODE_QKV) {
+                // this thread's 128 columns are one head of its token (BN / 2 == head size)
+                const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
+                qkv::head(qkv_e, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + col_half * (BN / 2)),
+                          row, item, row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+            }
 #pragma unroll 1
-            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
+            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2) && mode != MODE_QKV; c0 += 32) {
                 float v[32];
                 tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c0), v);
                 const int col = n0 + c0;
@@ -240,18 +248,10 @@ extern "C" int ti_gemm_tcgen05_2sm_supported(int m, int n, int k, int lda, int l
     return n % 4 == 0 && ldc % 4 == 0;
 }
 
-// Same contract as ti_gemm_tcgen05; meant for outputs with at least as many 256 x 256 tiles as the GPU
-// has pairs of SMs.
-extern "C" int ti_gemm_tcgen05_2sm(const void* a, const void* w, float* c, void* out_act, int m, int n,
-                                   int k, int lda, int ldw, int ldc, int ld_act, int mode, int* status,
-                                   void* stream) {
-    if (m == 0 || n == 0) return 0;
-    TI_REQUIRE(ti_gemm_tcgen05_2sm_supported(m, n, k, lda, ldw, ldc, mode),
-               "gemm_tcgen05_2sm: K=%d and the row strides %d, %d must be multiples of 8, N=%d a multiple "
-               "of 4 (16 with SwiGLU)", k, lda, ldw, n);
-    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0, "gemm_tcgen05_2sm: operands must be 16-byte aligned");
-    TI_REQUIRE(mode == MODE_SWIGLU ? ((uintptr_t)out_act % 16 == 0 && ld_act % 8 == 0) : (uintptr_t)c % 16 == 0,
-               "gemm_tcgen05_2sm: the output must be 16-byte aligned");
+namespace {
+
+int launch_pairs(const void* a, const void* w, const qkv::Epilogue& e, float* c, void* out_act, int m, int n,
+                 int k, int lda, int ldw, int ldc, int ld_act, int mode, int* status, void* stream) {
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -260,14 +260,52 @@ extern "C" int ti_gemm_tcgen05_2sm(const void* a, const void* w, float* c, void*
     if (int rc = make_map_bf16(&map_w, w, n, k, ldw, 128, "gemm_tcgen05_2sm")) return rc;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<256>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<256>::SMEM);
-        if (e != cudaSuccess) return ti_fail("gemm_tcgen05_2sm: %s", cudaGetErrorString(e));
+        cudaError_t e2 = cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<256>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<256>::SMEM);
+        if (e2 != cudaSuccess) return ti_fail("gemm_tcgen05_2sm: %s", cudaGetErrorString(e2));
         configured = true;
     }
     const int tiles = ((m + BM - 1) / BM) * ((n + 255) / 256);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
     gemm_tcgen05_2sm_kernel<256><<<2 * pairs, THREADS, Pair<256>::SMEM, (cudaStream_t)stream>>>(
-        map_a, map_w, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+        map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
     return ti_check_launch("gemm_tcgen05_2sm");
+}
+
+}  // namespace
+
+// Same contract as ti_gemm_tcgen05; meant for outputs with at least as many 256 x 256 tiles as the GPU
+// has pairs of SMs.
+extern "C" int ti_gemm_tcgen05_2sm(const void* a, const void* w, float* c, void* out_act, int m, int n,
+                                   int k, int lda, int ldw, int ldc, int ld_act, int mode, int* status,
+                                   void* stream) {
+    if (m == 0 || n == 0) return 0;
+    TI_REQUIRE(mode >= MODE_STORE && mode <= MODE_SWIGLU, "gemm_tcgen05_2sm: mode %d", mode);
+    TI_REQUIRE(ti_gemm_tcgen05_2sm_supported(m, n, k, lda, ldw, ldc, mode),
+               "gemm_tcgen05_2sm: K=%d and the row strides %d, %d must be multiples of 8, N=%d a multiple "
+               "of 4 (16 with SwiGLU)", k, lda, ldw, n);
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0, "gemm_tcgen05_2sm: operands must be 16-byte aligned");
+    TI_REQUIRE(mode == MODE_SWIGLU ? ((uintptr_t)out_act % 16 == 0 && ld_act % 8 == 0) : (uintptr_t)c % 16 == 0,
+               "gemm_tcgen05_2sm: the output must be 16-byte aligned");
+    return launch_pairs(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, status, stream);
+}
+
+// The QKV product of a prompt portion with the epilogue of qkv_epilogue.cuh (head size 128):
+// w is [(heads + 2 kv_heads) * 128, k]; nothing but q_out and the pages is written.
+extern "C" int ti_gemm_tcgen05_2sm_qkv(const void* a, const void* w, int m, int k, int lda, int ldw,
+                                       const float* q_weight, const float* k_weight, float eps,
+                                       const float* table, const int* positions, const int* req_of_tok,
+                                       const int* block_table, int bt_stride, void* pages, int num_pages,
+                                       int page_size, int write_kv, int num_heads, int num_kv_heads,
+                                       void* q_out, int* status, void* stream) {
+    if (m == 0) return 0;
+    const int n = (num_heads + 2 * num_kv_heads) * qkv::HEAD_DIM;
+    TI_REQUIRE(k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tcgen05_2sm_qkv: K=%d and the row strides %d, %d must be multiples of 8", k, lda, ldw);
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+               (uintptr_t)pages % 16 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)q_weight % 16 == 0 &&
+               (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_2sm_qkv: operands must be 16-byte aligned");
+    const qkv::Epilogue e{q_weight, k_weight, eps, table, positions, req_of_tok, block_table, bt_stride,
+                          (bf16*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, (bf16*)q_out};
+    return launch_pairs(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, status, stream);
 }

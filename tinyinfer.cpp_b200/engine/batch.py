@@ -57,7 +57,7 @@ class StepBatch:
     max_position: int = 0            # the model's longest context (bounds that do not vary by step)
     packed_size: int = 0             # int32 values in the packed device buffer
     block_tables: list[torch.Tensor] = field(default_factory=list)   # per group [R, blocks]
-    scratch: dict = field(default_factory=dict)   # per-step values kernels may cache
+    scratch: dict = field(default_factory=dict)   # what kernels derive from the step, kept for one forward pass
 
 
 def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],

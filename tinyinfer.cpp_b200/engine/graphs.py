@@ -56,7 +56,6 @@ class _Bucket:
             q_start_dev=d[b:2 * b], ctx_len_dev=d[2 * b:3 * b], logit_rows=ar,
             state_slots=d[3 * b:4 * b], decode_rows=ar, chunk_rows=ar[:0], chunk_tiles=ar[:0].view(-1, 3), chunk_tiles_big=ar[:0].view(-1, 3),
             max_position=engine.plan.max_position, block_tables=tables)
-        self.batch.scratch["graph"] = True
         self.graph = None
         self.logits = None
         self.launches = 0
@@ -161,7 +160,6 @@ class StepGraphs:
         probe = build_step_batch(entries, starts, tables, slots, **build)
         buffer = torch.zeros(probe.packed_size, dtype=torch.int32, device=eng.device)
         batch = build_step_batch(entries, starts, tables, slots, dev_buffer=buffer, **build)
-        batch.scratch["graph"] = True
         logits = eng.forward(batch)                    # this step, eagerly
         torch.cuda.synchronize(eng.device)
         graph = torch.cuda.CUDAGraph()

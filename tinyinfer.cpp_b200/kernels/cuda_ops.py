@@ -16,6 +16,9 @@ gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
     both take pre_norm=(x, weight, eps, dtype) instead of their first operand (None): the operand
     is then rmsnorm(x) * weight rounded to dtype, made inside the product's launch where it can be
 qk_norm_rope_store(...)                      q/k head norm, rotation, k/v into pages, q out
+qkv_rope_store(h, w, ..., pre_norm=None)     the QKV product followed by qk_norm_rope_store, in one
+                                             launch where the kernels can (step.scratch holds what
+                                             they derive from the step, for one forward pass)
 paged_attention(...)                         causal attention over the pages of each token's request
 argmax(logits, out) / sample(...)            next token per row
 """
@@ -76,6 +79,7 @@ class CudaOps:
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
         self.fuse_pre_norm = True         # the few-rows product normalises its own input rows
+        self.fuse_qkv_epilogue = True     # the prompt QKV product norms, rotates and stores its heads
         # few-rows products on tcgen05 with K split over blocks: for weights of at least this many
         # bytes (None: never), below which the direct-to-register kernel's shorter chain wins
         # (measured: 4096 x 4096 is even at 16 rows, larger weights gain 15-50 %)
@@ -126,6 +130,11 @@ class CudaOps:
             b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
+            qkv_args = [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
+                        _i, _i, _vp, _vp, _vp]
+            b.ti_gemm_tcgen05_qkv.argtypes = qkv_args
+            b.ti_gemm_tcgen05_2sm_qkv.argtypes = qkv_args
+            b.ti_rope_table.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
             b.ti_attn_prefill_supported.argtypes = [_i, _i]
             b.ti_attn_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f,
                                           _vp, _vp, _vp]
@@ -337,6 +346,55 @@ class CudaOps:
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
             cache.page_size, int(bool(cache.writes)), t, num_heads, num_kv_heads, head_dim,
             q_out.data_ptr(), _code(q_out, "q"), self.status.data_ptr(), self._stream()))
+
+    def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+                       num_heads, num_kv_heads, head_dim, pre_norm=None):
+        """``qk_norm_rope_store`` of ``h @ w_qkv.T`` (or of the product of ``pre_norm``'s normed
+        rows).  Prompt portions with head size 128 run as one tcgen05 product whose epilogue
+        norms, rotates and stores each head, so the float32 product never reaches memory."""
+        t = q_out.shape[0]
+        pages, bt = cache.pages, cache.block_table
+        fused = (self.fuse_qkv_epilogue and t > 64 and head_dim == 128 and w_qkv.dtype == torch.bfloat16
+                 and q_out.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
+                 and (h is None and pre_norm[3] == torch.bfloat16 or h is not None and h.dtype == torch.bfloat16)
+                 and w_qkv.stride(1) == 1 and w_qkv.stride(0) % 8 == 0 and w_qkv.shape[1] % 8 == 0
+                 and w_qkv.data_ptr() % 16 == 0 and q_out.is_contiguous() and pages.is_contiguous()
+                 and q_weight.data_ptr() % 16 == 0 and k_weight.data_ptr() % 16 == 0)
+        if not fused:
+            qkv = torch.empty((t, w_qkv.shape[0]), dtype=torch.float32, device=q_out.device)
+            self.linear(h, w_qkv, qkv, pre_norm=pre_norm)
+            self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+                                    num_heads, num_kv_heads, head_dim)
+            return
+        if h is None:
+            x, norm_w, norm_eps, dtype = pre_norm
+            h = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
+            self.rmsnorm(x, norm_w, norm_eps, h)
+        n, k = w_qkv.shape
+        _need(h.shape == (t, k) and h.stride(1) == 1 and n == (num_heads + 2 * num_kv_heads) * head_dim,
+              "qkv_rope_store: shapes do not agree")
+        _need(tuple(pages.shape[1:]) == (2, num_kv_heads, cache.page_size, head_dim),
+              "qkv_rope_store: page layout")
+        _need(bt.dtype == torch.int32 and bt.stride(1) == 1, "qkv_rope_store: block table int32")
+        _need(inv_freq.shape[0] == head_dim // 2 and inv_freq.dtype == torch.float32,
+              "qkv_rope_store: the rotation table must hold head_dim/2 float32 values")
+        key = ("rope_table", inv_freq.data_ptr())
+        table = step.scratch.get(key)
+        if table is None:                       # once per forward pass: the same for every layer
+            table = torch.empty((t, 2, head_dim // 2), dtype=torch.float32, device=q_out.device)
+            self._ok(self.bf16.ti_rope_table(step.positions.data_ptr(), inv_freq.data_ptr(), t,
+                                             head_dim // 2, table.data_ptr(), self._stream()), self.bf16)
+            step.scratch[key] = table
+        fn = (self.bf16.ti_gemm_tcgen05_2sm_qkv if self._tc_gemm(t, n) is self.bf16.ti_gemm_tcgen05_2sm
+              else self.bf16.ti_gemm_tcgen05_qkv)
+        if h.data_ptr() % 16 or h.stride(0) % 8:
+            h = h.contiguous()
+        self._ok(fn(h.data_ptr(), w_qkv.data_ptr(), t, k, h.stride(0), w_qkv.stride(0),
+                    q_weight.data_ptr(), k_weight.data_ptr(), float(eps), table.data_ptr(),
+                    step.positions.data_ptr(), step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0),
+                    pages.data_ptr(), pages.shape[0], cache.page_size, int(bool(cache.writes)),
+                    num_heads, num_kv_heads, q_out.data_ptr(), self.status.data_ptr(), self._stream()),
+                 self.bf16)
 
     def decode_splits(self, rows: int, num_kv_heads: int, max_position: int, head_dim: int = 128) -> int:
         """In how many blocks the keys of a decoding row are cut, per kv head.  It depends on

@@ -73,15 +73,10 @@ class Attention(Part):
         t = residual.shape[0]
         dev = residual.device
         act = step.act_dtype if h is None else h.dtype
-        qkv = torch.empty((t, self.nq + 2 * self.nk), dtype=torch.float32, device=dev)
-        if h is None:
-            ops.linear(None, self.w_qkv, qkv, pre_norm=(residual, pre_norm.weight, pre_norm.eps, act))
-        else:
-            ops.linear(h, self.w_qkv, qkv)
         q = torch.empty((t, self.nq), dtype=act, device=dev)
-        ops.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.eps,
-                               self.position.table(dev), step, cache, q,
-                               self.num_heads, self.num_kv_heads, self.head_dim)
+        pre = None if h is not None else (residual, pre_norm.weight, pre_norm.eps, act)
+        ops.qkv_rope_store(h, self.w_qkv, self.q_norm, self.k_norm, self.eps, self.position.table(dev),
+                           step, cache, q, self.num_heads, self.num_kv_heads, self.head_dim, pre_norm=pre)
         out = torch.empty((t, self.nq), dtype=act, device=dev)
         ops.paged_attention(q, step, cache, out, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.window, self.scale)

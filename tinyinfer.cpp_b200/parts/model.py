@@ -71,6 +71,7 @@ class CausalLM:
 
     # ---- forward -------------------------------------------------------------------------
     def forward(self, ops, step, cache_views: Mapping[tuple[int, bool], object]) -> torch.Tensor:
+        step.scratch.clear()           # what kernels derived from the step in an earlier pass is stale
         x = torch.empty((step.num_tokens, self.plan.hidden_size), dtype=torch.float32,
                         device=step.token_ids.device)
         self.embedding.forward(ops, step.token_ids, x)

@@ -14,6 +14,9 @@ import torch
 from .base import Part, register_part
 
 
+_TABLES: dict[tuple, torch.Tensor] = {}      # layers with the same constants share one device tensor
+
+
 class RopeNeox(Part):
     category = "position"
 
@@ -22,7 +25,6 @@ class RopeNeox(Part):
             raise ValueError(f"rotary head_dim {head_dim} must be even")
         self.head_dim = int(head_dim)
         self.theta = float(theta)
-        self._tables: dict[str, torch.Tensor] = {}
 
     def inv_freq(self) -> torch.Tensor:
         half = self.head_dim // 2
@@ -31,10 +33,10 @@ class RopeNeox(Part):
                          -2.0 * k / self.head_dim).to(torch.float32)
 
     def table(self, device) -> torch.Tensor:
-        key = str(device)
-        if key not in self._tables:
-            self._tables[key] = self.inv_freq().to(device)
-        return self._tables[key]
+        key = (self.head_dim, self.theta, str(device))
+        if key not in _TABLES:
+            _TABLES[key] = self.inv_freq().to(device)
+        return _TABLES[key]
 
 
 register_part("position", "rope_neox", RopeNeox)
