@@ -86,10 +86,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    pdl_launch();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    pdl_wait();        // queries, keys and values come from the kernel before
     const unsigned tmem_o = tmem_base + 256;
 
     bool ok = true;
@@ -345,8 +347,8 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
         configured = true;
     }
     dim3 grid(num_heads, num_tiles);
-    attn_prefill_tc_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
-        map_q, map_kv, tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads,
-        num_kv_heads, window, scale * LOG2E, (bf16*)out, status);
+    ti_launch_pdl(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,
+                  tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads, num_kv_heads,
+                  window, scale * LOG2E, (bf16*)out, status);
     return ti_check_launch("attn_prefill_tc");
 }

@@ -73,10 +73,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tmem_alloc(tmem_slot, T::TMEM_COLS);
     }
+    pdl_launch();
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
+    pdl_wait();        // the set-up above overlaps the end of the kernel before; its results are read below
 
     // tiles in order of m fastest, so that blocks running together share few panels of W
     bool ok = true;
@@ -198,6 +200,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // table[t] = {cos(pos_t * inv_freq[0 .. half)), sin(...)}: the rotation of every token of a step.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   int num_tokens, int half, float* __restrict__ table) {
+    pdl_launch();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= num_tokens * half) return;
     const int t = i / half, k = i % half;
@@ -228,12 +232,12 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
     }
     if (wide) {
         const int tiles = tiles_m * ((n + 255) / 256);
-        gemm_tcgen05_kernel<256><<<tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM, (cudaStream_t)stream>>>(
-            map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+        ti_launch_pdl(gemm_tcgen05_kernel<256>, tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM,
+                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
     } else {
         const int tiles = tiles_m * ((n + 127) / 128);
-        gemm_tcgen05_kernel<128><<<tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM, (cudaStream_t)stream>>>(
-            map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+        ti_launch_pdl(gemm_tcgen05_kernel<128>, tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM,
+                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
     }
     return ti_check_launch("gemm_tcgen05");
 }
@@ -292,7 +296,7 @@ extern "C" int ti_rope_table(const int* positions, const float* inv_freq, int nu
                              float* table, void* stream) {
     if (num_tokens == 0 || half == 0) return 0;
     const int total = num_tokens * half;
-    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, num_tokens,
-                                                                             half, table);
+    ti_launch_pdl(rope_table_kernel, (total + 255) / 256, 256, 0, (cudaStream_t)stream, positions, inv_freq,
+                  num_tokens, half, table);
     return ti_check_launch("rope_table");
 }

@@ -123,11 +123,13 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                      ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
     }
+    pdl_launch();
     tc_fence_before();
     __syncthreads();
     cluster_sync();                                      // both blocks' barriers exist before any use
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    pdl_wait();        // the set-up above overlaps the end of the kernel before; its results are read below
 
     bool ok = true;
     if (warp == 0) {
@@ -267,8 +269,8 @@ int launch_pairs(const void* a, const void* w, const qkv::Epilogue& e, float* c,
     }
     const int tiles = ((m + BM - 1) / BM) * ((n + 255) / 256);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-    gemm_tcgen05_2sm_kernel<256><<<2 * pairs, THREADS, Pair<256>::SMEM, (cudaStream_t)stream>>>(
-        map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    ti_launch_pdl(gemm_tcgen05_2sm_kernel<256>, 2 * pairs, THREADS, Pair<256>::SMEM, (cudaStream_t)stream,
+                  map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
     return ti_check_launch("gemm_tcgen05_2sm");
 }
 

@@ -73,6 +73,53 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
     }
 }
 
+// The warp-per-row norm for rows of at most 2,048 elements: a lane keeps its up to sixteen 16-byte
+// pieces in registers, so the row is read once and all its loads are in flight together.  The sum
+// of squares runs in the same order as in rmsnorm_warp_kernel.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                        const int* __restrict__ rows, float eps, int n, int num_rows,
+                        TO* __restrict__ out) {
+    constexpr int MAXV = 16;
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= num_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const int n4 = n >> 2;
+    float4 v[MAXV];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j)
+        if (lane + 32 * j < n4) v[j] = xr[lane + 32 * j];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        if (lane + 32 * j < n4) {
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+    TO* o = out + (size_t)r * n;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= n4) continue;
+        const float4 g = w4[i];
+        const float4 y = make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z,
+                                     v[j].w * inv * g.w);
+        if constexpr (sizeof(TO) == 2) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(y.x, y.y), b = __floats2bfloat162_rn(y.z, y.w);
+            *reinterpret_cast<uint2*>(o + 4 * i) =
+                make_uint2(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b));
+        } else {
+            *reinterpret_cast<float4*>(o + 4 * i) = y;
+        }
+    }
+}
+
 // The same norm with one block per row for few rows whose length is a multiple of 4 and at most
 // 16 * THREADS: a thread keeps its up to four 16-byte pieces of the row in registers, so the row
 // is read once and all loads are in flight together; the weights are fetched before the wait on
@@ -264,7 +311,11 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
         (uintptr_t)x % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0) {
         // many rows: a warp per row.  (Few rows keep a block per row: more threads per row.)
         const unsigned grid = (unsigned)((num_rows + 7) / 8);
-        if (out_dtype == TI_BF16)
+        if (out_dtype == TI_BF16 && n <= 2048)
+            ti_launch_pdl(rmsnorm_warp_reg_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
+        else if (n <= 2048)
+            ti_launch_pdl(rmsnorm_warp_reg_kernel<float>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (float*)out);
+        else if (out_dtype == TI_BF16)
             ti_launch_pdl(rmsnorm_warp_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
         else
             ti_launch_pdl(rmsnorm_warp_kernel<float>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (float*)out);
