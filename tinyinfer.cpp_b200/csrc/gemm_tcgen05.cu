@@ -134,10 +134,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            // narrow tiles that add to C fetch C's old values while the products still run
+            constexpr int OLD = BN == 128 ? BN / 8 : 1;
+            float4 old[OLD];
+            if constexpr (BN == 128) {
+                if (mode == MODE_ACCUMULATE) {
+                    const float* src = c + (size_t)row * ldc + n0 + col_half * (BN / 2);
+#pragma unroll
+                    for (int i = 0; i < OLD; ++i)
+                        old[i] = row < m && n0 + col_half * (BN / 2) + 4 * i < n
+                                     ? __ldcg(reinterpret_cast<const float4*>(src + 4 * i))
+                                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
             ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int row = m0 + quarter * 32 + lane;
             if constexpr (BN == 256) {
                 if (mode == MODE_QKV) {
                     // this thread's 128 columns are one head of its token (BN / 2 == head size)
@@ -146,8 +159,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                               row, item, row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
                 }
             }
-#pragma unroll 1
-            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2) && mode != MODE_QKV; c0 += 32) {
+#pragma unroll
+            for (int cc = 0; cc < BN / 64; ++cc) {
+                if (mode == MODE_QKV) break;
+                const int c0 = col_half * (BN / 2) + cc * 32;
                 float v[32];
                 tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c0), v);
                 const int col = n0 + c0;
@@ -175,8 +190,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (col + i >= n) break;
                         float4 x = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                         if (mode == MODE_ACCUMULATE) {
-                            const float4 old = *reinterpret_cast<const float4*>(dst + i);
-                            x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                            float4 was;
+                            if constexpr (BN == 128) was = old[cc * 8 + i / 4];
+                            else was = *reinterpret_cast<const float4*>(dst + i);
+                            x.x += was.x; x.y += was.y; x.z += was.z; x.w += was.w;
                         }
                         *reinterpret_cast<float4*>(dst + i) = x;
                     }
