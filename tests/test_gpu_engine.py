@@ -117,6 +117,53 @@ def test_graph_replay_equals_eager_bit_for_bit(tmp_path_factory, dtype):
     assert torch.equal(results[0], results[1]), "graph replay and eager steps differ"
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_graph_replay_with_requests_coming_going_and_changing_rows(tmp_path_factory, name):
+    """Replayed decode steps keep a host mirror of each row's block table and send only what a
+    request gained.  Here requests finish, new ones take their rows, the order of the batch
+    changes, an id is used again and (configuration C) windows give pages back: every step must
+    equal the eager engine bit for bit."""
+    from tinyinfer_b200 import StepEntry
+    d = make_model(tmp_path_factory.getbasetemp(), name)
+    vocab = TINY[name]["vocab_size"]
+    limit = TINY[name]["max_position_embeddings"]
+    rng = torch.Generator().manual_seed(5)
+    engines = [_engine(d, "bfloat16", max_tokens=4096), _engine(d, "bfloat16", max_tokens=4096)]
+    live, fresh, out = [], 0, [[], []]
+    lengths = {}
+    for step in range(70):
+        if step % 9 == 0 and len(live) < 4:                       # a new request joins
+            rid = f"r{fresh % 5}"                                 # ids come round again
+            fresh += 1
+            if rid not in live:
+                prompt = random_tokens(vocab, 5 + 13 * (fresh % 4), seed=fresh)
+                for eng in engines:
+                    eng.step([StepEntry(rid, prompt, [])])
+                live.append(rid)
+                lengths[rid] = len(prompt)
+        if step % 13 == 12 and live:                              # the oldest one finishes
+            gone = live.pop(0)
+            for eng in engines:
+                eng.finish(gone)
+        if step % 7 == 6:                                         # the batch changes its order
+            live = live[1:] + live[:1]
+        live = [r for r in live if lengths[r] < limit - 1]
+        if not live:
+            continue
+        toks = torch.randint(0, vocab, (len(live),), generator=rng).tolist()
+        entries = [StepEntry(r, [t], [0]) for r, t in zip(live, toks)]
+        out[0].append(engines[0].step(entries).clone())
+        out[1].append(engines[1].decode_step(entries).clone())
+        for r in live:
+            lengths[r] += 1
+    assert len(out[0]) > 50
+    for a, b in zip(out[0], out[1]):
+        assert torch.equal(a, b), "graph replay and eager steps differ"
+    for eng in engines:
+        eng.ops.check_status()
+        eng.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_step_graphs_equal_eager_bit_for_bit(tmp_path_factory, dtype):
     """Steps of a shape seen before are replayed from CUDA graphs: prompt portions of the same

@@ -101,6 +101,8 @@ class CacheManager:
         self.state_slots = IdPool(max_requests, "state slot")
         self._lengths: dict[Hashable, int] = {}
         self._state_slot: dict[Hashable, int] = {}
+        self._version: dict[Hashable, int] = {}
+        self._versions = 0
         if device is not None:
             for g in self.groups:
                 s = g.spec
@@ -121,10 +123,21 @@ class CacheManager:
         slot = self.state_slots.take()
         self._lengths[req] = 0
         self._state_slot[req] = slot
+        self._touch(req)
         for g in self.groups:
             g.tables[req] = []
         for t in self._state_storage.values():
             t[slot].zero_()
+
+    def _touch(self, req: Hashable) -> None:
+        self._versions += 1
+        self._version[req] = self._versions
+
+    def table_version(self, req: Hashable) -> int:
+        """A number that changes whenever the request's block tables change otherwise than by
+        gaining entries at their end (the request is new, or a window has passed some pages):
+        who mirrors the tables elsewhere copies only the new entries while it stays the same."""
+        return self._version[req]
 
     def has_request(self, req: Hashable) -> bool:
         return req in self._lengths
@@ -182,12 +195,15 @@ class CacheManager:
             raise OutOfPages(
                 f"{len(new)} new requests, {self.state_slots.num_free} request slots are free")
         need = [0] * len(self.groups)
+        per_item = []
         for req, n in items:
             end = self._lengths.get(req, 0) + n
             if max_position is not None and end > max_position:
                 raise ValueError(
                     f"request {req!r} would reach {end} tokens; the model allows {max_position}")
-            for g, k in enumerate(self.pages_needed(req, n)):
+            mine = self.pages_needed(req, n)
+            per_item.append(mine)
+            for g, k in enumerate(mine):
                 need[g] += k
         for g, k in enumerate(need):
             if k > self.groups[g].pool.num_free:
@@ -195,7 +211,14 @@ class CacheManager:
                     f"the step needs {k} pages of group {g}, {self.groups[g].pool.num_free} are free")
         for req in new:
             self.add_request(req)
-        return [self.append(req, n) for req, n in items]
+        starts = []
+        for (req, n), mine in zip(items, per_item):          # the pages are there: hand them out
+            for k, g in zip(mine, self.groups):
+                if k:
+                    g.tables[req].extend(g.pool.take() for _ in range(k))
+            starts.append(self._lengths[req])
+            self._lengths[req] += n
+        return starts
 
     def release_passed(self, req: Hashable) -> int:
         """Give back pages that lie wholly behind a window.  Returns how many were freed."""
@@ -210,6 +233,8 @@ class CacheManager:
                     g.pool.give_back(table[b])
                     table[b] = RELEASED
                     freed += 1
+        if freed:
+            self._touch(req)
         return freed
 
     def free_request(self, req: Hashable) -> None:
@@ -221,6 +246,7 @@ class CacheManager:
                     g.pool.give_back(page)
         self.state_slots.give_back(self._state_slot.pop(req))
         del self._lengths[req]
+        del self._version[req]
 
     # ---- what a step reads ----------------------------------------------------------------
     def block_table(self, group: int, req: Hashable) -> list[int]:

@@ -59,34 +59,70 @@ class _Bucket:
         self.graph = None
         self.logits = None
         self.launches = 0
+        # host mirror of the packed integers and what each row holds
+        self.mirror = np.zeros(self.total, dtype=np.int32)
+        self.row_req: list = [None] * b
+        self.row_version = [0] * b
+        self.row_blocks = [[0] * groups for _ in range(b)]
+        for i in range(b):
+            self._reset_row(i, cache)
+            self.row_req[i] = _PADDING
 
     def fill(self, engine, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
+        """Stage the step's integers and start their copy to the device.  A host mirror keeps what
+        the rows held last time: a request that sits in the same row as before only gets the
+        block-table entries it has gained since (decoding adds a page every ``page_size`` steps)."""
         cache = engine.cache
         b, w = self.size, self.width
         n = len(entries)
+        m = self.mirror
+        for i, e in enumerate(entries):
+            req = e.req_id
+            if self.row_req[i] != req or cache.table_version(req) != self.row_version[i]:
+                self._reset_row(i, cache)
+                self.row_req[i] = req
+                self.row_version[i] = cache.table_version(req)
+                m[3 * b + i] = cache.state_slot(req)
+            have = self.row_blocks[i]
+            for g in range(len(cache.groups)):
+                tb = cache.block_table(g, req)
+                if len(tb) > have[g]:
+                    base = 4 * b + g * b * w + i * w
+                    m[base + have[g]: base + len(tb)] = tb[have[g]:]
+                    have[g] = len(tb)
+        for i in range(n, b):                                   # padding rows
+            if self.row_req[i] is not _PADDING:
+                self._reset_row(i, cache)
+                self.row_req[i] = _PADDING
+        m[0:n] = [int(e.tokens[0]) for e in entries]
+        m[b:b + n] = starts
+        m[2 * b:2 * b + n] = m[b:b + n] + 1
         turn = self.turn
         self.turn = (turn + 1) % len(self.hosts)
         if self.copied[turn] is not None:
             self.copied[turn].synchronize()
         host = self.hosts[turn]
-        buf = host.numpy()
-        buf[:4 * b] = 0
-        buf[2 * b:3 * b] = 1                                      # padding rows: one token
-        buf[3 * b:4 * b] = cache.max_requests                     # padding rows: spare state slot
-        buf[4 * b:] = cache.null_page
-        buf[0:n] = [int(e.tokens[0]) for e in entries]
-        buf[b:b + n] = starts
-        buf[2 * b:2 * b + n] = np.asarray(starts) + 1
-        buf[3 * b:3 * b + n] = [cache.state_slot(e.req_id) for e in entries]
-        for g in range(len(cache.groups)):
-            base = 4 * b + g * b * w
-            for i, e in enumerate(entries):
-                tb = cache.block_table(g, e.req_id)
-                buf[base + i * w: base + i * w + len(tb)] = tb
+        np.copyto(host.numpy(), m)
         self.dev.copy_(host, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
         self.copied[turn] = done
+
+    def _reset_row(self, i: int, cache) -> None:
+        """Row ``i`` as a padding row: token 0 at position 0 of a request of one token that owns
+        the spare state slot and only null pages."""
+        b, w, m = self.size, self.width, self.mirror
+        m[i] = 0
+        m[b + i] = 0
+        m[2 * b + i] = 1
+        m[3 * b + i] = cache.max_requests
+        for g in range(len(cache.groups)):
+            base = 4 * b + g * b * w + i * w
+            m[base:base + w] = cache.null_page
+        self.row_blocks[i] = [0] * len(cache.groups)
+
+
+_PADDING = object()
 
 
 class DecodeGraphs:
