@@ -3,7 +3,9 @@
 The toy architecture has a mixer with state of its own (a running mean over the request's
 tokens, kept in a fixed-size state slot), layers of different kinds, a layer that runs twice
 and an entry that reads the cache another entry wrote.  It is registered, built, loaded and
-stepped through the engine without a change to the framework's files.
+stepped through the engine without a change to the framework's files.  A second toy architecture
+has a feed-forward with a router and experts in some of its layers and a position encoding of
+its own.  Neither is a model of anyone's.
 """
 import math
 from dataclasses import dataclass
@@ -307,4 +309,167 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path):
         assert_close_logits(torch.cat(got[r]), plain[r], FP32_RTOL, f"toy request {r}")
     eng.finish("b")
     eng.finish("c")
+    eng.cache.check()
+
+
+# ---- a second toy architecture: a feed-forward with routing, another position encoding -----------
+
+def _register_routed_toy():
+    from tinyinfer_b200.config import Architecture, PartSpec, register_architecture
+    from tinyinfer_b200.config.plan import LayerPlan, ModelPlan, default_schedule
+    from tinyinfer_b200.parts import MATRIX, Part, WeightSpec, build_part, register_part
+
+    class SlowRope(Part):
+        """The rotation of rope_neox with every frequency divided by ``factor``."""
+        category = "position"
+
+        def __init__(self, head_dim, theta, factor):
+            self.inner = build_part("position", PartSpec("rope_neox", {"head_dim": head_dim, "theta": theta}))
+            self.factor = float(factor)
+            self._table = None
+
+        def table(self, device):
+            if self._table is None:
+                self._table = (self.inner.inv_freq() / self.factor).to(device)
+            return self._table
+
+    class TopOneExperts(Part):
+        """Each token goes to the expert with the largest router logit (float32): a SwiGLU of its
+        own.  The experts are the framework's swiglu parts; routing is done here."""
+        category = "ffn"
+
+        def __init__(self, hidden_size, intermediate_size, num_experts):
+            self.hidden, self.n = hidden_size, num_experts
+            spec = PartSpec("swiglu", {"hidden_size": hidden_size, "intermediate_size": intermediate_size})
+            self.experts = [build_part("ffn", spec) for _ in range(num_experts)]
+            self.router = None
+
+        def weight_specs(self):
+            specs = {"router.weight": WeightSpec((self.n, self.hidden), MATRIX)}
+            for e, part in enumerate(self.experts):
+                specs.update({f"experts.{e}.{k}": v for k, v in part.weight_specs().items()})
+            return specs
+
+        def load_weights(self, tensors, ops):
+            self.router = tensors["router.weight"].float().contiguous()
+            for e, part in enumerate(self.experts):
+                pre = f"experts.{e}."
+                part.load_weights({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)}, ops)
+
+        def forward(self, ops, h, residual, step):
+            logits = torch.empty((h.shape[0], self.n), dtype=torch.float32, device=h.device)
+            ops.linear(h, self.router, logits)
+            choice = logits.argmax(dim=-1)
+            for e, part in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    out = torch.zeros((rows.numel(), self.hidden), dtype=torch.float32, device=h.device)
+                    part.forward(ops, h[rows].contiguous(), out, step)
+                    residual.index_add_(0, rows, out)
+
+    register_part("position", "slow_rope", SlowRope)
+    register_part("ffn", "top_one_experts", TopOneExperts)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        hidden_size: int
+        vocab_size: int
+        intermediate_size: int
+        max_position_embeddings: int
+        num_experts: int
+
+        def to_dict(self):
+            return {**self.__dict__, "architectures": ["ToyRoutedForCausalLM"]}
+
+    def from_dict(cfg):
+        return RoutedConfig(*(cfg[k] for k in ("hidden_size", "vocab_size", "intermediate_size",
+                                               "max_position_embeddings", "num_experts")))
+
+    def build_plan(c):
+        norm = PartSpec("rmsnorm", {"size": c.hidden_size, "eps": 1e-5})
+        dense = PartSpec("swiglu", {"hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size})
+        routed = PartSpec("top_one_experts", {"hidden_size": c.hidden_size, "num_experts": c.num_experts,
+                                              "intermediate_size": c.intermediate_size})
+        att = PartSpec("attention", {
+            "hidden_size": c.hidden_size, "num_heads": 3, "num_kv_heads": 1, "head_dim": 32,
+            "qk_norm_eps": 1e-5, "window": None,
+            "position": PartSpec("slow_rope", {"head_dim": 32, "theta": 1e4, "factor": 4.0})})
+        layers = []
+        for i, ffn in enumerate([routed, dense, routed]):          # feed-forwards differ by layer
+            p = f"toy.{i}."
+            layers.append(LayerPlan(PartSpec("prenorm"), att, ffn, norm, norm,
+                                    {"mixer": p + "mixer.", "ffn": p + "ffn.",
+                                     "mixer_norm": p + "norm1.", "ffn_norm": p + "norm2."}))
+        return ModelPlan("ToyRoutedForCausalLM", c.hidden_size, c.vocab_size, c.max_position_embeddings,
+                         layers, default_schedule(len(layers)),
+                         PartSpec("embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}),
+                         norm, PartSpec("lm_head", {"vocab_size": c.vocab_size,
+                                                    "hidden_size": c.hidden_size, "tied": False}),
+                         {"embedding": "toy.embed.", "final_norm": "toy.norm.", "head": "toy.head."})
+
+    register_architecture(Architecture("ToyRoutedForCausalLM", from_dict, build_plan))
+
+
+def _routed_plain(w, tokens, num_experts):
+    """The routed toy model on a whole sequence; also the smallest gap between a token's two best
+    router logits, relative to the largest logit."""
+    s_len = len(tokens)
+    x = plain_embedding(w["toy.embed.weight"], torch.tensor(tokens))
+    ang = plain_rope_angles(torch.arange(s_len), 32, 1e4) / 4.0
+    gap = math.inf
+
+    def swiglu(p, h):
+        return plain_swiglu(h @ w[p + "gate_proj.weight"].to(F64).T,
+                            h @ w[p + "up_proj.weight"].to(F64).T) @ w[p + "down_proj.weight"].to(F64).T
+
+    for i in range(3):
+        p = f"toy.{i}.mixer."
+        h = plain_rmsnorm(x, w[f"toy.{i}.norm1.weight"], 1e-5)
+        q = plain_rope_neox(plain_rmsnorm((h @ w[p + "q_proj.weight"].to(F64).T).view(s_len, 3, 32),
+                                          w[p + "q_norm.weight"], 1e-5), ang)
+        k = plain_rope_neox(plain_rmsnorm((h @ w[p + "k_proj.weight"].to(F64).T).view(s_len, 1, 32),
+                                          w[p + "k_norm.weight"], 1e-5), ang)
+        v = (h @ w[p + "v_proj.weight"].to(F64).T).view(s_len, 1, 32)
+        x = x + plain_attention(q, k, v, 1.0 / math.sqrt(32)).reshape(s_len, 96) @ w[p + "o_proj.weight"].to(F64).T
+        h = plain_rmsnorm(x, w[f"toy.{i}.norm2.weight"], 1e-5)
+        p = f"toy.{i}.ffn."
+        if i == 1:
+            x = x + swiglu(p, h)
+            continue
+        logits = h @ w[p + "router.weight"].to(F64).T
+        top = logits.topk(2, dim=-1).values
+        gap = min(gap, ((top[:, 0] - top[:, 1]) / logits.abs().max()).min().item())
+        choice = logits.argmax(dim=-1)
+        y = torch.zeros_like(x)
+        for e in range(num_experts):
+            rows = (choice == e).nonzero().flatten()
+            y[rows] = swiglu(f"{p}experts.{e}.", h[rows])
+        x = x + y
+    return plain_rmsnorm(x, w["toy.norm.weight"], 1e-5) @ w["toy.head.weight"].to(F64).T, gap
+
+
+def test_toy_architecture_with_routing_and_another_position_encoding(tmp_path):
+    """A feed-forward with a router and experts (in some layers only) and a position encoding of
+    its own, both defined here, registered and run through the engine in portions and token by
+    token, against the plain functions."""
+    from tinyinfer_b200 import Engine, StepEntry, write_random_model
+    _register_routed_toy()
+    cfg = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "vocab_size": 150,
+           "intermediate_size": 80, "max_position_embeddings": 128, "num_experts": 3}
+    tokens = random_tokens(150, 60, seed=2)
+    for seed in range(20):           # a model whose routing does not hang on the last bits
+        d = str(tmp_path / f"routed{seed}")
+        write_random_model(d, cfg, seed=seed, dtype=torch.float32)
+        _, w = load_folder(d)
+        plain, gap = _routed_plain(w, tokens, 3)
+        if gap > 1e-3:
+            break
+    else:
+        pytest.fail("no seed gave a clear routing")
+    eng = Engine(d, dtype="float32", page_size=16, max_tokens=128, max_requests=2)
+    got = [eng.step([StepEntry("a", tokens[:23], list(range(23)))]).cpu(),
+           eng.step([StepEntry("a", tokens[23:41], list(range(18)))]).cpu()]
+    got += [eng.step([StepEntry("a", [t], [0])]).cpu() for t in tokens[41:]]
+    assert_close_logits(torch.cat(got), plain, FP32_RTOL, "routed toy")
+    eng.finish("a")
     eng.cache.check()
