@@ -37,26 +37,14 @@ class RefOps:
         inv = torch.rsqrt((src * src).mean(dim=-1, keepdim=True) + eps)
         out.copy_((src * inv * weight.to(F32)).to(out.dtype))
 
-    def _normed(self, pre_norm):
-        x, weight, eps, dtype = pre_norm
-        a = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
-        self.rmsnorm(x, weight, eps, a)
-        return a
-
-    def linear(self, a, w, out, accumulate=False, pre_norm=None):
-        if pre_norm is not None:                       # (x, weight, eps, dtype): a = norm(x)
-            assert a is None
-            a = self._normed(pre_norm)
+    def linear(self, a, w, out, accumulate=False):
         prod = a.to(F32) @ w.to(F32).T
         if accumulate:
             out.add_(prod)
         else:
             out.copy_(prod)
 
-    def gate_up_swiglu(self, h, w_gate_up, out, pre_norm=None):
-        if pre_norm is not None:
-            assert h is None
-            h = self._normed(pre_norm)
+    def gate_up_swiglu(self, h, w_gate_up, out):
         inter = out.shape[1]
         gu = h.to(F32) @ w_gate_up.to(F32).T
         gate, up = gu[:, :inter], gu[:, inter:]
@@ -93,9 +81,9 @@ class RefOps:
             cache.pages[page, 1, :, pos % ps, :] = v.to(cache.pages.dtype)
 
     def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
-                       num_heads, num_kv_heads, head_dim, pre_norm=None):
+                       num_heads, num_kv_heads, head_dim):
         qkv = torch.empty((q_out.shape[0], w_qkv.shape[0]), dtype=F32, device=q_out.device)
-        self.linear(h, w_qkv, qkv, pre_norm=pre_norm)
+        self.linear(h, w_qkv, qkv)
         self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
                                 num_heads, num_kv_heads, head_dim)
 

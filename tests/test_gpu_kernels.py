@@ -428,48 +428,3 @@ def test_sample_follows_the_distribution(ops):
     freq = torch.bincount(out.long(), minlength=vocab).float() / n
     prob = torch.softmax(base[0], dim=-1)
     assert (freq - prob).abs().max().item() < 0.03
-
-
-@pytest.mark.parametrize("m", [1, 8, 13, 16, 17])
-@pytest.mark.parametrize("nk", [(4096, 1024), (1024, 2048), (100, 256), (331, 288), (64, 128)])
-def test_products_that_norm_their_own_input(ops, m, nk):
-    """``pre_norm``: the few-rows product makes A = bfloat16(rmsnorm(x) * g) itself (up to 16
-    rows, K from 256); the result equals the norm kernel followed by the product, whichever
-    way it ran, up to the rounding of the norm's sum."""
-    n, k = nk
-    x = _rand((m, k), seed=0, scale=3.0)
-    g = 1 + _rand((k,), seed=3, scale=0.1)
-    w = _rand((n, k), torch.bfloat16, seed=1, scale=0.05)
-    base = _rand((m, n), seed=2)
-    normed = torch.empty((m, k), dtype=torch.bfloat16, device=DEV)
-    RefOps().rmsnorm(x, g, 1e-5, normed)
-    fusable = bool(ops.bf16.ti_gemm_skinny_prenorm_supported(m, n, k, x.stride(0), w.stride(0)))
-    assert fusable == (m <= 16 and k >= 256)
-    for acc in (False, True):
-        out = base.clone()
-        before = ops.launches
-        ops.linear(None, w, out, accumulate=acc, pre_norm=(x, g, 1e-5, torch.bfloat16))
-        assert ops.launches - before == (1 if fusable else 2)
-        want = normed.double() @ w.double().T + (base.double() if acc else 0)
-        _close(out, want, 5e-4, f"pre_norm product m={m} {nk} acc={acc}")
-    if n % 16 == 0:
-        gate, up = w[:n // 2].contiguous(), w[n // 2:].contiguous()
-        y = torch.zeros((m, n // 2), dtype=torch.bfloat16, device=DEV)
-        ref = torch.empty_like(y)
-        ops.gate_up_swiglu(None, ops.pack_gate_up(gate, up), y, pre_norm=(x, g, 1e-5, torch.bfloat16))
-        r = RefOps()
-        r.gate_up_swiglu(None, r.pack_gate_up(gate, up), ref, pre_norm=(x, g, 1e-5, torch.bfloat16))
-        _close(y, ref, 8e-3, f"pre_norm swiglu m={m} {nk}")
-    # the fused norm sums a row exactly as the warp-per-row norm kernel does (64 rows and more)
-    if fusable:
-        many = torch.empty((64, k), dtype=torch.bfloat16, device=DEV)
-        ops.rmsnorm(x[:1].expand(64, k).contiguous(), g, 1e-5, many)
-        out, two = torch.empty((m, n), device=DEV), torch.empty((1, n), device=DEV)
-        ops.linear(None, w, out, pre_norm=(x, g, 1e-5, torch.bfloat16))
-        keep = ops.fuse_pre_norm
-        ops.fuse_pre_norm = False
-        try:
-            ops.linear(many[:1], w, two)
-        finally:
-            ops.fuse_pre_norm = keep
-        assert torch.equal(out[0], two[0])

@@ -10,10 +10,6 @@
 // block are added in a fixed order in shared memory, so an output does not depend on M, on the
 // other rows or on the launch.
 //
-// Prologue (optional): the rows of A are not read but made, A = bfloat16(rmsnorm(X) * g) from the
-// float32 residual stream X, each block normalising the few rows for itself into shared memory
-// while its weights are in flight; this saves the norm's own launch and a round trip through L2.
-//
 // Epilogues: store, accumulate into C (the residual stream), or SwiGLU: W holds, in every strip,
 // 8 gate rows followed by their 8 up rows, and out[m, j] = silu(gate_j) * up_j in bfloat16.
 #include "common.cuh"
@@ -43,22 +39,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 
 // ROWS = 16: a block owns 16 rows of W.  ROWS = 8: it owns 8 (the upper half of the MMA's A
 // operand is zero), which doubles the number of blocks for narrow outputs.
-constexpr int PRE_PAD = 32;    // elements between the rows of the normalised A in shared memory
-
-template <int NT, int ROWS, bool PRENORM>
-__global__ void __launch_bounds__(WARPS * 32)
+constexpr int SHORT_K = WARPS * CHUNK * 4;     // what four chunks per warp cover: 1,024
+// BATCH: chunks of W a warp has in flight.  4 covers K <= 1,024 in one round and leaves registers
+// for three blocks per SM (384 blocks of a 6,144-row weight then run as one wave instead of 1.3).
+template <int NT, int ROWS, int BATCH>
+__global__ void __launch_bounds__(WARPS * 32, BATCH == 4 && NT == 1 ? 3 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ c,
                    bf16* __restrict__ out_act, int m, int n, int k, int lda, int ldw, int ldc,
-                   int ld_act, int mode, const float* __restrict__ pre_x, int ld_pre,
-                   const float* __restrict__ pre_w, float pre_eps) {
+                   int ld_act, int mode) {
     constexpr int MP = NT * 8;                                  // padded token count
-    constexpr int BATCH = 8;                                    // chunks a warp has in flight
     __shared__ float part[WARPS][ROWS][MP + 1];
-    extern __shared__ __align__(16) unsigned char pre_smem[];  // PRENORM: bf16 [m][k + PRE_PAD]
-    if (PRENORM) {
-        a = reinterpret_cast<const bf16*>(pre_smem);
-        lda = k + PRE_PAD;
-    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
     const int n0 = blockIdx.x * ROWS;
@@ -87,34 +77,7 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
             }
         }
         // the weights do not depend on the kernel before this one; the activations do
-        if (c0 == warp) {
-            pdl_wait();
-            if (PRENORM) {
-                // every warp is here (K >= 32 * WARPS): rows warp, warp + 8, ... of A, summed as
-                // the warp-per-row norm kernel sums them
-                const float4* g4 = reinterpret_cast<const float4*>(pre_w);
-                const int k4 = k >> 2;
-                for (int r = warp; r < m; r += WARPS) {
-                    const float4* xr = reinterpret_cast<const float4*>(pre_x + (size_t)r * ld_pre);
-                    float ss = 0.0f;
-                    for (int i = lane; i < k4; i += 32) {
-                        const float4 v = xr[i];
-                        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
-                        ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-                    }
-                    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)k + pre_eps);
-                    bf16* dst = reinterpret_cast<bf16*>(pre_smem) + (size_t)r * lda;
-                    for (int i = lane; i < k4; i += 32) {
-                        const float4 v = xr[i], g = g4[i];
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * g.x, v.y * inv * g.y);
-                        __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * g.z, v.w * inv * g.w);
-                        *reinterpret_cast<uint2*>(dst + 4 * i) =
-                            make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
-                    }
-                }
-                __syncthreads();
-            }
-        }
+        if (c0 == warp) pdl_wait();
 #pragma unroll
         for (int u = 0; u < BATCH; ++u) {
             const int ch = c0 + u * WARPS;
@@ -191,68 +154,21 @@ extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_
     const bool narrow = mode != MODE_SWIGLU && (n + STRIP - 1) / STRIP < 128;
 #define LAUNCH(NT)                                                                                  \
     if (narrow)                                                                                     \
-        ti_launch_pdl(gemm_skinny_kernel<NT, 8, false>, (unsigned)((n + 7) / 8), WARPS * 32, 0, s,  \
+        ti_launch_pdl(gemm_skinny_kernel<NT, 8, 8>, (unsigned)((n + 7) / 8), WARPS * 32, 0, s,      \
                       (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, lda, ldw, ldc,    \
-                      ld_act, mode, (const float*)nullptr, 0, (const float*)nullptr, 0.0f);         \
-    else                                                                                            \
-        ti_launch_pdl(gemm_skinny_kernel<NT, 16, false>, (unsigned)((n + STRIP - 1) / STRIP),       \
+                      ld_act, mode);                                                                \
+    else if (k <= SHORT_K)                                                                          \
+        ti_launch_pdl(gemm_skinny_kernel<NT, 16, 4>, (unsigned)((n + STRIP - 1) / STRIP),           \
                       WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
-                      lda, ldw, ldc, ld_act, mode, (const float*)nullptr, 0, (const float*)nullptr, \
-                      0.0f)
+                      lda, ldw, ldc, ld_act, mode);                                                 \
+    else                                                                                            \
+        ti_launch_pdl(gemm_skinny_kernel<NT, 16, 8>, (unsigned)((n + STRIP - 1) / STRIP),           \
+                      WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
+                      lda, ldw, ldc, ld_act, mode)
     if (m <= 8) { LAUNCH(1); }
     else if (m <= 16) { LAUNCH(2); }
     else if (m <= 32) { LAUNCH(4); }
     else { LAUNCH(8); }
 #undef LAUNCH
     return ti_check_launch("gemm_skinny");
-}
-
-constexpr int PRENORM_MAX_SMEM = 100 * 1024;
-
-extern "C" int ti_gemm_skinny_prenorm_supported(int m, int n, int k, int ld_x, int ldw) {
-    return m >= 1 && m <= 16 && n >= 1 && k >= CHUNK * WARPS && k % CHUNK == 0 && ld_x % 4 == 0 &&
-           ldw % 8 == 0 && (m <= 8 ? 8 : 16) * (k + PRE_PAD) * 2 <= PRENORM_MAX_SMEM;
-}
-
-// As ti_gemm_skinny with A = bfloat16(rmsnorm(x) * pre_w): x is float32 [m, k] with ld_x elements
-// between rows, pre_w float32 [k]; the sum of squares of a row runs as in the warp-per-row norm
-// kernel.  At most 16 rows; K at least 256 and small enough for the rows to fit shared memory.
-extern "C" int ti_gemm_skinny_prenorm(const float* x, int ld_x, const float* pre_w, float pre_eps,
-                                      const void* w, float* c, void* out_act, int m, int n, int k, int ldw,
-                                      int ldc, int ld_act, int mode, void* stream) {
-    if (m == 0 || n == 0) return 0;
-    TI_REQUIRE(ti_gemm_skinny_prenorm_supported(m, n, k, ld_x, ldw),
-               "gemm_skinny_prenorm: M=%d (1..16), K=%d (a multiple of 32, at least 256, rows must fit "
-               "shared memory) or row strides %d, %d are not supported", m, k, ld_x, ldw);
-    TI_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)pre_w % 16 == 0 && (uintptr_t)w % 16 == 0,
-               "gemm_skinny_prenorm: operands must be 16-byte aligned");
-    TI_REQUIRE(mode != MODE_SWIGLU || n % 16 == 0, "gemm_skinny_prenorm: SwiGLU needs N %% 16 == 0, got %d", n);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaSuccess;
-#define CONFIGURE(NT, ROWS)                                                                           \
-        if (e == cudaSuccess)                                                                         \
-            e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, ROWS, true>,                              \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, PRENORM_MAX_SMEM)
-        CONFIGURE(1, 8); CONFIGURE(1, 16); CONFIGURE(2, 8); CONFIGURE(2, 16);
-#undef CONFIGURE
-        if (e != cudaSuccess) return ti_fail("gemm_skinny_prenorm: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    cudaStream_t s = (cudaStream_t)stream;
-    const bool narrow = mode != MODE_SWIGLU && (n + STRIP - 1) / STRIP < 128;
-    const size_t smem = (size_t)(m <= 8 ? 8 : 16) * (k + PRE_PAD) * 2;
-#define LAUNCH(NT)                                                                                    \
-    if (narrow)                                                                                       \
-        ti_launch_pdl(gemm_skinny_kernel<NT, 8, true>, (unsigned)((n + 7) / 8), WARPS * 32, smem, s,  \
-                      (const bf16*)nullptr, (const bf16*)w, c, (bf16*)out_act, m, n, k, 0, ldw, ldc,  \
-                      ld_act, mode, x, ld_x, pre_w, pre_eps);                                         \
-    else                                                                                              \
-        ti_launch_pdl(gemm_skinny_kernel<NT, 16, true>, (unsigned)((n + STRIP - 1) / STRIP),          \
-                      WARPS * 32, smem, s, (const bf16*)nullptr, (const bf16*)w, c, (bf16*)out_act, m, \
-                      n, k, 0, ldw, ldc, ld_act, mode, x, ld_x, pre_w, pre_eps)
-    if (m <= 8) { LAUNCH(1); }
-    else { LAUNCH(2); }
-#undef LAUNCH
-    return ti_check_launch("gemm_skinny_prenorm");
 }

@@ -13,10 +13,8 @@ embed(table, token_ids, out)                 out[t] = float32(table[token_ids[t]
 rmsnorm(x, weight, eps, out, rows=None)      out[r] = norm(x[rows[r]] or x[r]), rounded to out.dtype
 linear(a, w, out, accumulate=False)          out (+)= a @ w.T in float32
 gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
-    both take pre_norm=(x, weight, eps, dtype) instead of their first operand (None): the operand
-    is then rmsnorm(x) * weight rounded to dtype, made inside the product's launch where it can be
 qk_norm_rope_store(...)                      q/k head norm, rotation, k/v into pages, q out
-qkv_rope_store(h, w, ..., pre_norm=None)     the QKV product followed by qk_norm_rope_store, in one
+qkv_rope_store(h, w, ...)                    the QKV product followed by qk_norm_rope_store, in one
                                              launch where the kernels can (step.scratch holds what
                                              they derive from the step, for one forward pass)
 paged_attention(...)                         causal attention over the pages of each token's request
@@ -78,7 +76,6 @@ class CudaOps:
         self._counters = None
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
-        self.fuse_pre_norm = True         # the few-rows product normalises its own input rows
         self.fuse_qkv_epilogue = True     # the prompt QKV product norms, rotates and stores its heads
         # few-rows products on tcgen05 with K split over blocks: for weights of at least this many
         # bytes (None: never), below which the direct-to-register kernel's shorter chain wins
@@ -115,9 +112,6 @@ class CudaOps:
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_gemm_skinny.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
-            b.ti_gemm_skinny_prenorm_supported.argtypes = [_i, _i, _i, _i, _i]
-            b.ti_gemm_skinny_prenorm.argtypes = [_vp, _i, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                                 _i, _vp]
             b.ti_gemm_tcgen05_few_supported.argtypes = [_i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_few_scratch.argtypes = [_i, _i, _i, ctypes.POINTER(ctypes.c_longlong),
                                                       ctypes.POINTER(ctypes.c_int)]
@@ -229,36 +223,8 @@ class CudaOps:
                                       x.shape[1], float(eps), out.data_ptr(),
                                       _code(out, "rmsnorm"), self._stream()))
 
-    def _pre_normed(self, pre_norm, w, n, c, out_act, mode) -> Optional[torch.Tensor]:
-        """Runs the few-rows product on rmsnorm(x) inside one launch if it applies (returns
-        None); else returns the normed rows for the caller to multiply."""
-        x, norm_w, eps, dtype = pre_norm
-        m, k = x.shape
-        _need(x.dtype == torch.float32 and x.stride(1) == 1, "pre_norm: x must be float32 rows")
-        _need(norm_w.dtype == torch.float32 and norm_w.shape[0] == k, "pre_norm: weight must be float32 [K]")
-        if (self.fuse_pre_norm and dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.stride(1) == 1
-                and (self.few_tc_min_bytes is None or n * k * 2 < self.few_tc_min_bytes)
-                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and norm_w.data_ptr() % 16 == 0
-                and self.bf16.ti_gemm_skinny_prenorm_supported(m, n, k, x.stride(0), w.stride(0))):
-            self._ok(self.bf16.ti_gemm_skinny_prenorm(
-                x.data_ptr(), x.stride(0), norm_w.data_ptr(), float(eps), w.data_ptr(), _ptr(c),
-                _ptr(out_act), m, n, k, w.stride(0), c.stride(0) if c is not None else 0,
-                out_act.stride(0) if out_act is not None else 0, mode, self._stream()), self.bf16)
-            return None
-        a = torch.empty((m, k), dtype=dtype, device=x.device)
-        self.rmsnorm(x.contiguous(), norm_w, eps, a)
-        return a
-
-    def linear(self, a, w, out, accumulate=False, pre_norm=None):
-        """out (+)= a @ w.T.  ``pre_norm=(x, weight, eps, dtype)`` with ``a=None``:
-        a = rmsnorm(x) * weight in dtype."""
-        if pre_norm is not None:
-            _need(a is None, "linear: give either a or pre_norm")
-            _need(w.shape[1] == pre_norm[0].shape[1] and tuple(out.shape) == (pre_norm[0].shape[0], w.shape[0])
-                  and out.dtype == torch.float32 and out.stride(1) == 1, "linear: shapes do not agree")
-            a = self._pre_normed(pre_norm, w, w.shape[0], out, None, 1 if accumulate else 0)
-            if a is None:
-                return
+    def linear(self, a, w, out, accumulate=False):
+        """out (+)= a @ w.T"""
         m, k = a.shape
         n = w.shape[0]
         _need(w.shape[1] == k and tuple(out.shape) == (m, n), "linear: shapes do not agree")
@@ -287,22 +253,10 @@ class CudaOps:
             m, n, k, a.stride(0), w.stride(0), out.stride(0), int(bool(accumulate)),
             self._stream()))
 
-    def gate_up_swiglu(self, h, w_gate_up, out, pre_norm=None):
+    def gate_up_swiglu(self, h, w_gate_up, out):
         inter = out.shape[1]
         _need(w_gate_up.shape[0] == 2 * inter, "gate_up_swiglu: weight must hold gate and up rows")
         interleaved = bool(getattr(w_gate_up, "_ti_interleaved", False))
-        if pre_norm is not None:
-            _need(h is None, "gate_up_swiglu: give either h or pre_norm")
-            _need(w_gate_up.shape[1] == pre_norm[0].shape[1] and out.shape[0] == pre_norm[0].shape[0],
-                  "gate_up_swiglu: shapes do not agree")
-            if interleaved and out.dtype == torch.bfloat16 and out.stride(1) == 1:
-                h = self._pre_normed(pre_norm, w_gate_up, 2 * inter, None, out, 2)
-                if h is None:
-                    return
-            else:
-                x, norm_w, eps, dtype = pre_norm
-                h = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
-                self.rmsnorm(x, norm_w, eps, h)
         m, k = h.shape
         if (interleaved and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
                 and self._few_tc(h, w_gate_up, None, out, 2)):
@@ -348,28 +302,23 @@ class CudaOps:
             q_out.data_ptr(), _code(q_out, "q"), self.status.data_ptr(), self._stream()))
 
     def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
-                       num_heads, num_kv_heads, head_dim, pre_norm=None):
-        """``qk_norm_rope_store`` of ``h @ w_qkv.T`` (or of the product of ``pre_norm``'s normed
-        rows).  Prompt portions with head size 128 run as one tcgen05 product whose epilogue
+                       num_heads, num_kv_heads, head_dim):
+        """``qk_norm_rope_store`` of ``h @ w_qkv.T``.  Prompt portions with head size 128 run as one tcgen05 product whose epilogue
         norms, rotates and stores each head, so the float32 product never reaches memory."""
         t = q_out.shape[0]
         pages, bt = cache.pages, cache.block_table
         fused = (self.fuse_qkv_epilogue and t > 64 and head_dim == 128 and w_qkv.dtype == torch.bfloat16
                  and q_out.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
-                 and (h is None and pre_norm[3] == torch.bfloat16 or h is not None and h.dtype == torch.bfloat16)
+                 and h.dtype == torch.bfloat16
                  and w_qkv.stride(1) == 1 and w_qkv.stride(0) % 8 == 0 and w_qkv.shape[1] % 8 == 0
                  and w_qkv.data_ptr() % 16 == 0 and q_out.is_contiguous() and pages.is_contiguous()
                  and q_weight.data_ptr() % 16 == 0 and k_weight.data_ptr() % 16 == 0)
         if not fused:
             qkv = torch.empty((t, w_qkv.shape[0]), dtype=torch.float32, device=q_out.device)
-            self.linear(h, w_qkv, qkv, pre_norm=pre_norm)
+            self.linear(h, w_qkv, qkv)
             self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
                                     num_heads, num_kv_heads, head_dim)
             return
-        if h is None:
-            x, norm_w, norm_eps, dtype = pre_norm
-            h = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
-            self.rmsnorm(x, norm_w, norm_eps, h)
         n, k = w_qkv.shape
         _need(h.shape == (t, k) and h.stride(1) == 1 and n == (num_heads + 2 * num_kv_heads) * head_dim,
               "qkv_rope_store: shapes do not agree")

@@ -22,7 +22,6 @@ from .base import (MATRIX, NORM_WEIGHT, PagedKVSpec, Part, WeightSpec, as_float3
 
 class Attention(Part):
     category = "mixer"
-    takes_norm = True        # forward(ops, None, residual, ..., pre_norm=norm) norms the residual itself
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: float, position: PartSpec, window: Optional[int] = None,
@@ -67,16 +66,11 @@ class Attention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, ops, h, residual, step, cache, pre_norm=None):
-        """``h`` is the normed residual, or None with ``pre_norm`` the RMSNorm part to apply to
-        ``residual`` inside the first product."""
-        t = residual.shape[0]
-        dev = residual.device
-        act = step.act_dtype if h is None else h.dtype
+    def forward(self, ops, h, residual, step, cache):
+        t, dev, act = h.shape[0], h.device, h.dtype
         q = torch.empty((t, self.nq), dtype=act, device=dev)
-        pre = None if h is not None else (residual, pre_norm.weight, pre_norm.eps, act)
         ops.qkv_rope_store(h, self.w_qkv, self.q_norm, self.k_norm, self.eps, self.position.table(dev),
-                           step, cache, q, self.num_heads, self.num_kv_heads, self.head_dim, pre_norm=pre)
+                           step, cache, q, self.num_heads, self.num_kv_heads, self.head_dim)
         out = torch.empty((t, self.nq), dtype=act, device=dev)
         ops.paged_attention(q, step, cache, out, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.window, self.scale)

@@ -14,9 +14,6 @@ position  ``table(device)``: what the mixer's kernels need to rotate a head at a
 mixer     ``cache_spec()``: what it keeps per request (``PagedKVSpec``, ``FixedStateSpec`` or
           None); ``forward(ops, h, residual, step, cache)``: adds its output to ``residual``.
 ffn       ``forward(ops, h, residual, step)``: adds its output to ``residual``.
-          Optional for both: a class attribute ``takes_norm = True`` and a keyword
-          ``pre_norm=<RMSNorm part>``; the block then passes ``h=None`` and the part applies
-          the norm to ``residual`` itself, inside its first product's launch.
 block     arrangement of the four parts of a layer: ``forward(ops, x, step, cache)``.
 embedding ``forward(ops, token_ids, out)``;  head ``forward(ops, h) -> logits``.
 

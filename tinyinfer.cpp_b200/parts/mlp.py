@@ -13,7 +13,6 @@ from .base import MATRIX, Part, WeightSpec, register_part
 
 class SwiGLU(Part):
     category = "ffn"
-    takes_norm = True        # forward(ops, None, residual, ..., pre_norm=norm) norms the residual itself
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = int(hidden_size)
@@ -35,17 +34,9 @@ class SwiGLU(Part):
         self.w_gate_up = ops.pack_gate_up(g, u)
         self.w_down = ops.pack_linear(tensors["down_proj.weight"])
 
-    def forward(self, ops, h, residual, step, pre_norm=None):
-        """``h`` is the normed residual, or None with ``pre_norm`` the RMSNorm part to apply to
-        ``residual`` inside the first product."""
-        t, dev = residual.shape[0], residual.device
-        act = step.act_dtype if h is None else h.dtype
-        y = torch.empty((t, self.intermediate_size), dtype=act, device=dev)
-        if h is None:
-            ops.gate_up_swiglu(None, self.w_gate_up, y,
-                               pre_norm=(residual, pre_norm.weight, pre_norm.eps, act))
-        else:
-            ops.gate_up_swiglu(h, self.w_gate_up, y)
+    def forward(self, ops, h, residual, step):
+        y = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        ops.gate_up_swiglu(h, self.w_gate_up, y)
         ops.linear(y, self.w_down, residual, accumulate=True)
 
 

@@ -12,7 +12,6 @@ from .base import NORM_WEIGHT, Part, WeightSpec, as_float32, register_part
 
 class RMSNorm(Part):
     category = "norm"
-    is_rmsnorm = True        # a product after it may apply it to its own input (``pre_norm``)
 
     def __init__(self, size: int, eps: float):
         self.size = int(size)
