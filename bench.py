@@ -6,7 +6,7 @@
 
 Default run: the Qwen3-0.6B layer sizes (28 layers, hidden 1024, 16 heads over 8 kv heads of
 128, intermediate 3072, vocabulary 151936, tied head) with seeded random weights, 8 requests
-decoding at a context of 4,096 tokens, pages of 16 tokens.  A step is one decode step of the
+decoding at a context of 4,096 tokens, pages of 64 tokens.  A step is one decode step of the
 whole batch.  Prints one JSON line:
 
 value      decoded tokens a second, timed on the device with CUDA events over K graph-replayed
@@ -55,7 +55,7 @@ QWEN3_32B = dict(QWEN3_0_6B, num_hidden_layers=64, hidden_size=5120, num_attenti
                  num_key_value_heads=8, intermediate_size=25600, tie_word_embeddings=False)
 SHAPES = {"0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "8b": ("Qwen3-8B shape", QWEN3_8B),
           "32b": ("Qwen3-32B shape", QWEN3_32B)}
-PAGE = 16
+PAGE = 64
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -291,6 +291,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
     ap.add_argument("--shape", choices=list(SHAPES), default="0.6b", help="layer sizes of the model")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per cache page")
     ap.add_argument("--only", choices=["decode", "prefill", "chains"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
@@ -318,7 +319,7 @@ def main() -> int:
     pk, pk_kind = peaks()
     nums = model_numbers(cfg)
     max_batch = max(args.batch, 1 if (args.no_points or args.only) else 64)
-    engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE,
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
                     max_tokens=max_batch * args.context, max_requests=max_batch + 1, step_graphs=True)
 
     if args.only == "decode":
@@ -363,7 +364,7 @@ def main() -> int:
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"], "global_batch": args.batch,
-            "seq_len": args.context, "page_size": PAGE, "parallelism": "single GPU",
+            "seq_len": args.context, "page_size": args.page_size, "parallelism": "single GPU",
             "cuda_graph": True, "l2": "working set > L2, no flush", "peaks": pk_kind,
         },
         "clocks": clocks,

@@ -200,7 +200,7 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory, graph):
     prompts = [random_tokens(512, n, seed=n) for n in (1, 9, 33, 64)]
     want = [plain_greedy(cfg, w, p, 12) for p in prompts]
     llm = LLM(d, dtype="float32", max_seq=128, max_num_seqs=4, max_batched_tokens=48, chunk=16,
-              kv_tokens=160, cuda_graph=graph)
+              kv_tokens=160, page_size=16, cuda_graph=graph)
     outs = llm.generate(prompts, SamplingParams(max_tokens=12))
     assert [o.tokens for o in outs] == want
     assert llm.stats.preemptions >= 1                    # 160 tokens of cache for four requests

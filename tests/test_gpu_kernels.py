@@ -273,7 +273,8 @@ def test_paged_attention(ops, dtype, geom, window):
     _close(out, ref, 2e-5 if dtype == torch.float32 else 1.5e-2, f"attention {geom} window={window}")
 
 
-@pytest.mark.parametrize("geom", [(16, 8, 128, 16), (4, 1, 128, 32), (6, 6, 128, 16)])
+@pytest.mark.parametrize("geom", [(16, 8, 128, 16), (4, 1, 128, 32), (6, 6, 128, 16), (4, 2, 128, 64),
+                                  (2, 1, 128, 128), (3, 1, 128, 48), (2, 2, 128, 256)])
 @pytest.mark.parametrize("window", [None, 1, 200])
 def test_prompt_attention_on_tcgen05_matches_the_mma_kernel_and_the_plain_statement(ops, geom, window):
     """Head size 128 takes the tcgen05 kernel: long and short portions, earlier context, ragged ends."""

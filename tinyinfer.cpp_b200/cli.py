@@ -48,7 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--chunk", type=int, default=None, help="longest prompt portion per step")
     ap.add_argument("--max-batched-tokens", type=int, default=2048)
     ap.add_argument("--max-num-seqs", type=int, default=16)
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--kv-tokens", type=int, default=None, help="tokens the cache pool holds")
     ap.add_argument("--random-weights", metavar="CONFIG.json",
                     help="run this configuration with random weights drawn from --seed")

@@ -5,9 +5,9 @@
 // request's keys in tiles of 128, from the first key any of its rows may see to its last row's own
 // position (keys of earlier steps and of this portion alike).  Roles:
 //   warp 0     TMA: the query tile once, then key and value tiles into two-stage rings.  A tile is
-//              eight runs of 16 tokens, each run one box of the page pool seen as a 2-D tensor
-//              (rows = token slots, 128-byte swizzle); runs nobody may see are fetched from outside
-//              the tensor, which TMA fills with zeros.
+//              128 / run runs of tokens that lie in one page, each run one box of the page pool
+//              seen as a 2-D tensor (rows = token slots, 128-byte swizzle); runs nobody may see are
+//              fetched from outside the tensor, which TMA fills with zeros.
 //   warp 1     tcgen05.mma: S = Q K^T (128 x 128 x 128, both operands K-major) into one of two
 //              score accumulators in tensor memory, one tile ahead of the softmax; then O += P V
 //              (P K-major from shared memory, V with its rows along N) into the output accumulator.
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                        const int* __restrict__ tiles, const int* __restrict__ positions,
                        const int* __restrict__ block_table, int bt_stride, int num_pages, int page_size,
-                       int num_heads, int num_kv_heads, int window, float scale_log2,
+                       int num_heads, int num_kv_heads, int window, int run, float scale_log2,
                        bf16* __restrict__ out, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -96,8 +96,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     bool ok = true;
     if (warp == 0) {
-        // Lanes 0-7 each own one run of 16 keys of a tile: they look up its page and issue its four
-        // boxes (two halves of the head dimension, keys and values); lane 0 also does the waiting.
+        // A tile is cut into runs of `run` keys that lie in one page (16 to 128, the largest power of
+        // two that divides the page size: the fewer and larger the boxes, the less the TMA unit's
+        // issue rate of about one box per 64 cycles paces the tile).  Each of the first 128 / run
+        // lanes owns one run: it looks up its page and issues its four boxes (two halves of the
+        // head dimension, keys and values); lane 0 also does the waiting.
         const int* table = block_table + (size_t)req * bt_stride;
         const int oob_row = num_pages * 2 * num_kv_heads * page_size;          // outside the tensor: zeros
         const int to_v = num_kv_heads * page_size;                             // keys -> values of a page
@@ -106,12 +109,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tma_load_2d(smem + SMEM_Q, &map_q, q_full, h * HD, tok0);
             tma_load_2d(smem + SMEM_Q + SUB, &map_q, q_full, h * HD + 64, tok0);
         }
-        for (int j = 0; j < num_kt && ok; ++j) {
-            const int st = j & 1, kt = kt_lo + j;
+        // the row of the pool's 2-D view where this lane's run of 16 keys of tile j begins
+        auto lookup = [&](int j) {
             int krow = oob_row;
-            if (lane < 8) {
-                const int key0 = kt * BN + lane * 16;
-                if (key0 <= pos_last && key0 + 16 > kv_lo) {
+            if (lane < BN / run) {
+                const int key0 = (kt_lo + j) * BN + lane * run;
+                if (key0 <= pos_last && key0 + run > kv_lo) {
                     const int pg = table[key0 / page_size];
                     if (pg >= 0 && pg < num_pages)
                         krow = (pg * 2 * num_kv_heads + kvh) * page_size + key0 % page_size;
@@ -119,14 +122,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         atomicCAS(status, 0, 1);
                 }
             }
+            return krow;
+        };
+        int krow_next = lookup(0);
+        for (int j = 0; j < num_kt && ok; ++j) {
+            const int st = j & 1;
+            const int krow = krow_next;
+            // the next tile's block-table entries are on their way while this tile is issued
+            if (j + 1 < num_kt) krow_next = lookup(j + 1);
             if (lane == 0) {
                 ok = mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1);
                 if (ok) mbar_expect_tx(&k_full[st], 2 * SUB);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (lane < 8) {
-                unsigned char* kdst = smem + SMEM_K + st * 2 * SUB + lane * 2048;
+            if (lane < BN / run) {
+                unsigned char* kdst = smem + SMEM_K + st * 2 * SUB + lane * run * 128;
                 tma_load_2d(kdst, &map_kv, &k_full[st], 0, krow);
                 tma_load_2d(kdst + SUB, &map_kv, &k_full[st], 64, krow);
             }
@@ -136,9 +147,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (lane < 8) {
+            if (lane < BN / run) {
                 const int vrow = krow == oob_row ? oob_row : krow + to_v;
-                unsigned char* vdst = smem + SMEM_V + st * 2 * SUB + lane * 2048;
+                unsigned char* vdst = smem + SMEM_V + st * 2 * SUB + lane * run * 128;
                 tma_load_2d(vdst, &map_kv, &v_full[st], 0, vrow);
                 tma_load_2d(vdst + SUB, &map_kv, &v_full[st], 64, vrow);
             }
@@ -338,7 +349,9 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
     if (int rc = make_map_bf16(&map_q, q, num_tokens, num_heads * HD, (long long)num_heads * HD, BM,
                                "attn_prefill_tc"))
         return rc;
-    if (int rc = make_map_bf16(&map_kv, pages, pool_rows, HD, HD, 16, "attn_prefill_tc")) return rc;
+    int run = 128;
+    while (page_size % run) run /= 2;
+    if (int rc = make_map_bf16(&map_kv, pages, pool_rows, HD, HD, run, "attn_prefill_tc")) return rc;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
@@ -349,6 +362,6 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
     dim3 grid(num_heads, num_tiles);
     ti_launch_pdl(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,
                   tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads, num_kv_heads,
-                  window, scale * LOG2E, (bf16*)out, status);
+                  window, run, scale * LOG2E, (bf16*)out, status);
     return ti_check_launch("attn_prefill_tc");
 }

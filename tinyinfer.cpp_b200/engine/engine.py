@@ -53,7 +53,7 @@ class Engine:
 
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[Mapping[str, Any]] = None,
                  seed: Optional[int] = None, dtype="bfloat16", device="cuda:0",
-                 page_size: int = 16, max_tokens: Optional[int] = None,
+                 page_size: int = 64, max_tokens: Optional[int] = None,
                  num_pages: Optional[int] = None, max_requests: int = 64, ops=None,
                  step_graphs: bool = False):
         self.dtype = parse_dtype(dtype)

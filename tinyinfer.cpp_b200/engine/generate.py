@@ -46,7 +46,7 @@ class LLM:
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[Mapping[str, Any]] = None,
                  seed: Optional[int] = None, dtype="bfloat16", device="cuda:0",
                  max_seq: int = 2048, max_num_seqs: int = 16, max_batched_tokens: int = 2048,
-                 chunk: Optional[int] = None, page_size: int = 16,
+                 chunk: Optional[int] = None, page_size: int = 64,
                  kv_tokens: Optional[int] = None, cuda_graph: bool = False, ops=None):
         if kv_tokens is None:
             kv_tokens = max_num_seqs * max_seq
