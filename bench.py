@@ -48,7 +48,7 @@ QWEN3_0_6B = dict(
     num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
     vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
     max_position_embeddings=4096)
-# the other two shapes of the reference's architecture that BASELINE.json names (untied heads)
+# the two larger shapes of the same architecture (untied heads)
 QWEN3_8B = dict(QWEN3_0_6B, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
                 num_key_value_heads=8, intermediate_size=12288, tie_word_embeddings=False)
 QWEN3_32B = dict(QWEN3_0_6B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
