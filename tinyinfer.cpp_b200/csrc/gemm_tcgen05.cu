@@ -78,22 +78,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
-    pdl_wait();        // the set-up above overlaps the end of the kernel before; its results are read below
 
     // tiles in order of m fastest, so that blocks running together share few panels of W
     bool ok = true;
     if (warp == 0) {
         if (lane == 0) {
+            // The weights do not depend on the kernel before this one: the first ring-full of W
+            // tiles is requested before waiting for it; its results (A) follow after the wait.
+            int primed = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && primed < STAGES; tile += gridDim.x) {
+                const int n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb && primed < STAGES; ++kb, ++primed) {
+                    mbar_expect_tx(&full[primed], T::STAGE_A + T::STAGE_B);
+                    tma_load_2d(stage_b + primed * T::STAGE_B, &map_w, &full[primed], kb * BK, n0);
+                }
+            }
+            pdl_wait();
             int it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
-                    ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
-                    if (!ok) break;
-                    mbar_expect_tx(&full[s], T::STAGE_A + T::STAGE_B);
+                    if (it >= primed) {
+                        ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
+                        if (!ok) break;
+                        mbar_expect_tx(&full[s], T::STAGE_A + T::STAGE_B);
+                        tma_load_2d(stage_b + s * T::STAGE_B, &map_w, &full[s], kb * BK, n0);
+                    }
                     tma_load_2d(stage_a + s * T::STAGE_A, &map_a, &full[s], kb * BK, m0);
-                    tma_load_2d(stage_b + s * T::STAGE_B, &map_w, &full[s], kb * BK, n0);
                 }
             }
         }
@@ -130,6 +142,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         const int quarter = warp & 3;                 // the TMEM lanes this warp may read
         const int col_half = (warp - 2) >> 2;         // two warps share a quarter: half of the columns each
+        pdl_wait();                                   // C and what the QKV epilogue reads belong to the chain
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int buf = local & 1;

@@ -129,23 +129,35 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     cluster_sync();                                      // both blocks' barriers exist before any use
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
-    pdl_wait();        // the set-up above overlaps the end of the kernel before; its results are read below
 
     bool ok = true;
     if (warp == 0) {
         if (lane == 0) {
+            // The weights do not depend on the kernel before this one: the first ring-full of W
+            // tiles is requested before waiting for it; its results (A) follow after the wait.
+            int primed = 0;
+            for (int tile = pair; tile < num_tiles && primed < STAGES; tile += num_pairs) {
+                const int n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < num_kb && primed < STAGES; ++kb, ++primed) {
+                    if (leader) mbar_expect_tx(&full[primed], 2 * (STAGE_A + STAGE_B));   // both blocks' bytes
+                    tma_load_2d_pair(stage_b + primed * STAGE_B, &map_w, map_to_rank(&full[primed], 0), kb * BK, n0);
+                }
+            }
+            pdl_wait();
             int it = 0;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 const int m0 = (tile % tiles_m) * BM + (int)rank * 128;
                 const int n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
-                    ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
-                    if (!ok) break;
-                    if (leader) mbar_expect_tx(&full[s], 2 * (STAGE_A + STAGE_B));   // both blocks' bytes
                     const unsigned bar = map_to_rank(&full[s], 0);
+                    if (it >= primed) {
+                        ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
+                        if (!ok) break;
+                        if (leader) mbar_expect_tx(&full[s], 2 * (STAGE_A + STAGE_B));   // both blocks' bytes
+                        tma_load_2d_pair(stage_b + s * STAGE_B, &map_w, bar, kb * BK, n0);
+                    }
                     tma_load_2d_pair(stage_a + s * STAGE_A, &map_a, bar, kb * BK, m0);
-                    tma_load_2d_pair(stage_b + s * STAGE_B, &map_w, bar, kb * BK, n0);
                 }
             }
         }
@@ -178,6 +190,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     } else {
         const int quarter = warp & 3;                 // the TMEM lanes this warp may read
         const int col_half = (warp - 2) >> 2;         // two warps share a quarter: half of the columns each
+        pdl_wait();                                   // C and what the QKV epilogue reads belong to the chain
         int local = 0;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
             const int buf = local & 1;
