@@ -11,7 +11,7 @@ from tinyinfer_b200 import Engine, StepEntry
 from tinyinfer_b200.config import ConfigError, Qwen3Config
 from tinyinfer_b200.config.qwen3 import gguf_metadata, gguf_tensor_name
 from tinyinfer_b200.weights import GgufError, GgufFile, WeightsError, write_gguf
-from util import TINY, assert_close_logits, make_model, random_tokens
+from util import assert_close_logits, make_model, random_tokens
 
 
 def _to_gguf(tmp_path, name, drop=(), extra=None, version=3):

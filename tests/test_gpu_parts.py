@@ -9,14 +9,13 @@ its own.  Neither is a model of anyone's.
 """
 import math
 from dataclasses import dataclass
-from types import SimpleNamespace
 
 import pytest
 import torch
 
 from plain_qwen3 import (load_folder, plain_attention, plain_embedding, plain_rmsnorm,
                          plain_rope_angles, plain_rope_neox, plain_swiglu)
-from util import BF16_RTOL, FP32_RTOL, assert_close_logits, random_tokens
+from util import FP32_RTOL, assert_close_logits, random_tokens
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"

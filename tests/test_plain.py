@@ -5,7 +5,7 @@ import torch
 
 from plain_qwen3 import (load_folder, plain_attention, plain_forward, plain_greedy, plain_rmsnorm,
                          plain_rope_angles, plain_rope_neox, plain_swiglu)
-from util import TINY, make_model, random_tokens
+from util import make_model, random_tokens
 
 
 def test_rmsnorm_formula():

@@ -14,7 +14,7 @@ from typing import Any, Hashable, Mapping, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheManager, OutOfPages
+from ..cache import CacheManager
 from ..config.registry import architecture_of, load_config
 from ..parts.model import CausalLM
 from ..weights.loader import load_gguf, load_model_weights, load_model_weights_gguf

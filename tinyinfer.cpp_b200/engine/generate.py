@@ -11,8 +11,6 @@ import time
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Sequence
 
-import torch
-
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .engine import Engine
