@@ -11,8 +11,9 @@ whole batch.  Prints one JSON line:
 
 value      decoded tokens a second, timed on the device with CUDA events over K graph-replayed
            steps with the argmax on the device (nothing is read back inside the timed region);
-e2e        the same through the Python entry point: every step copies its host token ids to
-           the device from pinned memory and reads the chosen tokens back;
+e2e        the same through the Python entry point (LLM.start and Session.step, after the prompts
+           have run): every step schedules, copies its host token ids and block tables to the
+           device from pinned memory, decodes, samples and reads the chosen tokens back;
 prefill    one request's 2,048-token prompt in one step: tokens a second and the step's
            flops / time / bf16 peak;
 roofline   the bytes a decode step has to read (every weight once, and the keys and values of
@@ -177,41 +178,44 @@ def decode_device_timed(engine, ids, steps, warmup, torch):
     return ms / steps, clocks.summary(), engine.ops.launches - before
 
 
-def decode_e2e(engine, ids, steps, warmup, torch):
-    """The same steps as a user runs them: host token ids in, chosen token ids out."""
-    from tinyinfer_b200 import StepEntry
-    from tinyinfer_b200.sampling import Sampler, SamplingParams
-    sampler = Sampler(engine.ops, engine.device)
-    params = [SamplingParams()] * len(ids)
-    tokens = [1] * len(ids)
-    numbers = list(range(len(ids)))
-
-    def one(tokens):
-        logits = engine.decode_step([StepEntry(r, [t], [0]) for r, t in zip(ids, tokens)])
-        return sampler(logits, params, numbers, [0] * len(ids)).tolist()
-
+def decode_e2e(llm, batch, context, steps, warmup, torch):
+    """The same steps through the Python entry point (``LLM.start`` / ``Session.step``): prompts
+    are run first; then every timed step packs the host's token ids, copies them to the device
+    from pinned memory, decodes, samples and reads the chosen tokens back."""
+    from tinyinfer_b200 import SamplingParams
+    g = torch.Generator().manual_seed(1)
+    # requests that finish their prompt early decode while the others' prompts still run: room
+    # for those tokens, so that nobody reaches its limit inside the timed steps
+    slack = -(-batch * context // llm.max_batched_tokens) + batch + 4
+    prompt_len = context - (steps + warmup) - slack - 2
+    prompts = [torch.randint(0, llm.engine.plan.vocab_size, (prompt_len,), generator=g).tolist()
+               for _ in range(batch)]
+    session = llm.start(prompts, SamplingParams(max_tokens=steps + warmup + slack + 1))
+    while not all(r.output for r in session.requests):      # the prompts, in portions
+        session.step()
     for _ in range(warmup):
-        tokens = one(tokens)
+        session.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(steps):
-        tokens = one(tokens)
+        made = session.step()
+        assert len(made) == batch
     torch.cuda.synchronize()
     sec = time.perf_counter() - t0
-    bk = engine._graphs.buckets[max(engine._graphs.buckets)]
-    return sec / steps * 1e3, bk.total * 4, len(ids) * 4
+    while not session.done:
+        session.step()
+    session.finish()
+    bk = llm.engine._graphs.buckets[max(llm.engine._graphs.buckets)]
+    return sec / steps * 1e3, bk.total * 4, batch * 4
 
 
-def measure_decode(engine, batch, context, steps, warmup, torch, e2e=False):
-    start_ctx = context - (steps + warmup) * (2 if e2e else 1) - 2
-    ids = fill_requests(engine, batch, start_ctx, torch)
+def measure_decode(engine, batch, context, steps, warmup, torch):
+    ids = fill_requests(engine, batch, context - (steps + warmup) - 2, torch)
     try:
-        dev = decode_device_timed(engine, ids, steps, warmup, torch)
-        host = decode_e2e(engine, ids, steps, warmup, torch) if e2e else None
+        return decode_device_timed(engine, ids, steps, warmup, torch)
     finally:
         for r in ids:
             engine.finish(r)
-    return dev, host
 
 
 def measure_prefill(engine, tokens, reps, torch):
@@ -308,7 +312,7 @@ def main() -> int:
     warmup = max(args.warmup, 3)
 
     import torch
-    from tinyinfer_b200 import Engine
+    from tinyinfer_b200 import LLM
 
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
@@ -319,11 +323,12 @@ def main() -> int:
     pk, pk_kind = peaks()
     nums = model_numbers(cfg)
     max_batch = max(args.batch, 1 if (args.no_points or args.only) else 64)
-    engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
-                    max_tokens=max_batch * args.context, max_requests=max_batch + 1, step_graphs=True)
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size, max_seq=args.context,
+              max_num_seqs=max_batch + 1, kv_tokens=max_batch * args.context, cuda_graph=True)
+    engine = llm.engine
 
     if args.only == "decode":
-        (ms, _, launches), _ = measure_decode(engine, args.batch, args.context, args.steps, warmup, torch)
+        ms, _, launches = measure_decode(engine, args.batch, args.context, args.steps, warmup, torch)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context,
                           "ms_per_step": round(ms, 4), "gpu_launches": launches}))
         return 0
@@ -335,8 +340,8 @@ def main() -> int:
         pf_ms = measure_prefill(engine, 2048, max(1, args.steps), torch)
         print(json.dumps({"only": "prefill", "tokens": 2048, "ms": round(pf_ms, 3)}))
         return 0
-    (ms, clocks, launches), (e2e_ms, h2d, d2h) = measure_decode(
-        engine, args.batch, args.context, args.steps, warmup, torch, e2e=True)
+    ms, clocks, launches = measure_decode(engine, args.batch, args.context, args.steps, warmup, torch)
+    e2e_ms, h2d, d2h = decode_e2e(llm, args.batch, args.context, args.steps, warmup, torch)
     ctx_mid = args.context - args.steps // 2
     step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -344,7 +349,7 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            (pms, _, _), _ = measure_decode(engine, b, args.context, min(args.steps, 32), warmup, torch)
+            pms, _, _ = measure_decode(engine, b, args.context, min(args.steps, 32), warmup, torch)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
 
     pf_tokens = 2048

@@ -93,3 +93,30 @@ def test_sampling_does_not_depend_on_the_batch(tmp_path):
     other_seed = LLM(d, dtype="float32", device="cpu", ops=RefOps(), max_seq=64).generate(
         prompts, SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=8, max_tokens=6))
     assert [o.tokens for o in other_seed] != [o.tokens for o in together]
+
+
+def test_a_generation_can_be_stepped_and_streams_its_tokens(tmp_path):
+    """``LLM.start`` + ``Session.step``: the tokens each step reports, put together, are what
+    ``generate`` returns."""
+    d = make_model(tmp_path, "A")
+    prompts = [random_tokens(TINY["A"]["vocab_size"], n, seed=n) for n in (3, 20, 41)]
+    sp = SamplingParams(max_tokens=9)
+    kw = dict(dtype="float32", device="cpu", ops=RefOps(), max_seq=64, max_num_seqs=3, max_batched_tokens=24)
+    want = LLM(d, **kw).generate(prompts, sp)
+    session = LLM(d, **kw).start(prompts, sp)
+    streamed = {i: [] for i in range(len(prompts))}
+    while not session.done:
+        for index, token in session.step():
+            streamed[index].append(token)
+    got = session.finish()
+    assert [o.tokens for o in got] == [o.tokens for o in want]
+    assert [streamed[i] for i in range(len(prompts))] == [o.tokens for o in want]
+
+
+def test_request_span_reads_across_prompt_and_output():
+    from tinyinfer_b200.engine.scheduler import Request
+    r = Request(req_id="r", prompt=[1, 2, 3, 4], output=[5, 6, 7])
+    for start in range(7):
+        for count in range(0, 8 - start):
+            assert r.span(start, count) == r.tokens[start:start + count]
+    assert r.num_tokens == 7

@@ -61,52 +61,79 @@ class LLM:
         self.eos_token_ids = tuple(eos)
         self.stats = RunStats()
 
+    def start(self, prompts: Sequence[Sequence[int]],
+              params: SamplingParams | Sequence[SamplingParams] = SamplingParams(),
+              log_steps: bool = False) -> "Session":
+        """Queue the prompts and return the running generation; ``Session.step()`` advances it by
+        one engine step (for callers that stream tokens or measure steps)."""
+        return Session(self, prompts, params, log_steps)
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: SamplingParams | Sequence[SamplingParams] = SamplingParams(),
                  log_steps: bool = False) -> list[Generation]:
+        session = self.start(prompts, params, log_steps)
+        while not session.done:
+            session.step()
+        return session.finish()
+
+
+class Session:
+    """One call of ``LLM.generate`` in progress."""
+
+    def __init__(self, llm: LLM, prompts, params, log_steps: bool = False):
         if isinstance(params, SamplingParams):
             params = [params] * len(prompts)
         if len(params) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
-        engine = self.engine
-        sched = Scheduler(engine.cache, max_num_seqs=self.max_num_seqs,
-                          max_batched_tokens=self.max_batched_tokens, chunk=self.chunk,
-                          max_position=self.max_seq, eos_token_ids=self.eos_token_ids)
-        requests = [Request(req_id=("gen", i), prompt=[int(t) for t in p], params=sp)
-                    for i, (p, sp) in enumerate(zip(prompts, params))]
-        for r in requests:
-            sched.add(r)
-        stats = self.stats = RunStats()
-        t0 = time.perf_counter()
-        while sched.has_work():
-            plan = sched.schedule()
-            if not plan:
-                raise RuntimeError("the scheduler found nothing to run although requests wait; "
-                                   "the cache pool is too small for the oldest request")
-            entries = []
-            for s in plan:
-                toks = s.request.tokens[s.start:s.start + s.count]
-                entries.append(StepEntry(s.request.req_id, toks, [s.count - 1] if s.samples else []))
-            if self.cuda_graph and all(s.count == 1 and s.samples for s in plan):
-                logits = engine.decode_step(entries)
+        self.llm = llm
+        self.log_steps = log_steps
+        self.sched = Scheduler(llm.engine.cache, max_num_seqs=llm.max_num_seqs,
+                               max_batched_tokens=llm.max_batched_tokens, chunk=llm.chunk,
+                               max_position=llm.max_seq, eos_token_ids=llm.eos_token_ids)
+        self.requests = [Request(req_id=("gen", i), prompt=[int(t) for t in p], params=sp)
+                         for i, (p, sp) in enumerate(zip(prompts, params))]
+        for r in self.requests:
+            self.sched.add(r)
+        self.stats = llm.stats = RunStats()
+        self._t0 = time.perf_counter()
+
+    @property
+    def done(self) -> bool:
+        return not self.sched.has_work()
+
+    def step(self) -> list[tuple[int, int]]:
+        """Run one engine step; returns (prompt index, token) for every token generated in it."""
+        llm, engine, sched, stats = self.llm, self.llm.engine, self.sched, self.stats
+        plan = sched.schedule()
+        if not plan:
+            raise RuntimeError("the scheduler found nothing to run although requests wait; "
+                               "the cache pool is too small for the oldest request")
+        entries = []
+        decoding = llm.cuda_graph
+        for s in plan:
+            toks = s.request.span(s.start, s.count)
+            entries.append(StepEntry(s.request.req_id, toks, [s.count - 1] if s.samples else []))
+            decoding = decoding and s.count == 1 and s.samples
+        logits = engine.decode_step(entries) if decoding else engine.step(entries)
+        samplers = [s for s in plan if s.samples]
+        ids = llm.sampler(logits, [s.request.params for s in samplers],
+                          [s.request.number for s in samplers],
+                          [len(s.request.output) for s in samplers])
+        sampled = ids.tolist()
+        stats.steps += 1
+        for s in plan:
+            if s.count == 1 and s.start >= len(s.request.prompt):
+                stats.decode_tokens += 1
             else:
-                logits = engine.step(entries)
-            samplers = [s for s in plan if s.samples]
-            ids = self.sampler(logits, [s.request.params for s in samplers],
-                               [s.request.number for s in samplers],
-                               [len(s.request.output) for s in samplers])
-            sampled = ids.tolist()
-            stats.steps += 1
-            for s in plan:
-                if s.count == 1 and s.start >= len(s.request.prompt):
-                    stats.decode_tokens += 1
-                else:
-                    stats.prompt_tokens += s.count
-            stats.generated += len(sampled)
-            if log_steps:
-                stats.step_log.append([(s.request.req_id, s.start, s.count) for s in plan])
-            sched.step_done(plan, sampled)
-        engine.ops.check_status()
-        stats.preemptions = sched.num_preemptions
-        stats.seconds = time.perf_counter() - t0
-        return [Generation(r.prompt, r.output, r.finish_reason, r.preemptions) for r in requests]
+                stats.prompt_tokens += s.count
+        stats.generated += len(sampled)
+        if self.log_steps:
+            stats.step_log.append([(s.request.req_id, s.start, s.count) for s in plan])
+        sched.step_done(plan, sampled)
+        return [(s.request.req_id[1], t) for s, t in zip(samplers, sampled)]
+
+    def finish(self) -> list[Generation]:
+        self.llm.engine.ops.check_status()
+        self.stats.preemptions = self.sched.num_preemptions
+        self.stats.seconds = time.perf_counter() - self._t0
+        return [Generation(r.prompt, r.output, r.finish_reason, r.preemptions) for r in self.requests]

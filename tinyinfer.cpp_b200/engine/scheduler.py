@@ -45,6 +45,19 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def span(self, start: int, count: int) -> list[int]:
+        """Tokens start .. start + count of prompt followed by output, without joining the two."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
+
+    @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
 
@@ -119,7 +132,7 @@ class Scheduler:
         def take(req: Request, n: int) -> None:
             for g, k in enumerate(self.cache.pages_needed(req.req_id, n)):
                 taken[g] += k
-            planned.append(Scheduled(req, req.computed, n, req.computed + n == len(req.tokens)))
+            planned.append(Scheduled(req, req.computed, n, req.computed + n == req.num_tokens))
 
         # 1. one token for every decoding request
         for req in list(self.running):
@@ -184,7 +197,7 @@ class Scheduler:
                 reason = "stop"
             elif len(req.output) >= req.params.max_tokens:
                 reason = "length"
-            elif len(req.tokens) >= self.max_position:
+            elif req.num_tokens >= self.max_position:
                 reason = "context"
             if reason:
                 self.running.remove(req)
