@@ -21,7 +21,9 @@ from util import BF16_RTOL, FP32_RTOL, TINY, assert_close_logits, make_model, ra
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [70, 45, 120, 33, 90, 64, 17, 2], "B": [100, 9, 33, 64, 250, 77, 1, 130],
-           "C": [150, 40, 300, 64, 97, 210, 31], "D": [200, 33, 520, 64, 130, 95, 17, 2]}
+           "C": [150, 40, 300, 64, 97, 210, 31], "D": [200, 33, 520, 64, 130, 95, 17, 2],
+           "E": [300, 70, 150, 33, 260, 129]}
+PAGE = {"E": 64}              # the other configurations run with pages of 16 tokens
 TOL = {"float32": FP32_RTOL, "bfloat16": BF16_RTOL}
 FAMILIES = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
             "mixed": traces.mixed}
@@ -44,9 +46,9 @@ def _plain(model_dir, name, dtype):
     return _PLAIN[key]
 
 
-def _run_engine(model_dir, dtype, steps, max_tokens):
+def _run_engine(model_dir, dtype, steps, max_tokens, page_size=16):
     from tinyinfer_b200 import Engine, StepEntry
-    eng = Engine(model_dir, dtype=dtype, page_size=16, num_pages=-(-max_tokens // 16),
+    eng = Engine(model_dir, dtype=dtype, page_size=page_size, num_pages=-(-max_tokens // page_size),
                  max_requests=8)
     outputs = {}
     for s in steps:
@@ -72,12 +74,12 @@ def _compare(steps, outputs, plain, rtol, what):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_cuttings_match_plain(tmp_path_factory, name, family, dtype):
     model_dir = make_model(tmp_path_factory.getbasetemp(), name)
     steps = FAMILIES[family](_requests(name))
     max_tokens = traces.max_live_tokens(steps)
-    outputs = _run_engine(model_dir, dtype, steps, max_tokens)
+    outputs = _run_engine(model_dir, dtype, steps, max_tokens, PAGE.get(name, 16))
     err = _compare(steps, outputs, _plain(model_dir, name, dtype), TOL[dtype],
                    f"tiny-{name} {family} {dtype}")
     print(f"tiny-{name} {family} {dtype}: max error {err:.2e} of the largest logit")

@@ -32,7 +32,13 @@ TINY_D = dict(architectures=ARCH, num_hidden_layers=3, hidden_size=128, num_atte
               rope_theta=200000.0, rms_norm_eps=2e-6, tie_word_embeddings=True,
               max_position_embeddings=1024, sliding_window=40,
               layer_types=["full_attention", "sliding_attention", "full_attention"])
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# head size 128: prompts of more than 64 tokens take the tcgen05 products (with the QKV epilogue)
+# and the tcgen05 attention
+TINY_E = dict(architectures=ARCH, num_hidden_layers=2, hidden_size=192, num_attention_heads=3,
+              num_key_value_heads=1, head_dim=128, intermediate_size=272, vocab_size=777,
+              rope_theta=300000.0, rms_norm_eps=4e-6, tie_word_embeddings=False,
+              max_position_embeddings=640)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 FP32_RTOL = 2e-5      # of the largest reference logit: float32 engine against float64 plain
 BF16_RTOL = 2e-2      # bfloat16 engine against plain with the reference's rounding points
