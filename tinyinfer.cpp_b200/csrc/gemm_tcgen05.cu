@@ -161,6 +161,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 }
             }
+            bf16* qkv_dst = nullptr;                  // looked up while the products still run
+            if constexpr (BN == 256) {
+                if (mode == MODE_QKV) {
+                    const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
+                    qkv_dst = qkv::destination(qkv_e, row, item,
+                                               row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+                }
+            }
             ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -169,7 +177,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     // this thread's 128 columns are one head of its token (BN / 2 == head size)
                     const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
                     qkv::head(qkv_e, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + col_half * (BN / 2)),
-                              row, item, row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+                              row, item, qkv_dst);
                 }
             }
 #pragma unroll

@@ -195,15 +195,21 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
             const int buf = local & 1;
             const int m0 = (tile % tiles_m) * BM + (int)rank * 128, n0 = (tile / tiles_m) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            bf16* qkv_dst = nullptr;                  // looked up while the products still run
+            if (mode == MODE_QKV) {
+                const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
+                qkv_dst = qkv::destination(qkv_e, row, item,
+                                           row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+            }
             ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
             if (mode == MODE_QKV) {
                 // this thread's 128 columns are one head of its token (BN / 2 == head size)
                 const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
                 qkv::head(qkv_e, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + col_half * (BN / 2)),
-                          row, item, row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+                          row, item, qkv_dst);
             }
 #pragma unroll 1
             for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2) && mode != MODE_QKV; c0 += 32) {

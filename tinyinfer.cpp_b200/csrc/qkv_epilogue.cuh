@@ -38,11 +38,11 @@ __device__ __forceinline__ uint4 pack8(const float* y) {
                       *reinterpret_cast<unsigned*>(&c), *reinterpret_cast<unsigned*>(&d));
 }
 
-// `taddr`: tensor-memory address of this thread's lane at the first of the head's 128 columns.
-// `t`: the token (row of the product), `item`: the head among [queries, keys, values].  All 32
-// lanes of the warp call this (tcgen05.ld is warp-wide); `live` says whether the row and head exist.
-__device__ __forceinline__ void head(const Epilogue& e, unsigned taddr, int t, int item, bool live,
-                                     int* status) {
+// Where the head `item` (among [queries, keys, values]) of token `t` goes: a row of q_out or the
+// token's slot in its request's page; null if the row or head does not exist (`live`) or nothing
+// is to be written.  The look-ups (position, request, block table) depend on nothing the product
+// computes, so the caller does them before it waits for the accumulator.
+__device__ __forceinline__ bf16* destination(const Epilogue& e, int t, int item, bool live, int* status) {
     const int kind = item < e.num_heads ? 0 : item < e.num_heads + e.num_kv_heads ? 1 : 2;
     bf16* dst = nullptr;
     if (live) {
@@ -60,6 +60,14 @@ __device__ __forceinline__ void head(const Epilogue& e, unsigned taddr, int t, i
             }
         }
     }
+    return dst;
+}
+
+// `taddr`: tensor-memory address of this thread's lane at the first of the head's 128 columns.
+// `t`: the token (row of the product), `item`: the head, `dst` from destination().  All 32 lanes of
+// the warp call this (tcgen05.ld is warp-wide).
+__device__ __forceinline__ void head(const Epilogue& e, unsigned taddr, int t, int item, bf16* dst) {
+    const int kind = item < e.num_heads ? 0 : item < e.num_heads + e.num_kv_heads ? 1 : 2;
     float v[32];
     if (kind == 2) {                                   // values: rounded and stored as they are
 #pragma unroll 1
@@ -73,16 +81,17 @@ __device__ __forceinline__ void head(const Epilogue& e, unsigned taddr, int t, i
         }
         return;
     }
-    float ss = 0.0f;
+    float ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // four chains: one warp has little else to issue
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
         sm100::tmem_load32(taddr + (unsigned)(c * 32), v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) ss = fmaf(v[i], v[i], ss);
+        for (int i = 0; i < 32; ++i) ss4[i & 3] = fmaf(v[i], v[i], ss4[i & 3]);
     }
+    const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
     const float inv = 1.0f / sqrtf(ss / (float)HEAD_DIM + e.eps);
     const float* w = kind == 0 ? e.q_weight : e.k_weight;
-    const float* tab = e.table + (size_t)(live ? t : 0) * HEAD_DIM;
+    const float* tab = e.table + (size_t)(dst != nullptr ? t : 0) * HEAD_DIM;
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
         // the sines and cosines come from L2: all of this half's loads are in flight together
