@@ -212,6 +212,33 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory, graph):
     assert agree >= 40, f"bfloat16 greedy tokens agree in only {agree} of 48 places"
 
 
+def test_steps_launched_ahead_give_the_same_tokens(tmp_path_factory):
+    """With graphs a decode step is launched before the ids of the step before it are read, its
+    tokens fed on the device.  The same tokens as without that, also when a request stops on a
+    stop token in the middle (its extra step is dropped), when the pool is so small that
+    requests are preempted, and with sampling."""
+    from tinyinfer_b200 import LLM, SamplingParams
+    d = make_model(tmp_path_factory.getbasetemp(), "B")
+    prompts = [random_tokens(512, n, seed=n) for n in (5, 9, 33, 64)]
+    kw = dict(dtype="bfloat16", max_seq=128, max_num_seqs=4, page_size=16, cuda_graph=True)
+    base = LLM(d, lookahead=False, **kw)
+    plain = base.generate(prompts, SamplingParams(max_tokens=20))
+    # every request gets a stop token that it meets at a different place
+    stops = [SamplingParams(max_tokens=20, stop_token_ids=(o.tokens[3 + 4 * i],)) for i, o in enumerate(plain)]
+    temp = [SamplingParams(temperature=0.7, seed=3 + i, max_tokens=15) for i in range(4)]
+    for params, more in ((SamplingParams(max_tokens=20), {}), (stops, {}), (temp, {}),
+                         (SamplingParams(max_tokens=20), {"kv_tokens": 192})):
+        want = LLM(d, lookahead=False, **kw, **more).generate(prompts, params)
+        llm = LLM(d, **kw, **more)
+        got = llm.generate(prompts, params)
+        assert [o.tokens for o in got] == [o.tokens for o in want]
+        assert [o.finish_reason for o in got] == [o.finish_reason for o in want]
+        llm.engine.cache.check()
+        assert llm.engine.cache.live_requests() == []
+    assert any(o.finish_reason == "stop" and len(o.tokens) < 20
+               for o in LLM(d, **kw).generate(prompts, stops))
+
+
 def test_temperature_sampling_is_reproducible_across_cuttings(tmp_path_factory):
     """tiny-B, temperature 0.8 with a fixed seed: the same tokens whether prompts run whole or
     in portions of 16 beside decoding, eager or from graphs."""

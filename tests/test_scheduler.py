@@ -142,3 +142,68 @@ def test_portion_is_shortened_to_the_pages_there_are():
     sched.add(_req("b", 10, max_tokens=2))                       # 1 page: fits
     plan, _ = _run_step(cache, sched)
     assert [(s.request.req_id, s.count) for s in plan] == [("a", 1), ("b", 10)]
+
+
+def test_lookahead_tells_the_next_step_only_when_it_is_certain():
+    """The step after a running one can be told ahead when all its requests choose a token now,
+    none ends by its length, nothing waits and the pages are there."""
+    cache, sched = _setup(num_pages=5, max_num_seqs=2, budget=64, eos=(9,))
+    sched.add(_req("a", 20, max_tokens=3))
+    sched.add(_req("b", 31, max_tokens=5))
+    sched.add(_req("c", 4))                                     # waits for a request slot
+    plan = sched.schedule()
+    cache.reserve_step([(s.request.req_id, s.count) for s in plan])
+    assert sched.lookahead(plan) is None                        # c waits for admission
+    sched.waiting.clear()
+    told = sched.lookahead(plan)
+    assert [(s.request.req_id, s.start, s.count, s.samples) for s in told] == \
+        [("a", 20, 1, True), ("b", 31, 1, True)]
+    # the step told ahead is put on the device; only then are the first step's tokens known
+    cache.reserve_step([(s.request.req_id, s.count) for s in told])
+    sched.step_done(plan, [5, 5])
+    third = sched.lookahead(told)
+    assert [(s.request.req_id, s.start) for s in third] == [("a", 21), ("b", 32)]
+    cache.reserve_step([(s.request.req_id, s.count) for s in third])
+    sched.step_done(told, [5, 5])
+    assert sched.lookahead(third) is None                       # a's third token is its last
+    fin = sched.step_done(third, [5, 5])
+    assert [r.req_id for r in fin] == ["a"] and fin[0].output == [5, 5, 5]
+    plan = sched.schedule()
+    assert [(s.request.req_id, s.start) for s in plan] == [("b", 33)]
+    cache.check()
+
+
+def test_lookahead_needs_the_pages_and_no_unfinished_prompt():
+    cache, sched = _setup(num_pages=4, max_num_seqs=2, budget=40, chunk=None)
+    sched.add(_req("a", 32, max_tokens=9))                      # two full pages: its next token needs a third
+    sched.add(_req("b", 16, max_tokens=9))                      # cut: 8 tokens fit the budget
+    plan = sched.schedule()
+    assert [(s.request.req_id, s.count, s.samples) for s in plan] == [("a", 32, True), ("b", 8, False)]
+    cache.reserve_step([(s.request.req_id, s.count) for s in plan])
+    assert sched.lookahead(plan) is None                        # b is still inside its prompt
+    sched.step_done(plan, [5])
+    plan = sched.schedule()
+    cache.reserve_step([(s.request.req_id, s.count) for s in plan])
+    assert [(s.request.req_id, s.count) for s in plan] == [("a", 1), ("b", 8)]
+    assert sched.lookahead(plan) is None                        # all four pages are taken: b's 17th token has none
+    cache.check()
+
+
+def test_a_request_that_stops_drops_the_token_of_the_step_told_ahead():
+    cache, sched = _setup(eos=(9,))
+    sched.add(_req("a", 3, max_tokens=50))
+    sched.add(_req("b", 5, max_tokens=50))
+    plan = sched.schedule()
+    cache.reserve_step([(s.request.req_id, s.count) for s in plan])
+    told = sched.lookahead(plan)
+    cache.reserve_step([(s.request.req_id, s.count) for s in told])
+    fin = sched.step_done(plan, [9, 4])                         # a stops on the token nobody knew
+    assert [r.req_id for r in fin] == ["a"] and cache.live_requests() == ["b"]
+    assert sched.lookahead(told) is None                        # the batch has changed
+    assert sched.step_done(told, [7, 8]) == []
+    a, b = plan[0].request, plan[1].request
+    assert a.output == [9] and a.finish_reason == "stop"
+    assert b.output == [4, 8] and b.computed == 6
+    plan = sched.schedule()
+    assert [(s.request.req_id, s.start, s.count) for s in plan] == [("b", 6, 1)]
+    cache.check()

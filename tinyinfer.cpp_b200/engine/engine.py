@@ -154,9 +154,12 @@ class Engine:
             self.cache.release_passed(e.req_id)
         return logits
 
-    def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def decode_step(self, entries: Sequence[StepEntry], device_tokens=None) -> torch.Tensor:
         """A step in which every request brings one token and wants its logits, replayed from a
-        CUDA graph.  Returns ``[requests, vocab]``; the tensor is reused by the next call."""
+        CUDA graph.  Returns ``[requests, vocab]``; the tensor is reused by the next call.
+        With ``device_tokens`` (int32 on the device, one per entry, each a valid id) the entries'
+        own tokens are placeholders and the step runs the given ones: the ids that the step
+        before chose, fed back without a round trip through the host."""
         entries = list(entries)
         vocab = self.plan.vocab_size
         for e in entries:
@@ -166,11 +169,15 @@ class Engine:
                 raise ValueError(f"request {e.req_id!r}: token id {e.tokens[0]} is outside [0, {vocab})")
         if not entries:
             return torch.empty((0, vocab), dtype=torch.float32, device=self.device)
+        if device_tokens is not None and (device_tokens.dtype != torch.int32
+                                          or tuple(device_tokens.shape) != (len(entries),)
+                                          or device_tokens.device != self.device):
+            raise ValueError("device_tokens must be int32 on the engine's device, one per entry")
         if self._graphs is None:
             from .graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)
         starts = self.reserve(entries)
-        logits = self._graphs.run(entries, starts)
+        logits = self._graphs.run(entries, starts, device_tokens)
         for e in entries:
             self.cache.release_passed(e.req_id)
         return logits

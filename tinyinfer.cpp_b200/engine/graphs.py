@@ -68,10 +68,13 @@ class _Bucket:
             self._reset_row(i, cache)
             self.row_req[i] = _PADDING
 
-    def fill(self, engine, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
+    def fill(self, engine, entries: Sequence[StepEntry], starts: Sequence[int],
+             device_tokens=None) -> None:
         """Stage the step's integers and start their copy to the device.  A host mirror keeps what
         the rows held last time: a request that sits in the same row as before only gets the
-        block-table entries it has gained since (decoding adds a page every ``page_size`` steps)."""
+        block-table entries it has gained since (decoding adds a page every ``page_size`` steps).
+        ``device_tokens`` (int32, one per entry, on the device) replaces the entries' tokens: the
+        ids the previous step chose, which the host has not read yet."""
         cache = engine.cache
         b, w = self.size, self.width
         n = len(entries)
@@ -104,6 +107,8 @@ class _Bucket:
         host = self.hosts[turn]
         np.copyto(host.numpy(), m)
         self.dev.copy_(host, non_blocking=True)
+        if device_tokens is not None:
+            self.dev[0:n].copy_(device_tokens)
         done = torch.cuda.Event()
         done.record()
         self.copied[turn] = done
@@ -130,13 +135,14 @@ class DecodeGraphs:
         self.engine = engine
         self.buckets: dict[int, _Bucket] = {}
 
-    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int],
+            device_tokens=None) -> torch.Tensor:
         eng = self.engine
         size = bucket_of(len(entries))
         bk = self.buckets.get(size)
         if bk is None:
             bk = self.buckets[size] = _Bucket(eng, size)
-        bk.fill(eng, entries, starts)
+        bk.fill(eng, entries, starts, device_tokens)
         if bk.graph is None:
             # run once outside capture (loads kernels, sizes the allocator), then capture
             side = torch.cuda.Stream(device=eng.device)

@@ -179,18 +179,47 @@ class Scheduler:
             n = max(0, end - length)
         return n
 
+    def lookahead(self, plan: Sequence[Scheduled]) -> Optional[list[Scheduled]]:
+        """The plan of the step after ``plan``, told while ``plan`` is still running and its tokens
+        are unknown (its pages are reserved, ``step_done`` has not been called for it): one token
+        for each of its requests, in the same order.  None unless that is certain but for a stop
+        token: every request of ``plan`` is choosing a token now and none ends by its length,
+        nothing waits for admission, and the pages are there.  A request that does stop on the
+        unknown token runs one token too many in the step told here; ``step_done`` drops it."""
+        if self.waiting or len(plan) != len(self.running):
+            return None
+        taken = [0] * len(self.cache.groups)
+        free = self.cache.free_pages()
+        told = []
+        for s in plan:
+            req = s.request
+            if req.state != RUNNING or not s.samples:
+                return None
+            if (len(req.output) + 1 >= req.params.max_tokens
+                    or req.num_tokens + 1 >= self.max_position):
+                return None
+            for g, k in enumerate(self.cache.pages_needed(req.req_id, 1)):
+                taken[g] += k
+                if taken[g] > free[g]:
+                    return None
+            told.append(Scheduled(req, s.start + s.count, 1, True))
+        return told
+
     # ---- results -------------------------------------------------------------------------
     def step_done(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
         """Account for a finished step; ``sampled`` holds one token per entry that samples, in
-        plan order.  Returns the requests that finished."""
+        plan order.  Returns the requests that finished.  An entry whose request stopped while
+        the step was already running (``lookahead``) is dropped with its token."""
         finished = []
         it = iter(sampled)
         for s in plan:
             req = s.request
+            tok = int(next(it)) if s.samples else None
+            if req.state != RUNNING:
+                continue
             req.computed += s.count
             if not s.samples:
                 continue
-            tok = int(next(it))
             req.output.append(tok)
             reason = None
             if tok in self.eos or tok in req.params.stop_token_ids:
