@@ -236,6 +236,35 @@ def measure_prefill(engine, tokens, reps, torch):
     return statistics.median(times)
 
 
+def measure_mixed(engine, decoders, chunk, context, torch):
+    """One step with ``decoders`` requests decoding near ``context`` and a portion of ``chunk``
+    tokens of another request's prompt beside them (the step shape of chunked prefill under
+    load).  The portion moves along its prompt from step to step; the first three steps run
+    eagerly and capture the shape's graph.  Returns ms per step (median)."""
+    from tinyinfer_b200 import StepEntry
+    g = torch.Generator().manual_seed(2)
+    timed = max(1, min(5, context // chunk - 3))
+    ids = fill_requests(engine, decoders, context - timed - 5, torch)
+    prompt = torch.randint(0, engine.plan.vocab_size, ((timed + 3) * chunk,), generator=g).tolist()
+    times = []
+    try:
+        for i in range(timed + 3):
+            entries = [StepEntry(r, [1], [0]) for r in ids]
+            entries.append(StepEntry(("bench", "prompt"), prompt[i * chunk:(i + 1) * chunk], []))
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            engine.step(entries)
+            stop.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(start.elapsed_time(stop))
+    finally:
+        for r in ids + [("bench", "prompt")]:
+            engine.finish(r)
+    return statistics.median(times)
+
+
 def measure_chains(engine, batch, torch):
     """Each decode product alone: a CUDA graph of 56 dependent launches with distinct weights,
     timed with CUDA events; microseconds per launch."""
@@ -296,7 +325,7 @@ def main() -> int:
     ap.add_argument("--shape", choices=list(SHAPES), default="0.6b", help="layer sizes of the model")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per cache page")
-    ap.add_argument("--only", choices=["decode", "prefill", "chains"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
 
@@ -322,7 +351,7 @@ def main() -> int:
         cfg["num_hidden_layers"] = args.layers
     pk, pk_kind = peaks()
     nums = model_numbers(cfg)
-    max_batch = max(args.batch, 1 if (args.no_points or args.only) else 64)
+    max_batch = max(args.batch, 1 if (args.no_points or args.only not in (None, "mixed")) else 64)
     llm = LLM(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size, max_seq=args.context,
               max_num_seqs=max_batch + 1, kv_tokens=max_batch * args.context, cuda_graph=True)
     engine = llm.engine
@@ -335,6 +364,10 @@ def main() -> int:
     if args.only == "chains":
         print(json.dumps({"only": "chains", "batch": args.batch, "us_per_launch":
                           measure_chains(engine, args.batch, torch)}))
+        return 0
+    if args.only == "mixed":
+        mx_ms = measure_mixed(engine, 63, 512, args.context, torch)
+        print(json.dumps({"only": "mixed", "decoding": 63, "portion": 512, "ms": round(mx_ms, 3)}))
         return 0
     if args.only == "prefill":
         pf_ms = measure_prefill(engine, 2048, max(1, args.steps), torch)
@@ -351,6 +384,9 @@ def main() -> int:
         for b in (1, 64):
             pms, _, _ = measure_decode(engine, b, args.context, min(args.steps, 32), warmup, torch)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+        # chunked prefill under load: 63 requests decode beside a 512-token portion of a prompt
+        mx_ms = measure_mixed(engine, 63, 512, args.context, torch)
+        points["mixed_63_decoding_512_portion"] = round((63 + 512) / (mx_ms * 1e-3), 1)
 
     pf_tokens = 2048
     pf_ms = measure_prefill(engine, pf_tokens, 3, torch)
