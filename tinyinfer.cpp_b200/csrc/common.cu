@@ -21,5 +21,3 @@ int ti_check_launch(const char* what) {
     if (err == cudaSuccess) return 0;
     return ti_fail("%s: %s", what, cudaGetErrorString(err));
 }
-
-extern "C" int ti_abi_version() { return 1; }

@@ -54,7 +54,8 @@ class _Bucket:
             token_ids=d[0:b], positions=d[b:2 * b], req_of_tok=ar,
             cu_q=torch.arange(b + 1, dtype=torch.int32, device=dev),
             q_start_dev=d[b:2 * b], ctx_len_dev=d[2 * b:3 * b], logit_rows=ar,
-            state_slots=d[3 * b:4 * b], decode_rows=ar, chunk_rows=ar[:0], chunk_tiles=ar[:0].view(-1, 3), chunk_tiles_big=ar[:0].view(-1, 3),
+            state_slots=d[3 * b:4 * b], decode_rows=ar, chunk_rows=ar[:0],
+            chunk_tiles=ar[:0].view(-1, 3), chunk_tiles_big=ar[:0].view(-1, 3),
             max_position=engine.plan.max_position, block_tables=tables)
         self.graph = None
         self.logits = None

@@ -23,8 +23,8 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 # library name -> sources (each library is self-contained and links common.cu)
 LIBRARIES = {
     "core": ["common.cu", "rowwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
-    "bf16": ["common.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2sm.cu", "gemm_tcgen05_few.cu", "attn_decode.cu", "attn_prefill.cu",
-             "attn_prefill_tc.cu"],
+    "bf16": ["common.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2sm.cu",
+             "gemm_tcgen05_few.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],
 }
 
 NVCC_FLAGS = [

@@ -303,8 +303,9 @@ class CudaOps:
 
     def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
                        num_heads, num_kv_heads, head_dim):
-        """``qk_norm_rope_store`` of ``h @ w_qkv.T``.  Prompt portions with head size 128 run as one tcgen05 product whose epilogue
-        norms, rotates and stores each head, so the float32 product never reaches memory."""
+        """``qk_norm_rope_store`` of ``h @ w_qkv.T``.  Prompt portions with head size 128 run as
+        one tcgen05 product whose epilogue norms, rotates and stores each head, so the float32
+        product never reaches memory."""
         t = q_out.shape[0]
         pages, bt = cache.pages, cache.block_table
         fused = (self.fuse_qkv_epilogue and t > 64 and head_dim == 128 and w_qkv.dtype == torch.bfloat16

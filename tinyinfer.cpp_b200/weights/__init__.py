@@ -5,6 +5,7 @@ from .loader import (WeightsError, check_tensors, load_gguf, load_model_weights,
 from .random_init import random_tensor, write_random_model
 from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
 
-__all__ = ["GgufError", "GgufFile", "load_gguf", "load_model_weights_gguf", "write_gguf", "SafetensorsError", "SafetensorsFile", "WeightsError", "check_tensors",
-           "load_model_weights", "random_tensor", "storage_dtype", "write_random_model",
+__all__ = ["GgufError", "GgufFile", "SafetensorsError", "SafetensorsFile", "WeightsError",
+           "check_tensors", "load_gguf", "load_model_weights", "load_model_weights_gguf",
+           "random_tensor", "storage_dtype", "write_gguf", "write_random_model",
            "write_safetensors"]
