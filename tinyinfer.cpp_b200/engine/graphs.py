@@ -12,12 +12,29 @@ checks replay against eager the same way (src/inference.cu:297-341).
 """
 from __future__ import annotations
 
+import gc
 from typing import Sequence
 
 import numpy as np
 import torch
 
 from .batch import StepBatch, StepEntry, build_step_batch
+
+
+def capture(graph: "torch.cuda.CUDAGraph", run):
+    """Capture ``run()`` into ``graph`` and return what it returns.  Python's cycle collector
+    stays off meanwhile and runs once before: an old engine it finds (engines and their graphs
+    refer to each other) would destroy CUDA graphs and free device memory in the middle of the
+    capture, which CUDA refuses and which makes the capture invalid."""
+    gc.collect()
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            return run()
+    finally:
+        if was_on:
+            gc.enable()
 
 
 def bucket_of(n: int) -> int:
@@ -154,8 +171,7 @@ class DecodeGraphs:
             torch.cuda.synchronize(eng.device)
             graph = torch.cuda.CUDAGraph()
             before = getattr(eng.ops, "launches", 0)
-            with torch.cuda.graph(graph):
-                bk.logits = eng.forward(bk.batch)
+            bk.logits = capture(graph, lambda: eng.forward(bk.batch))
             bk.graph = graph
             bk.launches = getattr(eng.ops, "launches", 0) - before
         bk.graph.replay()
@@ -207,8 +223,7 @@ class StepGraphs:
         torch.cuda.synchronize(eng.device)
         graph = torch.cuda.CUDAGraph()
         before = getattr(eng.ops, "launches", 0)
-        with torch.cuda.graph(graph):
-            static_logits = eng.forward(batch)
+        static_logits = capture(graph, lambda: eng.forward(batch))
         self.graphs[key] = {"graph": graph, "buffer": buffer, "logits": static_logits,
                             "launches": getattr(eng.ops, "launches", 0) - before}
         while len(self.graphs) > self.capacity:
