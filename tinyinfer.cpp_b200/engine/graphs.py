@@ -13,6 +13,7 @@ checks replay against eager the same way (src/inference.cu:297-341).
 from __future__ import annotations
 
 import gc
+import weakref
 from typing import Sequence
 
 import numpy as np
@@ -148,9 +149,21 @@ class _Bucket:
 _PADDING = object()
 
 
-class DecodeGraphs:
+class _OfEngine:
+    """Keeps its engine by a weak reference: the engine owns this object, and a cycle between the
+    two would leave the engine's graphs and device memory to the cycle collector."""
+
     def __init__(self, engine):
-        self.engine = engine
+        self._engine = weakref.ref(engine)
+
+    @property
+    def engine(self):
+        return self._engine()
+
+
+class DecodeGraphs(_OfEngine):
+    def __init__(self, engine):
+        super().__init__(engine)
         self.buckets: dict[int, _Bucket] = {}
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int],
@@ -180,7 +193,7 @@ class DecodeGraphs:
         return bk.logits[:len(entries)]
 
 
-class StepGraphs:
+class StepGraphs(_OfEngine):
     """CUDA-graph replay of whole steps of any shape (prompt portions, mixed batches).
 
     A step's launches depend only on its entries' token counts and wanted places: positions,
@@ -193,7 +206,7 @@ class StepGraphs:
 
     def __init__(self, engine, capacity: int = 8):
         from collections import Counter, OrderedDict
-        self.engine = engine
+        super().__init__(engine)
         self.capacity = capacity
         self.graphs: "OrderedDict[tuple, dict]" = OrderedDict()
         self.seen: Counter = Counter()
