@@ -333,7 +333,9 @@ def main() -> int:
         print(json.dumps({"impl": "reference", "unavailable":
                           "beyondHJM/tinyinfer.cpp is a CMake C++/CUDA project; pip reports "
                           "\"Neither 'setup.py' nor 'pyproject.toml' found\", so it cannot be "
-                          "installed offline as the contract asks"}))
+                          "installed offline as the contract asks; built with its own CMakeLists for "
+                          "sm_100 instead, its program ended its first prefill on a B200 with 'CUDA error "
+                          "src/inference.cu:242: an illegal memory access was encountered' and is not run again"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU; this engine does no work on several (asked for {args.gpus})")
