@@ -178,6 +178,31 @@ def decode_device_timed(engine, ids, steps, warmup, torch):
     return ms / steps, clocks.summary(), engine.ops.launches - before
 
 
+def decode_eager_timed(engine, batch, context, steps, warmup, torch):
+    """The same decode steps launched kernel by kernel (no CUDA graph): what the graphs save."""
+    from tinyinfer_b200 import StepEntry
+    ids = fill_requests(engine, batch, context - (steps + warmup) - 2, torch)
+    out = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    graphs, engine._step_graphs = engine._step_graphs, None
+    try:
+        def one():
+            engine.ops.argmax(engine.step([StepEntry(r, [1], [0]) for r in ids]), out)
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps
+    finally:
+        engine._step_graphs = graphs
+        for r in ids:
+            engine.finish(r)
+
+
 def decode_e2e(llm, batch, context, steps, warmup, torch):
     """The same steps through the Python entry point (``LLM.start`` / ``Session.step``): prompts
     are run first; then every timed step packs the host's token ids, copies them to the device
@@ -386,6 +411,8 @@ def main() -> int:
         for b in (1, 64):
             pms, _, _ = measure_decode(engine, b, args.context, min(args.steps, 32), warmup, torch)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+        eager_ms = decode_eager_timed(engine, args.batch, args.context, min(args.steps, 32), warmup, torch)
+        points[f"decode_b{args.batch}_no_graph"] = round(args.batch / (eager_ms * 1e-3), 1)
         # chunked prefill under load: 63 requests decode beside a 512-token portion of a prompt
         mx_ms = measure_mixed(engine, 63, 512, args.context, torch)
         points["mixed_63_decoding_512_portion"] = round((63 + 512) / (mx_ms * 1e-3), 1)
