@@ -35,12 +35,6 @@ template <int BN> struct Tile {
 enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2, MODE_QKV = 3 };
 enum { TI_ERR_TIMEOUT = 2 };
 
-// silu(g) * u = g * u / (1 + e^-g) with the fast exponential and reciprocal (relative error about
-// 1e-6, far below the bfloat16 rounding of the result); e^-g = inf for very negative g gives -0.
-__device__ __forceinline__ float silu_mul(float g, float u) {
-    return g * u * __frcp_rn(1.0f + __expf(-g));
-}
-
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -73,6 +67,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tmem_alloc(tmem_slot, T::TMEM_COLS);
     }
+    __shared__ float qkv_norm_w[2 * qkv::HEAD_DIM];
+    if (mode == MODE_QKV) qkv::load_norm_weights(qkv_e, qkv_norm_w, threadIdx.x, THREADS);
     pdl_launch();
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -161,24 +157,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 }
             }
-            bf16* qkv_dst = nullptr;                  // looked up while the products still run
+            // where the tile's two heads go, and this warp's half of the token's sines and cosines:
+            // requested while the products still run
+            bf16 *qkv_dst0 = nullptr, *qkv_dst1 = nullptr;
+            qkv::Angles angles;
             if constexpr (BN == 256) {
                 if (mode == MODE_QKV) {
-                    const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
-                    qkv_dst = qkv::destination(qkv_e, row, item,
-                                               row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+                    const int item0 = n0 / qkv::HEAD_DIM, items = qkv_e.num_heads + 2 * qkv_e.num_kv_heads;
+                    qkv_dst0 = qkv::destination(qkv_e, row, item0, row < m && item0 < items, status);
+                    qkv_dst1 = qkv::destination(qkv_e, row, item0 + 1, row < m && item0 + 1 < items, status);
+                    qkv::load_angles(qkv_e, row, col_half, row < m, angles);
                 }
             }
             ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             if constexpr (BN == 256) {
-                if (mode == MODE_QKV) {
-                    // this thread's 128 columns are one head of its token (BN / 2 == head size)
-                    const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
-                    qkv::head(qkv_e, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + col_half * (BN / 2)),
-                              row, item, qkv_dst);
-                }
+                if (mode == MODE_QKV)
+                    qkv::two_heads(qkv_e, qkv_norm_w, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN),
+                                   n0 / qkv::HEAD_DIM, col_half, qkv_dst0, qkv_dst1, angles);
             }
 #pragma unroll
             for (int cc = 0; cc < BN / 64; ++cc) {
@@ -321,9 +318,9 @@ extern "C" int ti_gemm_tcgen05_qkv(const void* a, const void* w, int m, int k, i
     const int n = (num_heads + 2 * num_kv_heads) * qkv::HEAD_DIM;
     TI_REQUIRE(k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tcgen05_qkv: K=%d and the row strides %d, %d must be multiples of 8", k, lda, ldw);
-    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
-               (uintptr_t)pages % 16 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)q_weight % 16 == 0 &&
-               (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned");
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 32 == 0 &&
+               (uintptr_t)pages % 32 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)q_weight % 16 == 0 &&
+               (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned, q_out and the pages 32-byte");
     const qkv::Epilogue e{q_weight, k_weight, eps, table, positions, req_of_tok, block_table, bt_stride,
                           (bf16*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, (bf16*)q_out};
     return launch_tiles(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, true, status, stream);

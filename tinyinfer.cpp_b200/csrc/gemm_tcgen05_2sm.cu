@@ -38,12 +38,6 @@ template <int BN> struct Pair {
 enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2, MODE_QKV = 3 };
 enum { TI_ERR_TIMEOUT = 2 };
 
-// silu(g) * u = g * u / (1 + e^-g) with the fast exponential and reciprocal (relative error about
-// 1e-6, far below the bfloat16 rounding of the result); e^-g = inf for very negative g gives -0.
-__device__ __forceinline__ float silu_mul(float g, float u) {
-    return g * u * __frcp_rn(1.0f + __expf(-g));
-}
-
 __device__ __forceinline__ unsigned cluster_rank() {
     unsigned r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -123,6 +117,8 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                      ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
     }
+    __shared__ float qkv_norm_w[2 * qkv::HEAD_DIM];
+    if (mode == MODE_QKV) qkv::load_norm_weights(qkv_e, qkv_norm_w, threadIdx.x, THREADS);
     pdl_launch();
     tc_fence_before();
     __syncthreads();
@@ -196,21 +192,22 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const int buf = local & 1;
             const int m0 = (tile % tiles_m) * BM + (int)rank * 128, n0 = (tile / tiles_m) * BN;
             const int row = m0 + quarter * 32 + lane;
-            bf16* qkv_dst = nullptr;                  // looked up while the products still run
+            // where the tile's two heads go, and this warp's half of the token's sines and cosines:
+            // requested while the products still run
+            bf16 *qkv_dst0 = nullptr, *qkv_dst1 = nullptr;
+            qkv::Angles angles;
             if (mode == MODE_QKV) {
-                const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
-                qkv_dst = qkv::destination(qkv_e, row, item,
-                                           row < m && item < qkv_e.num_heads + 2 * qkv_e.num_kv_heads, status);
+                const int item0 = n0 / qkv::HEAD_DIM, items = qkv_e.num_heads + 2 * qkv_e.num_kv_heads;
+                qkv_dst0 = qkv::destination(qkv_e, row, item0, row < m && item0 < items, status);
+                qkv_dst1 = qkv::destination(qkv_e, row, item0 + 1, row < m && item0 + 1 < items, status);
+                qkv::load_angles(qkv_e, row, col_half, row < m, angles);
             }
             ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            if (mode == MODE_QKV) {
-                // this thread's 128 columns are one head of its token (BN / 2 == head size)
-                const int item = (n0 + col_half * (BN / 2)) / qkv::HEAD_DIM;
-                qkv::head(qkv_e, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + col_half * (BN / 2)),
-                          row, item, qkv_dst);
-            }
+            if (mode == MODE_QKV)
+                qkv::two_heads(qkv_e, qkv_norm_w, tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN),
+                               n0 / qkv::HEAD_DIM, col_half, qkv_dst0, qkv_dst1, angles);
 #pragma unroll 1
             for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2) && mode != MODE_QKV; c0 += 32) {
                 float v[32];
@@ -323,9 +320,9 @@ extern "C" int ti_gemm_tcgen05_2sm_qkv(const void* a, const void* w, int m, int 
     const int n = (num_heads + 2 * num_kv_heads) * qkv::HEAD_DIM;
     TI_REQUIRE(k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tcgen05_2sm_qkv: K=%d and the row strides %d, %d must be multiples of 8", k, lda, ldw);
-    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
-               (uintptr_t)pages % 16 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)q_weight % 16 == 0 &&
-               (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_2sm_qkv: operands must be 16-byte aligned");
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 32 == 0 &&
+               (uintptr_t)pages % 32 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)q_weight % 16 == 0 &&
+               (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_2sm_qkv: operands must be 16-byte aligned, q_out and the pages 32-byte");
     const qkv::Epilogue e{q_weight, k_weight, eps, table, positions, req_of_tok, block_table, bt_stride,
                           (bf16*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, (bf16*)q_out};
     return launch_pairs(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, status, stream);

@@ -1,7 +1,7 @@
 // Epilogue of the QKV product of a prompt portion, run by the tcgen05 kernels in place of storing
-// the product: a thread that owns one token's 128 accumulator columns of one head (head size 128)
-// applies the head's RMSNorm (queries and keys), rotates it (NeoX pairs k, k + 64) by the token's
-// position, and writes bfloat16: queries to q_out, keys and values into the token's slot of its
+// the product: the threads that own a token's accumulator columns of a head (head size 128)
+// apply the head's RMSNorm (queries and keys), rotate it (NeoX pairs k, k + 64) by the token's
+// position, and write bfloat16: queries to q_out, keys and values into the token's slot of its
 // request's page.  The float32 product never reaches memory, and the separate norm / rotation /
 // store launch and its read of the product are saved.
 //
@@ -63,69 +63,82 @@ __device__ __forceinline__ bf16* destination(const Epilogue& e, int t, int item,
     return dst;
 }
 
-// `taddr`: tensor-memory address of this thread's lane at the first of the head's 128 columns.
-// `t`: the token (row of the product), `item`: the head, `dst` from destination().  All 32 lanes of
-// the warp call this (tcgen05.ld is warp-wide).
-__device__ __forceinline__ void head(const Epilogue& e, unsigned taddr, int t, int item, bf16* dst) {
-    const int kind = item < e.num_heads ? 0 : item < e.num_heads + e.num_kv_heads ? 1 : 2;
-    float v[32];
-    if (kind == 2) {                                   // values: rounded and stored as they are
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-            sm100::tmem_load32(taddr + (unsigned)(c * 32), v);
-            if (dst != nullptr) {
+// A 256-column tile holds two heads of 128 tokens.  A warp of the epilogue has 32 of the tokens
+// (its lanes of tensor memory) and, of both heads, the rotation pairs 32 h .. 32 h + 31 (columns k
+// and k + 64), h = 0 or 1: so a thread needs half of its token's sines and cosines and uses them
+// for both heads.  It requests them, like the destinations, before it waits for the accumulator;
+// after the wait only tensor memory, arithmetic and 32-byte stores remain.
+struct Angles {
+    float4 cs[8], sn[8];         // of pairs 32 h .. 32 h + 31
+};
+
+__device__ __forceinline__ void load_angles(const Epilogue& e, int t, int h, bool live, Angles& a) {
+    const float* tab = e.table + (size_t)(live ? t : 0) * HEAD_DIM + h * 32;
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = pack8(v + j * 8);
+    for (int j = 0; j < 8; ++j) {
+        a.cs[j] = __ldg(reinterpret_cast<const float4*>(tab + j * 4));
+        a.sn[j] = __ldg(reinterpret_cast<const float4*>(tab + HALF + j * 4));
+    }
+}
+
+// The q and k norm weights, [2][128], copied once into shared memory by the block.
+__device__ __forceinline__ void load_norm_weights(const Epilogue& e, float* norm_w, int tid, int threads) {
+    for (int i = tid; i < 2 * HEAD_DIM; i += threads)
+        norm_w[i] = i < HEAD_DIM ? e.q_weight[i] : e.k_weight[i - HEAD_DIM];
+}
+
+__device__ __forceinline__ void store16(bf16* dst, const float* y) {      // 32 bytes, 32-byte aligned
+    const uint4 a = pack8(y), b = pack8(y + 8);
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(a.x), "r"(a.y),
+                 "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+
+// `taddr`: tensor-memory address of this thread's lane at the tile's first column; `item0`: the
+// tile's first head; `h`: which half of the pairs; `dst0`, `dst1` from destination() for the two
+// heads; `norm_w`: shared memory filled by load_norm_weights.  All 32 lanes of the warp call this
+// (tcgen05.ld is warp-wide).
+__device__ __forceinline__ void two_heads(const Epilogue& e, const float* norm_w, unsigned taddr, int item0,
+                                          int h, bf16* dst0, bf16* dst1, const Angles& a) {
+    const float* cs = reinterpret_cast<const float*>(a.cs);
+    const float* sn = reinterpret_cast<const float*>(a.sn);
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+        const int item = item0 + which;
+        if (item >= e.num_heads + 2 * e.num_kv_heads) break;           // the same for the whole warp
+        const int kind = item < e.num_heads ? 0 : item < e.num_heads + e.num_kv_heads ? 1 : 2;
+        bf16* dst = which ? dst1 : dst0;
+        const unsigned base = taddr + (unsigned)(which * HEAD_DIM);
+        float inv = 1.0f;
+        if (kind != 2) {
+            float ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};          // four chains: one warp has little else to issue
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                sm100::tmem_load32(base + (unsigned)(c * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) ss4[i & 3] = fmaf(v[i], v[i], ss4[i & 3]);
             }
+            const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
+            inv = 1.0f / sqrtf(ss / (float)HEAD_DIM + e.eps);
         }
-        return;
-    }
-    float ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // four chains: one warp has little else to issue
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-        sm100::tmem_load32(taddr + (unsigned)(c * 32), v);
+        const float* w = norm_w + (kind == 1 ? HEAD_DIM : 0);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) ss4[i & 3] = fmaf(v[i], v[i], ss4[i & 3]);
-    }
-    const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
-    const float inv = 1.0f / sqrtf(ss / (float)HEAD_DIM + e.eps);
-    const float* w = kind == 0 ? e.q_weight : e.k_weight;
-    const float* tab = e.table + (size_t)(dst != nullptr ? t : 0) * HEAD_DIM;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-        // the sines and cosines come from L2: all of this half's loads are in flight together
-        float4 cs[8], sn[8];
+        for (int c = 0; c < 2; ++c) {
+            float lo[16], hi[16];
+            sm100::tmem_load16(base + (unsigned)(h * 32 + c * 16), lo);
+            sm100::tmem_load16(base + (unsigned)(HALF + h * 32 + c * 16), hi);
+            if (dst == nullptr) continue;
+            if (kind != 2) {                                   // values are rounded and stored as they are
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            cs[j] = __ldg(reinterpret_cast<const float4*>(tab + c * 32 + j * 4));
-            sn[j] = __ldg(reinterpret_cast<const float4*>(tab + HALF + c * 32 + j * 4));
-        }
-        float hi[32];
-        sm100::tmem_load32(taddr + (unsigned)(c * 32), v);
-        sm100::tmem_load32(taddr + (unsigned)(HALF + c * 32), hi);
-        if (dst == nullptr) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float y0[8], y1[8];
-#pragma unroll
-            for (int i = 0; i < 8; i += 4) {
-                const int k = c * 32 + j * 8 + i;
-                const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + k));
-                const float4 w1 = __ldg(reinterpret_cast<const float4*>(w + HALF + k));
-                const float4 c4 = cs[j * 2 + i / 4], s4 = sn[j * 2 + i / 4];
-                const float cs_[4] = {c4.x, c4.y, c4.z, c4.w}, sn_[4] = {s4.x, s4.y, s4.z, s4.w};
-                const float w0_[4] = {w0.x, w0.y, w0.z, w0.w}, w1_[4] = {w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float x0 = v[j * 8 + i + u] * inv * w0_[u];
-                    const float x1 = hi[j * 8 + i + u] * inv * w1_[u];
-                    y0[i + u] = x0 * cs_[u] - x1 * sn_[u];
-                    y1[i + u] = x0 * sn_[u] + x1 * cs_[u];
+                for (int i = 0; i < 16; ++i) {
+                    const int k = h * 32 + c * 16 + i;
+                    const float x0 = lo[i] * inv * w[k], x1 = hi[i] * inv * w[HALF + k];
+                    lo[i] = x0 * cs[c * 16 + i] - x1 * sn[c * 16 + i];
+                    hi[i] = x0 * sn[c * 16 + i] + x1 * cs[c * 16 + i];
                 }
             }
-            *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = pack8(y0);
-            *reinterpret_cast<uint4*>(dst + HALF + c * 32 + j * 8) = pack8(y1);
+            store16(dst + h * 32 + c * 16, lo);
+            store16(dst + HALF + h * 32 + c * 16, hi);
         }
     }
 }

@@ -116,6 +116,20 @@ __device__ __forceinline__ void tmem_load32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 16 consecutive float32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_load16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_store32(unsigned taddr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -168,6 +182,17 @@ inline int make_map_bf16(CUtensorMap* map, const void* base, long long rows, int
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return ti_fail("%s: cuTensorMapEncodeTiled failed with %d", who, (int)r);
     return 0;
+}
+
+// silu(g) * u = g * u / (1 + e^-g) with the approximate exponential and reciprocal: one
+// special-function instruction each (the correctly rounded reciprocal is a sequence of about ten
+// instructions, and the SwiGLU epilogue of a 128 x 256 tile then takes longer than the tile's
+// products: 9,700 against 3,700 cycles).  The relative error, about 1e-6, is far below the
+// bfloat16 rounding of the result; e^-g = inf for very negative g gives -0.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + __expf(-g)));
+    return g * u * r;
 }
 
 }  // namespace sm100
