@@ -231,15 +231,28 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                 } else {
                     float* dst = c + (size_t)row * ldc + col;
+                    // whole 32-byte sectors where the rows allow it: a thread's stores are a row each
+                    const bool by8 = ((uintptr_t)c % 32 == 0) && ldc % 8 == 0 && n % 8 == 0;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
+                    for (int i = 0; i < 32; i += 8) {
                         if (col + i >= n) break;
                         float4 x = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        float4 y = make_float4(v[i + 4], v[i + 5], v[i + 6], v[i + 7]);
+                        const bool second = col + i + 4 < n;
                         if (mode == MODE_ACCUMULATE) {
                             const float4 old = *reinterpret_cast<const float4*>(dst + i);
                             x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                            if (second) {
+                                const float4 old2 = *reinterpret_cast<const float4*>(dst + i + 4);
+                                y.x += old2.x; y.y += old2.y; y.z += old2.z; y.w += old2.w;
+                            }
                         }
-                        *reinterpret_cast<float4*>(dst + i) = x;
+                        if (by8) {
+                            store_f32x8(dst + i, x, y);
+                        } else {
+                            *reinterpret_cast<float4*>(dst + i) = x;
+                            if (second) *reinterpret_cast<float4*>(dst + i + 4) = y;
+                        }
                     }
                 }
             }

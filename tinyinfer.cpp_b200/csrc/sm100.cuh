@@ -184,6 +184,12 @@ inline int make_map_bf16(CUtensorMap* map, const void* base, long long rows, int
     return 0;
 }
 
+// Eight consecutive float32 values in one 32-byte store (a whole sector of L2), p 32-byte aligned.
+__device__ __forceinline__ void store_f32x8(float* p, const float4& a, const float4& b) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(a.x), "f"(a.y), "f"(a.z),
+                 "f"(a.w), "f"(b.x), "f"(b.y), "f"(b.z), "f"(b.w) : "memory");
+}
+
 // silu(g) * u = g * u / (1 + e^-g) with the approximate exponential and reciprocal: one
 // special-function instruction each (the correctly rounded reciprocal is a sequence of about ten
 // instructions, and the SwiGLU epilogue of a 128 x 256 tile then takes longer than the tile's
