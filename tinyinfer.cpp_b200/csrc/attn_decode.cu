@@ -63,61 +63,80 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 // out[:] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s, by one warp, over the splits
-// in ascending order.  Loads go to L2: other blocks of the same launch wrote the partial results.
-// First the weights of all splits (lanes in parallel, kept in `wbuf`, MAX_SPLITS floats of shared
-// memory), then the weighted sum with several loads in flight.
-__device__ __forceinline__ void merge_head(const float* part_o, const float* part_ml, size_t base,
-                                           int num_splits, int head_dim, bf16* out, int lane,
-                                           float* wbuf) {
-    float mmax = -INFINITY;
-    for (int s = lane; s < num_splits; s += 32) mmax = fmaxf(mmax, __ldcg(part_ml + (base + s) * 2));
-    mmax = warp_max(mmax);
-    float total = 0.0f;
-    for (int s = lane; s < num_splits; s += 32) {
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2));
-        const float wgt = ml.x == -INFINITY ? 0.0f : exp2f(ml.x - mmax);
-        wbuf[s] = wgt;
-        total += ml.y * wgt;                                  // lanes hold disjoint splits
+// in ascending order, for H heads at once (1 or 2).  Other blocks of the same launch wrote the
+// partial results, so every load is a round trip to L2, and the merge is the exposed tail of the
+// kernel: all (m, l) pairs and the first eight partial outputs of every head are requested
+// together, before anything is computed (one round trip instead of two per head).  `wbuf` holds
+// H * MAX_SPLITS floats of shared memory.
+template <int H>
+__device__ __forceinline__ void merge_heads(const float* part_o, const float* part_ml, const size_t (&base)[H],
+                                            int num_splits, int head_dim, bf16* const (&out)[H], int lane,
+                                            float* wbuf) {
+    constexpr int PER_LANE = MAX_SPLITS / 32;                 // (m, l) pairs a lane holds per head
+    const int d0 = lane * 4;                                  // dims lane*4 .. lane*4 + 3
+    const bool has_dims = d0 < head_dim;
+    float4 v[H][8];
+    float2 ml[H][PER_LANE];
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (has_dims && u < num_splits)
+                v[h][u] = __ldcg(reinterpret_cast<const float4*>(part_o + (base[h] + u) * head_dim + d0));
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int s = lane + 32 * i;
+            ml[h][i] = s < num_splits ? __ldcg(reinterpret_cast<const float2*>(part_ml + (base[h] + s) * 2))
+                                      : make_float2(-INFINITY, 0.0f);
+        }
     }
-    // a fixed order of the additions: lane partial sums, then the shuffle tree
-    total = warp_sum(total);
+    float total[H];
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        float mmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) mmax = fmaxf(mmax, ml[h][i].x);
+        mmax = warp_max(mmax);
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int s = lane + 32 * i;
+            if (s >= num_splits) break;
+            const float wgt = ml[h][i].x == -INFINITY ? 0.0f : exp2f(ml[h][i].x - mmax);
+            wbuf[h * MAX_SPLITS + s] = wgt;
+            sum += ml[h][i].y * wgt;                              // lanes hold disjoint splits
+        }
+        // a fixed order of the additions: lane partial sums, then the shuffle tree
+        total[h] = warp_sum(sum);
+    }
     __syncwarp();
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane*4 .. lane*4 + 3
-    const int d0 = lane * 4;
-    if (d0 < head_dim) {
-        const float* src = part_o + base * head_dim + d0;
-        int s = 0;
-        for (; s + 8 <= num_splits; s += 8) {                 // eight loads in flight
-            float4 v[8];
+    if (has_dims) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-                v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s + u) * head_dim));
+        for (int h = 0; h < H; ++h) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float* src = part_o + base[h] * head_dim + d0;
+            const float* wgts = wbuf + h * MAX_SPLITS;
+            for (int s = 0; s < num_splits; s += 8) {
+                if (s > 0) {                                      // the next eight, again all at once
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float wgt = wbuf[s + u];
-                acc[0] = fmaf(v[u].x, wgt, acc[0]); acc[1] = fmaf(v[u].y, wgt, acc[1]);
-                acc[2] = fmaf(v[u].z, wgt, acc[2]); acc[3] = fmaf(v[u].w, wgt, acc[3]);
+                    for (int u = 0; u < 8; ++u)
+                        if (s + u < num_splits)
+                            v[h][u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s + u) * head_dim));
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (s + u >= num_splits) break;
+                    const float wgt = wgts[s + u];
+                    acc[0] = fmaf(v[h][u].x, wgt, acc[0]); acc[1] = fmaf(v[h][u].y, wgt, acc[1]);
+                    acc[2] = fmaf(v[h][u].z, wgt, acc[2]); acc[3] = fmaf(v[h][u].w, wgt, acc[3]);
+                }
             }
+            const float inv = 1.0f / total[h];
+            *reinterpret_cast<__nv_bfloat162*>(out[h] + d0) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(out[h] + d0 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
         }
-        if (s < num_splits) {                                 // the rest, again all at once
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (s + u < num_splits)
-                    v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s + u) * head_dim));
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (s + u >= num_splits) break;
-                const float wgt = wbuf[s + u];
-                acc[0] = fmaf(v[u].x, wgt, acc[0]); acc[1] = fmaf(v[u].y, wgt, acc[1]);
-                acc[2] = fmaf(v[u].z, wgt, acc[2]); acc[3] = fmaf(v[u].w, wgt, acc[3]);
-            }
-        }
-        const float inv = 1.0f / total;
-        *reinterpret_cast<__nv_bfloat162*>(out + d0) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-        *reinterpret_cast<__nv_bfloat162*>(out + d0 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
     }
-    __syncwarp();                                             // wbuf may be reused for the next head
+    __syncwarp();                                             // wbuf may be reused for the next heads
 }
 
 template <int HD>
@@ -359,10 +378,20 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
     if (ticket != (unsigned)num_splits - 1) return;
     __threadfence();
     if (lane == 0) *counter = 0u;
-    for (int r = 0; r < group; ++r) {
+    float* wbuf = reinterpret_cast<float*>(smem);
+    int r = 0;
+    for (; r + 2 <= group; r += 2) {                        // two heads at a time: their loads overlap
         const int h = kvh * group + r;
-        merge_head(part_o, part_ml, ((size_t)row * num_heads + h) * num_splits, active, HD,
-                   out + ((size_t)t * num_heads + h) * HD, lane, reinterpret_cast<float*>(smem));
+        const size_t base[2] = {((size_t)row * num_heads + h) * num_splits,
+                                ((size_t)row * num_heads + h + 1) * num_splits};
+        bf16* const dst[2] = {out + ((size_t)t * num_heads + h) * HD, out + ((size_t)t * num_heads + h + 1) * HD};
+        merge_heads<2>(part_o, part_ml, base, active, HD, dst, lane, wbuf);
+    }
+    if (r < group) {
+        const int h = kvh * group + r;
+        const size_t base[1] = {((size_t)row * num_heads + h) * num_splits};
+        bf16* const dst[1] = {out + ((size_t)t * num_heads + h) * HD};
+        merge_heads<1>(part_o, part_ml, base, active, HD, dst, lane, wbuf);
     }
 }
 
@@ -377,8 +406,9 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
     if (item >= num_rows * num_heads) return;
     const int row = item / num_heads, h = item % num_heads;
     const int t = rows ? rows[row] : row;
-    merge_head(part_o, part_ml, (size_t)item * num_splits, num_splits, head_dim,
-               out + ((size_t)t * num_heads + h) * head_dim, lane, wbuf[threadIdx.x >> 5]);
+    const size_t base[1] = {(size_t)item * num_splits};
+    bf16* const dst[1] = {out + ((size_t)t * num_heads + h) * head_dim};
+    merge_heads<1>(part_o, part_ml, base, num_splits, head_dim, dst, lane, wbuf[threadIdx.x >> 5]);
 }
 
 template <int HD>
