@@ -303,10 +303,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     __nv_bfloat162 pk = __floats2bfloat162_rn(v[i] * inv, v[i + 1] * inv);
                     packed[i >> 1] = *reinterpret_cast<unsigned*>(&pk);
                 }
+                // a thread's stores are a row each: whole 32-byte sectors (the row is 256 bytes, aligned)
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
-                    *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) =
-                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                for (int q8 = 0; q8 < 2; ++q8)
+                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(orow + c * 32 + q8 * 16),
+                                 "r"(packed[q8 * 8]), "r"(packed[q8 * 8 + 1]), "r"(packed[q8 * 8 + 2]),
+                                 "r"(packed[q8 * 8 + 3]), "r"(packed[q8 * 8 + 4]), "r"(packed[q8 * 8 + 5]),
+                                 "r"(packed[q8 * 8 + 6]), "r"(packed[q8 * 8 + 7]) : "memory");
             }
         }
     }
@@ -340,8 +343,8 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
     TI_REQUIRE(ti_attn_prefill_tc_supported(head_dim, page_size, num_heads, num_kv_heads),
                "attn_prefill_tc: head_dim %d (128), page size %d (multiple of 16) or heads %d/%d "
                "are not supported", head_dim, page_size, num_heads, num_kv_heads);
-    TI_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)pages % 16 == 0 && (uintptr_t)out % 16 == 0,
-               "attn_prefill_tc: tensors must be 16-byte aligned");
+    TI_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)pages % 16 == 0 && (uintptr_t)out % 32 == 0,
+               "attn_prefill_tc: tensors must be 16-byte aligned, the output 32-byte");
     TI_REQUIRE(num_tiles <= 65535, "attn_prefill_tc: %d tiles exceed the grid limit", num_tiles);
     const long long pool_rows = (long long)num_pages * 2 * num_kv_heads * page_size;
     TI_REQUIRE(pool_rows < (1LL << 31) - 1, "attn_prefill_tc: the page pool has too many token slots");
