@@ -72,17 +72,50 @@ def _compare(steps, outputs, plain, rtol, what):
     return worst
 
 
+_ROWS = {}          # (name, family, dtype) -> request id -> [(position, logits row)]
+
+
+def _rows_of(tmp_path_factory, name, family, dtype):
+    key = (name, family, dtype)
+    if key not in _ROWS:
+        model_dir = make_model(tmp_path_factory.getbasetemp(), name)
+        steps = FAMILIES[family](_requests(name))
+        max_tokens = traces.max_live_tokens(steps)
+        outputs = _run_engine(model_dir, dtype, steps, max_tokens, PAGE.get(name, 16))
+        _ROWS[key] = (steps, outputs, traces.collect(steps, outputs))
+    return _ROWS[key]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_cuttings_match_plain(tmp_path_factory, name, family, dtype):
     model_dir = make_model(tmp_path_factory.getbasetemp(), name)
-    steps = FAMILIES[family](_requests(name))
-    max_tokens = traces.max_live_tokens(steps)
-    outputs = _run_engine(model_dir, dtype, steps, max_tokens, PAGE.get(name, 16))
+    steps, outputs, _ = _rows_of(tmp_path_factory, name, family, dtype)
     err = _compare(steps, outputs, _plain(model_dir, name, dtype), TOL[dtype],
                    f"tiny-{name} {family} {dtype}")
     print(f"tiny-{name} {family} {dtype}: max error {err:.2e} of the largest logit")
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_float32_cuttings_give_the_same_bits(tmp_path_factory, name):
+    """In 32-bit the logits at a (request, position) are the same bits however the tokens were
+    cut into steps, whatever else was in the batch and whichever pages held them: every kernel
+    of that path adds in an order that depends on the token's own place only."""
+    base = _rows_of(tmp_path_factory, name, "whole", "float32")[2]
+    for family in ("tail", "portions", "mixed"):
+        rows = _rows_of(tmp_path_factory, name, family, "float32")[2]
+        assert rows.keys() == base.keys()
+        for r in base:
+            assert [p for p, _ in rows[r]] == [p for p, _ in base[r]]
+            got = torch.stack([row for _, row in rows[r]])
+            want = torch.stack([row for _, row in base[r]])
+            if not torch.equal(got, want):
+                first = int((got != want).any(dim=-1).nonzero()[0])
+                raise AssertionError(
+                    f"tiny-{name} float32: '{family}' and 'whole' differ in bits for request {r}, "
+                    f"first at position {base[r][first][0]} "
+                    f"(max difference {(got - want).abs().max().item():.3e})")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

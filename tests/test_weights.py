@@ -81,20 +81,53 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del w["model.norm.weight"]
     w["model.layers.1.self_attn.k_proj.weight"] = torch.zeros(16, 64, dtype=torch.bfloat16)
     w["model.layers.0.self_attn.q_norm.weight"] = torch.zeros(8)
-    w["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)      # tied: not expected
+    w["lm_head.weight"] = torch.zeros(255, 64, dtype=torch.bfloat16)      # tied: allowed, but of the table's shape
     w["model.layers.9.extra"] = torch.zeros(1)
     write_safetensors(os.path.join(d, "model.safetensors"), w)
     with pytest.raises(WeightsError) as info:
         load_model_weights(_model(TINY_A), d, "cpu", RefOps())
     e = info.value
     assert e.missing == ["model.layers.0.mlp.up_proj.weight", "model.norm.weight"]
-    assert e.unexpected == ["lm_head.weight", "model.layers.9.extra"]
+    assert e.unexpected == ["model.layers.9.extra"]
     assert [(n, tuple(a), tuple(b)) for n, a, b in e.wrong_shape] == [
+        ("lm_head.weight", (256, 64), (255, 64)),
         ("model.layers.0.self_attn.q_norm.weight", (16,), (8,)),
         ("model.layers.1.self_attn.k_proj.weight", (32, 64), (16, 64))]
     text = str(e)
-    for piece in ("missing (2)", "unexpected (2)", "wrong shape (2)", "expected [32, 64] found [16, 64]"):
+    for piece in ("missing (2)", "unexpected (1)", "wrong shape (3)", "expected [32, 64] found [16, 64]"):
         assert piece in text
+
+
+def test_tied_checkpoint_may_store_the_head_again(tmp_path):
+    """A folder with tied embeddings that also holds ``lm_head.weight`` loads; the embedding's
+    table is the one used, and a copy with other values is reported, not followed.  An untied
+    model still refuses a tensor it does not know."""
+    import warnings
+    d = make_model(tmp_path, "A", seed=6)
+    _, w = load_folder(d)
+    w = dict(w)
+    w["lm_head.weight"] = w["model.embed_tokens.weight"].clone()
+    write_safetensors(os.path.join(d, "model.safetensors"), w)
+    model = _model(TINY_A)
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        load_model_weights(model, d, "cpu", RefOps())
+    assert model.head.table is model.embedding.table
+    assert torch.equal(model.embedding.table, w["model.embed_tokens.weight"])
+    w["lm_head.weight"] = torch.zeros_like(w["model.embed_tokens.weight"])
+    write_safetensors(os.path.join(d, "model.safetensors"), w)
+    model = _model(TINY_A)
+    with pytest.warns(UserWarning, match="lm_head.weight is stored beside model.embed_tokens.weight"):
+        load_model_weights(model, d, "cpu", RefOps())
+    assert torch.equal(model.head.table, w["model.embed_tokens.weight"])
+    db = make_model(tmp_path, "B", seed=6)
+    _, wb = load_folder(db)
+    wb = dict(wb)
+    wb["model.embed_tokens.copy"] = wb["model.embed_tokens.weight"].clone()
+    write_safetensors(os.path.join(db, "model.safetensors"), wb)
+    with pytest.raises(WeightsError) as info:
+        load_model_weights(_model(TINY_B), db, "cpu", RefOps())
+    assert info.value.unexpected == ["model.embed_tokens.copy"]
 
 
 def test_storage_precision_is_never_narrowed(tmp_path):

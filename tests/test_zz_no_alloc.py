@@ -5,8 +5,10 @@ whole device to a pool of its own and forbids cudaMalloc, or it is plain C code 
 tensor library's allocator, or it sits in a loop where an allocation's possible device
 synchronisation is not acceptable.  ``ti_attn_decode_noalloc`` keeps the scratch in an 8 MiB
 array inside the library instead.  Here it is called twice in a row on different inputs (the
-array keeps what the first call left) and compared with ``ti_attn_decode``, which takes its
-scratch from the caller; a request beyond the array's size must be refused.
+array keeps what the first call left) and compared with the plain PyTorch statement of paged
+attention, within the tolerance the kernel tests use, and with ``ti_attn_decode``, which takes
+its scratch from the caller and must give the same bits (the same kernel, the same cut into
+splits); a request beyond the array's size must be refused.
 
 The file sorts last so that, in a run that stops at the first failure, every other test has
 already run.
@@ -70,8 +72,18 @@ def _run_both(lib, seed, heads, kv_heads, hd, page, contexts, splits, window):
     assert rc == 0, lib.ti_last_error().decode()
     torch.cuda.synchronize()
     assert int(status.item()) == 0
-    err = (got.float() - want.float()).abs().max().item()
-    scale_ref = want.float().abs().max().item()
+    # the same kernel over another scratch: a slip in the array's layout would show as other bits
+    assert torch.equal(got, want), "the no-alloc entry point and ti_attn_decode differ"
+    # and both against the plain statement, so that a fault the two share does not pass
+    from types import SimpleNamespace
+    from ref_ops import RefOps
+    plain = torch.zeros_like(q)
+    RefOps().paged_attention(
+        q, SimpleNamespace(positions=positions, req_of_tok=req),
+        SimpleNamespace(pages=pages, block_table=table, page_size=page), plain, heads, kv_heads, hd,
+        window or None, scale)
+    err = (got.float() - plain.float()).abs().max().item()
+    scale_ref = plain.float().abs().max().item()
     assert err <= 1.5e-2 * scale_ref, f"no-alloc result differs: {err:.3e} against {scale_ref:.3e}"
     return got
 

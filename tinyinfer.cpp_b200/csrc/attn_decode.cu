@@ -371,6 +371,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
     // The block that finishes last for this (row, kv head) merges the splits of the group's heads.
     // The counter returns to zero, so the next launch finds it ready.
     __threadfence();
+    __syncwarp();                                    // every lane's stores and fence come before the ticket
     unsigned ticket = 0;
     unsigned* counter = counters + (size_t)row * num_kv_heads + kvh;
     if (lane == 0) ticket = atomicAdd(counter, 1u);
@@ -418,12 +419,12 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
                   float scale, int num_splits, float* part_o, float* part_ml, unsigned* counters,
                   bf16* out, int* status, cudaStream_t s) {
     constexpr int SMEM = STAGES * 2 * TILE * (HD * 2 + 16);
-    static bool configured = false;
-    if (!configured) {
+    static TiPerDevice configured;
+    if (configured.first_use()) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return ti_fail("attn_decode: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     dim3 grid(num_splits, num_kv_heads, num_rows);
     ti_launch_pdl(attn_decode_kernel<HD>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,

@@ -254,12 +254,12 @@ int launch_prefill(const bf16* q, const int* tiles, int num_tiles, const int* po
                    int page_size, int num_heads, int num_kv_heads, int window, float scale,
                    bf16* out, int* status, cudaStream_t s) {
     constexpr int SMEM = STAGES * 2 * BN * (HD * 2 + 16);
-    static bool configured = false;
-    if (!configured) {
+    static TiPerDevice configured;
+    if (configured.first_use()) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return ti_fail("attn_prefill: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     dim3 grid(num_heads, num_tiles);
     attn_prefill_kernel<HD><<<grid, WARPS * 32, SMEM, s>>>(q, tiles, positions, block_table, bt_stride,

@@ -355,12 +355,12 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
     int run = 128;
     while (page_size % run) run /= 2;
     if (int rc = make_map_bf16(&map_kv, pages, pool_rows, HD, HD, run, "attn_prefill_tc")) return rc;
-    static bool configured = false;
-    if (!configured) {
+    static TiPerDevice configured;
+    if (configured.first_use()) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return ti_fail("attn_prefill_tc: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     dim3 grid(num_heads, num_tiles);
     ti_launch_pdl(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,

@@ -21,3 +21,19 @@ int ti_check_launch(const char* what) {
     if (err == cudaSuccess) return 0;
     return ti_fail("%s: %s", what, cudaGetErrorString(err));
 }
+
+static int current_device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    return dev;
+}
+
+bool TiPerDevice::first_use() {
+    const int dev = current_device_slot();
+    return dev < 0 || !done[dev];
+}
+
+void TiPerDevice::mark() {
+    const int dev = current_device_slot();
+    if (dev >= 0) done[dev] = true;
+}

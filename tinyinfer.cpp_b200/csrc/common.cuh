@@ -20,6 +20,15 @@ extern "C" const char* ti_last_error();
 int ti_fail(const char* fmt, ...);                 // records the message, returns 1
 int ti_check_launch(const char* what);             // cudaGetLastError -> 0 or ti_fail
 
+// Attributes of a kernel (its dynamic shared memory limit) belong to a device's context, so they
+// are set once per device that launches it.  `TiPerDevice seen;` as a function-local static:
+// `seen.first_use()` is true when the current device has not passed here before.
+struct TiPerDevice {
+    bool done[64] = {};
+    bool first_use();          // true also when the device cannot be told (then set it again)
+    void mark();
+};
+
 #define TI_REQUIRE(cond, ...)            \
     do {                                 \
         if (!(cond)) return ti_fail(__VA_ARGS__); \

@@ -6,7 +6,7 @@
 // shared-memory stages with TMA tile loads (64 elements of K = one 128-byte swizzled row per
 // matrix row); warp 1 issues tcgen05.mma (128 x BN x 16, both operands K-major from shared
 // memory) into one of two accumulators in TMEM and hands each stage back with tcgen05.commit;
-// warps 2-5 read a finished accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes = rows
+// warps 2-9 read a finished accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes = rows
 // that its position in the warpgroup allows) and run the epilogue while the next tile's
 // products already fill the other accumulator.  Epilogues: store, accumulate into C (the
 // residual stream), SwiGLU over 8 gate + 8 up columns into bfloat16, or (BN = 256) the QKV
@@ -270,15 +270,15 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
     CUtensorMap map_a, map_w;
     if (int rc = make_map_bf16(&map_a, a, m, k, lda, BM, "gemm_tcgen05")) return rc;
     if (int rc = make_map_bf16(&map_w, w, n, k, ldw, wide ? 256 : 128, "gemm_tcgen05")) return rc;
-    static bool configured = false;
-    if (!configured) {
+    static TiPerDevice configured;
+    if (configured.first_use()) {
         cudaError_t e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::SMEM);
         if (e2 == cudaSuccess)
             e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Tile<128>::SMEM);
         if (e2 != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e2));
-        configured = true;
+        configured.mark();
     }
     if (wide) {
         const int tiles = tiles_m * ((n + 255) / 256);

@@ -289,12 +289,12 @@ int launch_pairs(const void* a, const void* w, const qkv::Epilogue& e, float* c,
     CUtensorMap map_a, map_w;
     if (int rc = make_map_bf16(&map_a, a, m, k, lda, 128, "gemm_tcgen05_2sm")) return rc;
     if (int rc = make_map_bf16(&map_w, w, n, k, ldw, 128, "gemm_tcgen05_2sm")) return rc;
-    static bool configured = false;
-    if (!configured) {
+    static TiPerDevice configured;
+    if (configured.first_use()) {
         cudaError_t e2 = cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<256>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<256>::SMEM);
         if (e2 != cudaSuccess) return ti_fail("gemm_tcgen05_2sm: %s", cudaGetErrorString(e2));
-        configured = true;
+        configured.mark();
     }
     const int tiles = ((m + BM - 1) / BM) * ((n + 255) / 256);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;

@@ -266,12 +266,12 @@ template <int NTOK>
 int launch_few(const CUtensorMap& map_w, const CUtensorMap& map_x, float* c, bf16* out_act, float* ws,
                int* tickets, int m, int n, int k, int ldc, int ld_act, int mode, int splits, int sms,
                int* status, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
+    static TiPerDevice configured;
+    if (configured.first_use()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_few_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Few<NTOK>::SMEM);
         if (e != cudaSuccess) return ti_fail("gemm_tcgen05_few: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     const int units = ((n + BW - 1) / BW) * splits;
     const int slots = sms * BLOCKS_PER_SM;

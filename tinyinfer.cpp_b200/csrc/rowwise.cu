@@ -307,18 +307,18 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
                           int n, float eps, void* out, int out_dtype, void* stream) {
     if (num_rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (n % 4 == 0 && num_rows >= 64 && (out_dtype == TI_BF16 || out_dtype == TI_F32) &&
+    // A float32 result is the 32-bit path: there the kernel, and with it the order in which a
+    // row's squares are added, must not depend on how many rows the step happens to bring, so
+    // that a token's bits are the same however the tokens are cut into steps.  Only the
+    // bfloat16 path picks the warp-per-row kernels for many rows.
+    if (n % 4 == 0 && num_rows >= 64 && out_dtype == TI_BF16 &&
         (uintptr_t)x % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0) {
         // many rows: a warp per row.  (Few rows keep a block per row: more threads per row.)
         const unsigned grid = (unsigned)((num_rows + 7) / 8);
-        if (out_dtype == TI_BF16 && n <= 2048)
+        if (n <= 2048)
             ti_launch_pdl(rmsnorm_warp_reg_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
-        else if (n <= 2048)
-            ti_launch_pdl(rmsnorm_warp_reg_kernel<float>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (float*)out);
-        else if (out_dtype == TI_BF16)
-            ti_launch_pdl(rmsnorm_warp_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
         else
-            ti_launch_pdl(rmsnorm_warp_kernel<float>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (float*)out);
+            ti_launch_pdl(rmsnorm_warp_kernel<bf16>, grid, 256, 0, s, x, weight, rows, eps, n, num_rows, (bf16*)out);
         return ti_check_launch("rmsnorm");
     }
     if (n % 4 == 0 && n <= 16 * 1024 && (out_dtype == TI_BF16 || out_dtype == TI_F32) &&

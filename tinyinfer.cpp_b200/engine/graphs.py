@@ -175,11 +175,11 @@ class DecodeGraphs(_OfEngine):
             bk = self.buckets[size] = _Bucket(eng, size)
         bk.fill(eng, entries, starts, device_tokens)
         if bk.graph is None:
-            # run once outside capture (loads kernels, sizes the allocator), then capture
+            # run this step once outside capture (loads kernels, sizes the allocator), then capture
             side = torch.cuda.Stream(device=eng.device)
             side.wait_stream(torch.cuda.current_stream(eng.device))
             with torch.cuda.stream(side):
-                eng.forward(bk.batch)
+                first = eng.forward(bk.batch)
             torch.cuda.current_stream(eng.device).wait_stream(side)
             torch.cuda.synchronize(eng.device)
             graph = torch.cuda.CUDAGraph()
@@ -187,6 +187,11 @@ class DecodeGraphs(_OfEngine):
             bk.logits = capture(graph, lambda: eng.forward(bk.batch))
             bk.graph = graph
             bk.launches = getattr(eng.ops, "launches", 0) - before
+            # This step has run, eagerly, just now.  Replaying it as well would run it twice: the
+            # cache pages would be written with the same values again, but a mixer with state of
+            # its own would advance that state a second time.
+            bk.logits.copy_(first)
+            return bk.logits[:len(entries)]
         bk.graph.replay()
         if hasattr(eng.ops, "launches"):
             eng.ops.launches += bk.launches

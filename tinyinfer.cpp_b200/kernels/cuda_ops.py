@@ -82,6 +82,7 @@ class CudaOps:
         # (measured: 4096 x 4096 is even at 16 rows, larger weights gain 15-50 %)
         self.few_tc_min_bytes = 1 << 25
         self._few_tickets = None
+        self._retired = []                # outgrown counter buffers that captured graphs may still use
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -151,11 +152,23 @@ class CudaOps:
             raise KernelError((lib or self.core).ti_last_error().decode("utf-8", "replace"))
 
     def check_status(self) -> None:
-        """Raise if a kernel met a block-table entry outside the pool since the last check."""
+        """Raise if a kernel has written the status word since the last check (a page id outside
+        the pool, or a barrier wait that ran out)."""
         code = int(self.status.item())
         if code:
             self.status.zero_()
-            raise KernelError(f"a kernel reported device status {code} (1: page id outside the pool)")
+            meaning = {1: "a block-table entry named a page outside the pool",
+                       2: "a wait on a shared-memory barrier ran out (a tensor-core kernel gave up "
+                          "instead of hanging; its output is not valid)"}.get(code, "unknown code")
+            raise KernelError(f"a kernel reported device status {code}: {meaning}")
+
+    def _grown(self, old, need: int, device):
+        """A zeroed int32 buffer of at least ``need`` counters that replaces ``old``.  The old one
+        stays alive: a captured graph still holds its address, and its launches still count in
+        it and leave it at zero."""
+        if old is not None:
+            self._retired.append(old)
+        return torch.zeros(max(4096, 2 * need), dtype=torch.int32, device=device)
 
     def _tc_gemm(self, m: int, n: int):
         """The tcgen05 product to use: on pairs of SMs when every pair gets a 256 x 256 tile."""
@@ -175,7 +188,7 @@ class CudaOps:
         ws_floats, tickets = ctypes.c_longlong(0), ctypes.c_int(0)
         self.bf16.ti_gemm_tcgen05_few_scratch(m, n, k, ctypes.byref(ws_floats), ctypes.byref(tickets))
         if self._few_tickets is None or self._few_tickets.numel() < tickets.value:
-            self._few_tickets = torch.zeros(max(4096, tickets.value), dtype=torch.int32, device=a.device)
+            self._few_tickets = self._grown(self._few_tickets, tickets.value, a.device)
         ws = torch.empty(ws_floats.value, dtype=torch.float32, device=a.device) if ws_floats.value else None
         self._ok(self.bf16.ti_gemm_tcgen05_few(
             a.data_ptr(), w.data_ptr(), _ptr(c), _ptr(out_act), m, n, k, a.stride(0), w.stride(0),
@@ -377,8 +390,7 @@ class CudaOps:
                                   device=q.device)
             if self._counters is None or self._counters.numel() < n_dec * num_kv_heads:
                 # zero once; every launch leaves its counters at zero again
-                self._counters = torch.zeros(max(4096, n_dec * num_kv_heads), dtype=torch.int32,
-                                             device=q.device)
+                self._counters = self._grown(self._counters, n_dec * num_kv_heads, q.device)
             self._ok(self.bf16.ti_attn_decode_fused(
                 q.data_ptr(), step.decode_rows.data_ptr(), n_dec, step.positions.data_ptr(),
                 step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),

@@ -47,6 +47,15 @@ class CausalLM:
                 out[prefix + local] = spec
         return out
 
+    def duplicate_tensors(self) -> dict[str, str]:
+        """Checkpoint names the model does not need but a folder may still hold, each with the
+        name of the tensor it repeats: a tied head's own table beside the embedding's (some
+        published checkpoints with tied embeddings store the table twice).  The reference never
+        reads a head of its own (src/model.cpp:120-121)."""
+        if getattr(self.head, "tied", False):
+            return {self.plan.names["head"] + "weight": self.plan.names["embedding"] + "weight"}
+        return {}
+
     def load_weights(self, fetch: Callable[[str], torch.Tensor], ops) -> None:
         """``fetch(name)`` returns the checkpoint tensor on the device, dtype as stored."""
         for prefix, part in self._named:

@@ -8,6 +8,7 @@ lists every missing tensor, every unexpected tensor and every wrong shape.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Mapping
 
 import torch
@@ -35,13 +36,24 @@ class WeightsError(ValueError):
 
 
 def check_tensors(where: str, expected: Mapping[str, WeightSpec],
-                  found: Mapping[str, tuple[int, ...]]) -> None:
+                  found: Mapping[str, tuple[int, ...]],
+                  duplicates: Mapping[str, str] = {}) -> None:
+    """``duplicates``: names that may be present although the model does not need them, each
+    with the expected tensor it repeats; such a tensor is not "unexpected", but it must have the
+    shape of the one it repeats."""
     missing = [n for n in expected if n not in found]
-    unexpected = [n for n in found if n not in expected]
+    unexpected = [n for n in found if n not in expected and n not in duplicates]
     wrong = [(n, expected[n].shape, found[n]) for n in expected
              if n in found and tuple(found[n]) != tuple(expected[n].shape)]
+    wrong += [(n, expected[of].shape, found[n]) for n, of in duplicates.items()
+              if n in found and n not in expected and of in expected
+              and tuple(found[n]) != tuple(expected[of].shape)]
     if missing or unexpected or wrong:
         raise WeightsError(where, missing, unexpected, wrong)
+
+
+def _same_values(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return a.shape == b.shape and a.dtype == b.dtype and torch.equal(a, b)
 
 
 def storage_dtype(dtype: torch.dtype) -> torch.dtype:
@@ -59,7 +71,13 @@ def load_model_weights(model, model_dir: str, device, ops) -> None:
     try:
         index = tensor_index(files)
         expected = model.expected_tensors()
-        check_tensors(model_dir, expected, {n: f.shape(n) for n, f in index.items()})
+        duplicates = model.duplicate_tensors() if hasattr(model, "duplicate_tensors") else {}
+        check_tensors(model_dir, expected, {n: f.shape(n) for n, f in index.items()}, duplicates)
+        for name, of in duplicates.items():
+            if name in index and of in index and not _same_values(index[name].get(name),
+                                                                  index[of].get(of)):
+                warnings.warn(f"{model_dir}: {name} is stored beside {of} although the two are "
+                              f"tied, and its values differ; {of} is used", stacklevel=2)
 
         def fetch(name: str) -> torch.Tensor:
             t = index[name].get(name)
