@@ -26,7 +26,8 @@ BENCH_SHAPE = dict(
     num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
     vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
     max_position_embeddings=4096)
-SHARPEN = 2.0          # factor on q_norm and k_norm: scores spread 4 times wider
+SHARPEN = 1.4          # factor on q_norm and k_norm: scores spread twice as wide (beyond that the
+                       # rounding of bfloat16 queries and keys itself moves the logits past the tolerance)
 SEED = 5
 
 
