@@ -51,11 +51,15 @@ class RefOps:
         out.copy_((gate / (1.0 + torch.exp(-gate)) * up).to(out.dtype))
 
     # ---- attention -----------------------------------------------------------------------
-    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                            num_heads, num_kv_heads, head_dim):
+        """``rotation``: kind "neox" (half-split pairs over the first ``rotary_dim`` elements of a
+        head, the rest left alone) or "none"."""
+        assert rotation.kind in ("neox", "none"), rotation.kind
         t = qkv.shape[0]
         nq, nk = num_heads * head_dim, num_kv_heads * head_dim
-        half = head_dim // 2
+        rot = int(rotation.rotary_dim)
+        half = rot // 2
         q = qkv[:, :nq].reshape(t, num_heads, head_dim).to(F32)
         k = qkv[:, nq:nq + nk].reshape(t, num_kv_heads, head_dim).to(F32)
         v = qkv[:, nq + nk:].reshape(t, num_kv_heads, head_dim).to(F32)
@@ -63,15 +67,16 @@ class RefOps:
         def norm(x, w):
             return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * w.to(F32)
 
-        ang = step.positions.to(F32)[:, None] * inv_freq.to(F32)[None, :]
-        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        def rot_heads(x):
+            if rot == 0:
+                return x
+            ang = step.positions.to(F32)[:, None] * rotation.inv_freq.to(F32)[None, :]
+            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            x0, x1 = x[..., :half], x[..., half:rot]
+            return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c, x[..., rot:]], dim=-1)
 
-        def rot(x):
-            x0, x1 = x[..., :half], x[..., half:]
-            return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
-
-        q = rot(norm(q, q_weight))
-        k = rot(norm(k, k_weight))
+        q = rot_heads(norm(q, q_weight))
+        k = rot_heads(norm(k, k_weight))
         q_out.copy_(q.reshape(t, nq).to(q_out.dtype))
         if cache.writes:
             ps = cache.page_size
@@ -80,11 +85,11 @@ class RefOps:
             cache.pages[page, 0, :, pos % ps, :] = k.to(cache.pages.dtype)
             cache.pages[page, 1, :, pos % ps, :] = v.to(cache.pages.dtype)
 
-    def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+    def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                        num_heads, num_kv_heads, head_dim):
         qkv = torch.empty((q_out.shape[0], w_qkv.shape[0]), dtype=F32, device=q_out.device)
         self.linear(h, w_qkv, qkv)
-        self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+        self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                                 num_heads, num_kv_heads, head_dim)
 
     def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,

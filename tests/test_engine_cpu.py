@@ -120,3 +120,34 @@ def test_request_span_reads_across_prompt_and_output():
         for count in range(0, 8 - start):
             assert r.span(start, count) == r.tokens[start:start + count]
     assert r.num_tokens == 7
+
+
+def test_step_lists_are_packed_with_the_step():
+    """Lists that a kernel set or a part derives from a step's shape travel in the step's one
+    upload; the kernel set's own builders cut portions into tiles of a given height."""
+    import numpy as np
+    from tinyinfer_b200.engine.batch import StepList, build_lists, build_step_batch
+    from tinyinfer_b200.kernels.step_lists import attention_lists
+    entries = [StepEntry("a", [1] * 150, [149]), StepEntry("b", [2], [0]), StepEntry("c", [3] * 70, []),
+               StepEntry("d", [4], [0])]
+    starts = [10, 99, 300, 5]
+    lists = attention_lists([64, 128]) + [StepList("twice", lambda q, s: np.asarray(q) * 2)]
+    batch = build_step_batch(entries, starts, [[[0, 1, 2], [3, 4], [5, 6, 7, 8, 9, 10], [11]]], [0, 1, 2, 3],
+                             torch.float32, "cpu", lists=lists)
+    assert batch.lists["single_rows"].tolist() == [150, 221]
+    assert batch.lists["portion_rows"].tolist() == list(range(150)) + list(range(151, 221))
+    # tiles {request row, first flat token, rows}, the longest contexts first
+    assert batch.lists["portion_tiles_64"].tolist() == [[2, 215, 6], [2, 151, 64], [0, 128, 22], [0, 64, 64], [0, 0, 64]]
+    assert batch.lists["portion_tiles_128"].tolist() == [[2, 151, 70], [0, 128, 22], [0, 0, 128]]
+    assert batch.lists["twice"].tolist() == [300, 2, 140, 2]
+    assert batch.block_tables[0].shape == (4, 6) and batch.block_tables[0][1].tolist() == [3, 4, -1, -1, -1, -1]
+    assert batch.positions[150].item() == 99 and batch.logit_rows.tolist() == [149, 150, 221]
+    # the layout depends on the token counts only: other positions, the same addresses
+    again = build_step_batch(entries, [0, 0, 0, 0], [[[0, 1, 2], [3, 4], [5, 6, 7, 8, 9, 10], [11]]],
+                             [0, 1, 2, 3], torch.float32, "cpu", lists=lists)
+    assert again.packed_size == batch.packed_size
+    assert {k: tuple(v.shape) for k, v in again.lists.items()} == {k: tuple(v.shape) for k, v in batch.lists.items()}
+    with pytest.raises(ValueError, match="two step lists"):
+        build_lists([lists[0], lists[0]], [1], [0])
+    with pytest.raises(TypeError, match="integers"):
+        build_lists([StepList("bad", lambda q, s: np.asarray([0.5]))], [1], [0])

@@ -235,20 +235,20 @@ def _paged_case(num_heads, num_kv, hd, page_size, ctx_lens, q_lens, dtype, seed=
     for i, b in enumerate(blocks):
         bt[i, :b] = torch.tensor([next(it) for _ in range(b)], dtype=torch.int32)
     pages = _rand((num_pages, 2, num_kv, page_size, hd), dtype, seed=seed + 1)
-    positions, req_of_tok, dec, chk, tiles, tiles_big = [], [], [], [], [], []
+    positions, req_of_tok = [], []
     for i, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
-        if ql > 1:
-            tiles += [[i, len(positions) + lo, min(64, ql - lo)] for lo in range(0, ql, 64)]
-            tiles_big += [[i, len(positions) + lo, min(128, ql - lo)] for lo in range(0, ql, 128)]
         for j in range(ql):
-            (dec if ql == 1 else chk).append(len(positions))
             positions.append(c - ql + j)
             req_of_tok.append(i)
     ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), decode_rows=ti(dec),
-                           chunk_rows=ti(chk), chunk_tiles=ti(tiles).view(-1, 3),
-                           chunk_tiles_big=ti(tiles_big).view(-1, 3), max_position=max(ctx_lens), max_ctx_len=max(ctx_lens),
-                           scratch={})
+    # the lists the kernel set asks of a step (single-token rows, portions cut into its tiles)
+    from tinyinfer_b200.engine.batch import build_lists
+    from tinyinfer_b200.kernels import cuda_ops
+    lists = build_lists(cuda_ops(DEV).step_lists(torch.bfloat16), list(q_lens),
+                        [c - ql for c, ql in zip(ctx_lens, q_lens)])
+    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok),
+                           lists={name: torch.from_numpy(a).to(torch.int32).to(DEV) for name, a in lists.items()},
+                           max_position=max(ctx_lens), max_ctx_len=max(ctx_lens), scratch={})
     cache = SimpleNamespace(pages=pages, block_table=bt.to(DEV), page_size=page_size, writes=True)
     q = _rand((len(positions), num_heads * hd), dtype, seed=seed + 2)
     return step, cache, q
@@ -317,27 +317,62 @@ def test_decode_attention_finds_a_far_key(ops):
         assert (out[row].float() - want).abs().max() < 0.51, "the far key's value was not returned"
 
 
+def _rotation(hd, rotary_dim=None, theta=1e6):
+    from tinyinfer_b200.parts import Rotation
+    rot = hd if rotary_dim is None else rotary_dim
+    if rot == 0:
+        return Rotation("none", 0, None)
+    inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64),
+                         -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).float().to(DEV)
+    return Rotation("neox", rot, inv_freq)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("geom", [(4, 2, 16, 16), (3, 1, 48, 16), (16, 8, 128, 32), (5, 5, 144, 16)])
+@pytest.mark.parametrize("geom", [(4, 2, 16, 16, None), (3, 1, 48, 16, None), (16, 8, 128, 32, None),
+                                  (5, 5, 144, 16, None), (3, 1, 48, 16, 20), (4, 2, 128, 16, 64),
+                                  (2, 2, 80, 16, 0), (6, 2, 33, 16, 0)])
 def test_qk_norm_rope_store(ops, dtype, geom):
-    heads, kv, hd, ps = geom
+    """Also with a rotation over a part of the head only, and with none at all."""
+    heads, kv, hd, ps, rotary = geom
     ctx, qls = [5, 33, 64, 100], [5, 1, 17, 2]
     step, cache, _ = _paged_case(heads, kv, hd, ps, ctx, qls, dtype)
     t = step.positions.shape[0]
     qkv = _rand((t, (heads + 2 * kv) * hd), seed=3, scale=2.0)
     qw, kw = 1 + _rand((hd,), seed=4, scale=0.1), 1 + _rand((hd,), seed=5, scale=0.1)
-    inv_freq = torch.pow(torch.tensor(1e6, dtype=torch.float64),
-                         -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(DEV)
+    rotation = _rotation(hd, rotary)
     ref_cache = SimpleNamespace(**vars(cache))
     ref_cache.pages = cache.pages.clone()
     q_out = torch.empty((t, heads * hd), dtype=dtype, device=DEV)
     q_ref = torch.empty_like(q_out)
-    ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, inv_freq, step, cache, q_out, heads, kv, hd)
-    RefOps().qk_norm_rope_store(qkv, qw, kw, 1e-6, inv_freq, step, ref_cache, q_ref, heads, kv, hd)
+    ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, rotation, step, cache, q_out, heads, kv, hd)
+    RefOps().qk_norm_rope_store(qkv, qw, kw, 1e-6, rotation, step, ref_cache, q_ref, heads, kv, hd)
     tol = 3e-6 if dtype == torch.float32 else 8e-3
     _close(q_out, q_ref, tol, "rotated queries")
     _close(cache.pages, ref_cache.pages, tol, "pages after the store")
     ops.check_status()
+
+
+def test_rotation_kinds_without_a_kernel_are_refused_and_can_be_registered(ops):
+    from tinyinfer_b200.kernels import KernelError
+    from tinyinfer_b200.parts import Rotation
+    step, cache, _ = _paged_case(2, 1, 16, 16, [5], [5], torch.float32)
+    qkv = _rand((5, 4 * 16), seed=3)
+    qw = kw = torch.ones(16, device=DEV)
+    q_out = torch.zeros((5, 32), device=DEV)
+    odd = Rotation("pairs_of_neighbours", 16, None)
+    with pytest.raises(KernelError, match="pairs_of_neighbours"):
+        ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, odd, step, cache, q_out, 2, 1, 16)
+    with pytest.raises(KernelError, match="pairs_of_neighbours"):
+        ops.qkv_rope_store(qkv[:, :8].contiguous(), _rand((64, 8), seed=1), qw, kw, 1e-6, odd, step,
+                           cache, q_out, 2, 1, 16)
+    assert not q_out.any()
+    seen = []
+    ops.register_rotation("pairs_of_neighbours", lambda *a: seen.append(a[5].kind))
+    try:
+        ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, odd, step, cache, q_out, 2, 1, 16)
+    finally:
+        del ops._rotations["pairs_of_neighbours"]
+    assert seen == ["pairs_of_neighbours"]
 
 
 @pytest.mark.parametrize("geom", [(16, 8, 1024, [2048], [2048]), (5, 1, 136, [300, 77, 500], [150, 70, 333]),
@@ -354,20 +389,19 @@ def test_qkv_product_with_norm_rotation_and_store_in_its_epilogue(ops, geom, wri
     h = _rand((t, k), torch.bfloat16, seed=7)
     w = _rand(((heads + 2 * kv) * hd, k), torch.bfloat16, seed=8, scale=2.0 / math.sqrt(k))
     qw, kw = 1 + _rand((hd,), seed=4, scale=0.1), 1 + _rand((hd,), seed=5, scale=0.1)
-    inv_freq = torch.pow(torch.tensor(1e6, dtype=torch.float64),
-                         -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(DEV)
+    rotation = _rotation(hd)
     ref_cache = SimpleNamespace(**vars(cache))
     ref_cache.pages = cache.pages.clone()
     untouched = cache.pages.clone()
     q_out = torch.zeros((t, heads * hd), dtype=torch.bfloat16, device=DEV)
     q_ref = torch.empty_like(q_out)
     before = ops.launches
-    ops.qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, cache, q_out, heads, kv, hd)
+    ops.qkv_rope_store(h, w, qw, kw, 1e-6, rotation, step, cache, q_out, heads, kv, hd)
     assert ops.launches - before == 2                    # the rotation table of the step, the product
-    ops.qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, cache, q_out, heads, kv, hd)
+    ops.qkv_rope_store(h, w, qw, kw, 1e-6, rotation, step, cache, q_out, heads, kv, hd)
     assert ops.launches - before == 3                    # the next layer finds the table
     ops.check_status()
-    RefOps().qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, ref_cache, q_ref, heads, kv, hd)
+    RefOps().qkv_rope_store(h, w, qw, kw, 1e-6, rotation, step, ref_cache, q_ref, heads, kv, hd)
     _close(q_out, q_ref, 8e-3, "rotated queries")
     _close(cache.pages, ref_cache.pages, 8e-3, "pages after the store")
     if not writes:
@@ -379,7 +413,7 @@ def test_qkv_product_with_norm_rotation_and_store_in_its_epilogue(ops, geom, wri
         q_two = torch.empty_like(q_out)
         two = SimpleNamespace(**vars(cache))
         two.pages = untouched.clone()
-        ops.qkv_rope_store(h, w, qw, kw, 1e-6, inv_freq, step, two, q_two, heads, kv, hd)
+        ops.qkv_rope_store(h, w, qw, kw, 1e-6, rotation, step, two, q_two, heads, kv, hd)
     finally:
         ops.fuse_qkv_epilogue = keep
     _close(q_out, q_two, 8e-3, "fused against separate kernels")

@@ -92,6 +92,18 @@ def test_requests_that_can_never_fit_finish_at_once():
     assert r.finish_reason == "too_long" and not sched.has_work()
     with pytest.raises(ValueError, match="empty prompt"):
         sched.add(Request("e", []))
+    # a group with a window needs the window only, but that much it does need
+    for pages, fits in ((4, True), (3, False)):
+        cache = CacheManager([PagedKVSpec(2, 16, 40)], page_size=16, num_pages=pages, max_requests=2)
+        sched = Scheduler(cache, max_num_seqs=2, max_batched_tokens=16, max_position=1024)
+        r = _req("w", 200, max_tokens=100)                       # 41 keys: 3 pages and one at the edge
+        sched.add(r)
+        assert (r.finish_reason is None) == fits
+        while fits and sched.has_work():
+            plan, _ = _run_step(cache, sched)
+            for s in plan:
+                cache.release_passed(s.request.req_id)
+        assert not fits or (r.finish_reason == "length" and len(r.output) == 100)
 
 
 def test_pages_run_out_newest_is_preempted_and_recomputed():

@@ -43,7 +43,7 @@ class PagedKVView:
 class StateView:
     """What a mixer with fixed-size state sees of its cache slot during one step."""
     state: Optional[torch.Tensor]        # [max_requests, *shape]
-    slots: Optional[torch.Tensor]        # [requests] int64: the state slot of each request
+    slots: Optional[torch.Tensor]        # [requests] int32: the state slot of each request
     writes: bool
 
 

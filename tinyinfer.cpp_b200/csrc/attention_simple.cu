@@ -26,7 +26,7 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
                           const int* __restrict__ positions, const int* __restrict__ req_of_tok,
                           const int* __restrict__ block_table, int bt_stride,
                           TC* __restrict__ pages, int num_pages, int page_size, int write_kv,
-                          int num_heads, int num_kv_heads, int head_dim,
+                          int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
                           TQ* __restrict__ q_out, int* __restrict__ status) {
     __shared__ float vec[WARPS][MAX_HEAD_DIM];
     pdl_launch();
@@ -36,7 +36,7 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
     const int item = blockIdx.y * WARPS + warp;
     const int items = num_heads + 2 * num_kv_heads;
     if (item >= items) return;
-    const int half = head_dim >> 1;
+    const int half = rotary_dim >> 1;                 // pairs (k, k + half), k < half, are rotated
     const int nq = num_heads * head_dim, nk = num_kv_heads * head_dim;
     const int pos = positions[t];
 
@@ -90,6 +90,12 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
             dst[k] = from_f32<TC>(y0);
             dst[k + half] = from_f32<TC>(y1);
         }
+    }
+    // what lies beyond the rotated width is normed only
+    for (int d = rotary_dim + lane; d < head_dim; d += 32) {
+        const float y = vec[warp][d] * inv * w[d];
+        if (kind == 0) q_out[(size_t)t * nq + head * head_dim + d] = from_f32<TQ>(y);
+        else dst[d] = from_f32<TC>(y);
     }
 }
 
@@ -292,10 +298,15 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
                                      const int* block_table, int bt_stride, void* pages,
                                      int cache_dtype, int num_pages, int page_size, int write_kv,
                                      int num_tokens, int num_heads, int num_kv_heads, int head_dim,
-                                     void* q_out, int q_dtype, int* status, void* stream) {
+                                     int rotary_dim, void* q_out, int q_dtype, int* status,
+                                     void* stream) {
     if (num_tokens == 0) return 0;
-    TI_REQUIRE(head_dim >= 2 && head_dim % 2 == 0 && head_dim <= MAX_HEAD_DIM,
-               "qk_norm_rope_store: head_dim %d must be even and at most %d", head_dim, MAX_HEAD_DIM);
+    TI_REQUIRE(head_dim >= 1 && head_dim <= MAX_HEAD_DIM,
+               "qk_norm_rope_store: head_dim %d must be at most %d", head_dim, MAX_HEAD_DIM);
+    TI_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+               "qk_norm_rope_store: the rotated width %d must be even and at most head_dim %d",
+               rotary_dim, head_dim);
+    TI_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "qk_norm_rope_store: no rotation table");
     const int items = num_heads + 2 * num_kv_heads;
     dim3 grid(num_tokens, (items + WARPS - 1) / WARPS);
     cudaStream_t s = (cudaStream_t)stream;
@@ -303,7 +314,9 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
     int ipw = num_tokens >= 512 ? (items + WARPS - 1) / WARPS : 1;            // vectors per warp
     if (ipw > 8) ipw = 8;
     dim3 vgrid(num_tokens, (items + WARPS * ipw - 1) / (WARPS * ipw));
-    const int vec = (half % 4 == 0 && half > 64) ? 4 : (half % 2 == 0 && half <= 64) ? 2 : 0;
+    // the register kernel pairs element k with k + head_dim / 2: for a rotation over the whole head only
+    const int vec = rotary_dim != head_dim ? 0
+                    : (half % 4 == 0 && half > 64) ? 4 : (half % 2 == 0 && half <= 64) ? 2 : 0;
 #define CALL(TQ, TC)                                                                          \
     if (vec == 2)                                                                             \
         ti_launch_pdl(qk_norm_rope_store_vec_kernel<TQ, TC, 2>, vgrid, WARPS * 32, 0, s,       \
@@ -319,7 +332,7 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
         ti_launch_pdl(qk_norm_rope_store_kernel<TQ, TC>, grid, WARPS * 32, 0, s,               \
             qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
             bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
-            head_dim, (TQ*)q_out, status)
+            head_dim, rotary_dim, (TQ*)q_out, status)
     TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
 #undef CALL
     return ti_check_launch("qk_norm_rope_store");

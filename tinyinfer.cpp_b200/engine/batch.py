@@ -6,18 +6,18 @@ metadata is packed into one pinned host buffer and copied to the device once.
 The reference passes flat ``tokens/positions/seq_ids`` the same way
 (src/inference.cu:190-198) but only ever sends whole prompts or one token per
 sequence (src/main.cpp:211-219,269-274).
+
+What a kernel needs beyond that description (which flat tokens are single-token rows, how
+portions fall into its tiles) is not known here: the kernel set and the parts register
+``StepList`` builders, and the step packs what they return into the same upload.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, Optional, Sequence
+from typing import Callable, Hashable, Optional, Sequence
 
 import numpy as np
 import torch
-
-
-PREFILL_TILE_ROWS = 64     # query rows per block of the prompt-portion attention kernel (mma.sync)
-PREFILL_TILE_ROWS_BIG = 128    # the same for the tcgen05 kernel
 
 
 @dataclass(frozen=True)
@@ -27,6 +27,21 @@ class StepEntry:
     req_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+
+
+@dataclass(frozen=True)
+class StepList:
+    """A list of integers that a kernel set or a part derives on the host from a step's shape:
+    which flat tokens are single-token rows, how portions are cut into a kernel's tiles, and
+    the like.  ``build(q_lens, starts)`` gets every entry's token count and first position and
+    returns an integer array of one or two dimensions.  Its shape may depend on the token
+    counts only, never on the positions: a step of the same shape is replayed from a CUDA graph
+    over the same addresses, with only the contents renewed.  ``uses_starts`` says whether the
+    contents depend on the positions at all (a list that does not is built once per graph).
+    The step hands each list out as ``step.lists[name]`` (int32 on the device)."""
+    name: str
+    build: Callable[[Sequence[int], Sequence[int]], np.ndarray]
+    uses_starts: bool = False
 
 
 @dataclass
@@ -50,22 +65,36 @@ class StepBatch:
     ctx_len_dev: torch.Tensor        # [R] length of each request after this step
     logit_rows: torch.Tensor         # [K] flat token indices whose logits are wanted
     state_slots: torch.Tensor        # [R] state slot of each request
-    decode_rows: torch.Tensor        # flat indices of tokens that are their request's only token
-    chunk_rows: torch.Tensor         # flat indices of the tokens of requests that bring several
-    chunk_tiles: torch.Tensor        # [n, 3] {request row, first flat token, rows} in tiles of 64
-    chunk_tiles_big: torch.Tensor    # the same in tiles of 128
     max_position: int = 0            # the model's longest context (bounds that do not vary by step)
     packed_size: int = 0             # int32 values in the packed device buffer
     block_tables: list[torch.Tensor] = field(default_factory=list)   # per group [R, blocks]
+    lists: dict = field(default_factory=dict)     # name -> int32 device tensor of a registered StepList
     scratch: dict = field(default_factory=dict)   # what kernels derive from the step, kept for one forward pass
+
+
+def build_lists(lists: Sequence[StepList], q_lens: Sequence[int], starts: Sequence[int]) -> dict:
+    """Every list's array for a step of these token counts and first positions."""
+    out = {}
+    for sl in lists:
+        arr = np.asarray(sl.build(q_lens, starts))
+        if arr.size and arr.dtype.kind not in "iu":
+            raise TypeError(f"step list {sl.name!r} must hold integers, got {arr.dtype}")
+        if arr.ndim not in (1, 2):
+            raise ValueError(f"step list {sl.name!r} must have one or two dimensions")
+        if sl.name in out:
+            raise ValueError(f"two step lists are named {sl.name!r}")
+        out[sl.name] = arr.astype(np.int64, copy=False)
+    return out
 
 
 def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
                      tables: Sequence[Sequence[Sequence[int]]], slots: Sequence[int],
                      act_dtype: torch.dtype, device, min_blocks: int = 1,
-                     max_position: int = 0, dev_buffer: Optional[torch.Tensor] = None) -> StepBatch:
+                     max_position: int = 0, dev_buffer: Optional[torch.Tensor] = None,
+                     lists: Sequence[StepList] = ()) -> StepBatch:
     """Pack one step.  ``starts[r]`` is the position of entry r's first token,
-    ``tables[g][r]`` its block table in group g (already covering the new tokens).
+    ``tables[g][r]`` its block table in group g (already covering the new tokens);
+    ``lists`` are the integer lists that the kernel set and the parts have asked for.
 
     The packed layout depends only on the entries' token counts and wanted places once
     ``min_blocks`` fixes the block tables' width.  ``dev_buffer`` (int32, at least
@@ -85,22 +114,10 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
                     f"request {e.req_id!r}: wanted place {w} is outside its {q_lens[i]} tokens")
             rows.append(int(cu[i]) + int(w))
     k = len(rows)
-    dec = [int(cu[i]) for i in range(r) if q_lens[i] == 1]
-    chk_parts = [np.arange(cu[i], cu[i + 1]) for i in range(r) if q_lens[i] > 1]
-    chk = np.concatenate(chk_parts) if chk_parts else np.zeros(0, dtype=np.int64)
-    def tile_list(rows_per_tile):
-        found = []
-        for i in range(r):
-            if q_lens[i] > 1:
-                for lo in range(0, q_lens[i], rows_per_tile):
-                    found.append((starts[i] + lo, i, int(cu[i]) + lo, min(rows_per_tile, q_lens[i] - lo)))
-        found.sort(key=lambda x: -x[0])               # longest contexts first
-        return [x[1:] for x in found]
-
-    tiles = tile_list(PREFILL_TILE_ROWS)
-    tiles_big = tile_list(PREFILL_TILE_ROWS_BIG)
+    extra = build_lists(lists, q_lens, list(starts))
     widths = [max(min_blocks, max((len(tb) for tb in grp), default=0)) for grp in tables]
-    total = 4 * t + (r + 1) + 3 * r + k + 3 * len(tiles) + 3 * len(tiles_big) + sum(r * w for w in widths)
+    total = (3 * t + (r + 1) + 3 * r + k + sum(a.size for a in extra.values())
+             + sum(r * w for w in widths))
     host = torch.empty(max(total, 1), dtype=torch.int32,
                        pin_memory=(torch.device(device).type == "cuda"))
     buf = host.numpy()
@@ -120,11 +137,8 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         "tok": put(tok, t), "pos": put(pos, t), "roft": put(roft, t), "cu": put(cu, r + 1),
         "qs": put(np.asarray(starts, dtype=np.int64), r), "ctx": put(np.asarray(ctx), r),
         "slots": put(np.asarray(slots, dtype=np.int64), r), "rows": put(np.asarray(rows), k),
-        "dec": put(np.asarray(dec, dtype=np.int64), len(dec)),
-        "chk": put(chk, len(chk)),
-        "tiles": put(np.asarray(tiles, dtype=np.int64).reshape(-1), 3 * len(tiles)),
-        "tiles_big": put(np.asarray(tiles_big, dtype=np.int64).reshape(-1), 3 * len(tiles_big)),
     }
+    list_spans = {name: (put(a.reshape(-1), a.size), a.shape) for name, a in extra.items()}
     bt_spans = []
     for grp, w in zip(tables, widths):
         arr = np.full((r, w), -1, dtype=np.int64)
@@ -147,7 +161,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         max_q_len=max(q_lens, default=0), max_ctx_len=max(ctx, default=0),
         token_ids=view("tok"), positions=view("pos"), req_of_tok=view("roft"), cu_q=view("cu"),
         q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
-        state_slots=view("slots"), decode_rows=view("dec"), chunk_rows=view("chk"),
-        chunk_tiles=view("tiles").view(-1, 3), chunk_tiles_big=view("tiles_big").view(-1, 3),
+        state_slots=view("slots"),
         max_position=max_position, packed_size=host.shape[0],
-        block_tables=[dev[a:b].view(r, w) for (a, b), w in bt_spans])
+        block_tables=[dev[a:b].view(r, w) for (a, b), w in bt_spans],
+        lists={name: dev[a:b].view(shape) for name, ((a, b), shape) in list_spans.items()})

@@ -99,6 +99,12 @@ class Engine:
         self.cache = CacheManager(self.model.cache_specs(), page_size=page_size,
                                   num_pages=num_pages, max_requests=max_requests,
                                   kv_dtype=self.dtype, device=self.device)
+        # what the kernel set and the parts want built on the host for every step
+        wanted: dict = {}
+        for sl in list(ops.step_lists(self.dtype) if hasattr(ops, "step_lists") else []) + \
+                self.model.step_lists():
+            wanted.setdefault(sl.name, sl)
+        self.step_lists = list(wanted.values())
         self.last_batch: Optional[StepBatch] = None
         self._graphs = None
         self._step_graphs = None
@@ -147,7 +153,7 @@ class Engine:
             logits = self._step_graphs.run(entries, starts, tables, slots)
         if logits is None:
             batch = build_step_batch(entries, starts, tables, slots, self.dtype, self.device,
-                                     max_position=self.plan.max_position)
+                                     max_position=self.plan.max_position, lists=self.step_lists)
             logits = self.forward(batch)
             self.last_batch = batch
         for e in entries:

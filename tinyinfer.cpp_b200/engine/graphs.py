@@ -19,7 +19,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
-from .batch import StepBatch, StepEntry, build_step_batch
+from .batch import StepBatch, StepEntry, build_lists, build_step_batch
 
 
 def capture(graph: "torch.cuda.CUDAGraph", run):
@@ -53,8 +53,22 @@ class _Bucket:
         self.width = -(-engine.plan.max_position // cache.page_size)
         groups = len(cache.groups)
         b = size
-        # layout of the packed integers: tok, pos, ctx, slots, then one table per group
-        self.total = 4 * b + groups * b * self.width
+        # the lists that kernels and parts want of a step: those that depend on the token counts
+        # only are built once, those that also depend on the positions travel with every step
+        ones, zeros = [1] * b, [0] * b
+        fixed = build_lists([sl for sl in engine.step_lists if not sl.uses_starts], ones, zeros)
+        self.moving = [sl for sl in engine.step_lists if sl.uses_starts]
+        moving = build_lists(self.moving, ones, zeros)
+        self.moving = [sl for sl in self.moving if moving[sl.name].size]
+        # layout of the packed integers: tok, pos, ctx, slots, the moving lists (all of which
+        # change with every step), then one block table per group (of which a step changes little)
+        self.moving_at = {}
+        at = 4 * b
+        for sl in self.moving:
+            self.moving_at[sl.name] = (at, moving[sl.name].shape)
+            at += moving[sl.name].size
+        self.head = at
+        self.total = self.head + groups * b * self.width
         # a ring of pinned staging buffers: one is rewritten only after the copy that read it
         # has run on the device (the host runs ahead of the device by several steps)
         self.hosts = [torch.empty(self.total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
@@ -63,7 +77,7 @@ class _Bucket:
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
         d = self.dev
         ar = torch.arange(b, dtype=torch.int32, device=dev)
-        tables = [d[4 * b + g * b * self.width: 4 * b + (g + 1) * b * self.width].view(b, self.width)
+        tables = [d[self.head + g * b * self.width: self.head + (g + 1) * b * self.width].view(b, self.width)
                   for g in range(groups)]
         self.batch = StepBatch(
             num_tokens=b, num_requests=b, num_logit_rows=b, act_dtype=engine.dtype,
@@ -72,9 +86,16 @@ class _Bucket:
             token_ids=d[0:b], positions=d[b:2 * b], req_of_tok=ar,
             cu_q=torch.arange(b + 1, dtype=torch.int32, device=dev),
             q_start_dev=d[b:2 * b], ctx_len_dev=d[2 * b:3 * b], logit_rows=ar,
-            state_slots=d[3 * b:4 * b], decode_rows=ar, chunk_rows=ar[:0],
-            chunk_tiles=ar[:0].view(-1, 3), chunk_tiles_big=ar[:0].view(-1, 3),
+            state_slots=d[3 * b:4 * b],
             max_position=engine.plan.max_position, block_tables=tables)
+        for name, arr in fixed.items():
+            self.batch.lists[name] = torch.from_numpy(arr.astype(np.int32)).to(dev)
+        for name, arr in moving.items():
+            if name in self.moving_at:
+                lo, shape = self.moving_at[name]
+                self.batch.lists[name] = d[lo:lo + arr.size].view(shape)
+            else:                                           # empty for steps of single tokens
+                self.batch.lists[name] = torch.from_numpy(arr.astype(np.int32)).to(dev)
         self.graph = None
         self.logits = None
         self.launches = 0
@@ -83,6 +104,10 @@ class _Bucket:
         self.row_req: list = [None] * b
         self.row_version = [0] * b
         self.row_blocks = [[0] * groups for _ in range(b)]
+        # per group the span of its table that the device has not seen yet: [first, past the last]
+        self.stale = [[self.total, 0] for _ in range(groups)]
+        self.last_copy_ints = 0
+        self.copied_ints = 0               # all integers sent to the device so far
         for i in range(b):
             self._reset_row(i, cache)
             self.row_req[i] = _PADDING
@@ -109,8 +134,9 @@ class _Bucket:
             for g in range(len(cache.groups)):
                 tb = cache.block_table(g, req)
                 if len(tb) > have[g]:
-                    base = 4 * b + g * b * w + i * w
+                    base = self.head + g * b * w + i * w
                     m[base + have[g]: base + len(tb)] = tb[have[g]:]
+                    self._touched(g, base + have[g], base + len(tb))
                     have[g] = len(tb)
         for i in range(n, b):                                   # padding rows
             if self.row_req[i] is not _PADDING:
@@ -119,13 +145,29 @@ class _Bucket:
         m[0:n] = [int(e.tokens[0]) for e in entries]
         m[b:b + n] = starts
         m[2 * b:2 * b + n] = m[b:b + n] + 1
+        if self.moving:
+            now = build_lists(self.moving, [1] * b, list(starts) + [0] * (b - n))
+            for name, arr in now.items():
+                lo, shape = self.moving_at[name]
+                if arr.shape != shape:
+                    raise ValueError(f"step list {name!r} changed its shape with the positions")
+                m[lo:lo + arr.size] = arr.reshape(-1)
         turn = self.turn
         self.turn = (turn + 1) % len(self.hosts)
         if self.copied[turn] is not None:
             self.copied[turn].synchronize()
         host = self.hosts[turn]
-        np.copyto(host.numpy(), m)
-        self.dev.copy_(host, non_blocking=True)
+        staged = host.numpy()
+        # only what changed travels: the head, and of each table the span that was written
+        spans = [(0, self.head)] + [(lo, hi) for lo, hi in self.stale if lo < hi]
+        self.last_copy_ints = 0
+        for lo, hi in spans:
+            staged[lo:hi] = m[lo:hi]
+            self.dev[lo:hi].copy_(host[lo:hi], non_blocking=True)
+            self.last_copy_ints += hi - lo
+        self.copied_ints += self.last_copy_ints
+        for span in self.stale:
+            span[0], span[1] = self.total, 0
         if device_tokens is not None:
             self.dev[0:n].copy_(device_tokens)
         done = torch.cuda.Event()
@@ -141,9 +183,17 @@ class _Bucket:
         m[2 * b + i] = 1
         m[3 * b + i] = cache.max_requests
         for g in range(len(cache.groups)):
-            base = 4 * b + g * b * w + i * w
-            m[base:base + w] = cache.null_page
+            base = self.head + g * b * w + i * w
+            # a row that held fewer blocks than its width has null pages behind them already
+            used = w if self.row_req[i] is None else max(self.row_blocks[i][g], 0)
+            m[base:base + used] = cache.null_page
+            self._touched(g, base, base + used)
         self.row_blocks[i] = [0] * len(cache.groups)
+
+    def _touched(self, group: int, lo: int, hi: int) -> None:
+        if lo < hi:
+            span = self.stale[group]
+            span[0], span[1] = min(span[0], lo), max(span[1], hi)
 
 
 _PADDING = object()
@@ -223,7 +273,7 @@ class StepGraphs(_OfEngine):
         key = (tuple(len(e.tokens) for e in entries), tuple(tuple(e.want) for e in entries))
         ent = self.graphs.get(key)
         build = dict(act_dtype=eng.dtype, device=eng.device, min_blocks=self.width,
-                     max_position=eng.plan.max_position)
+                     max_position=eng.plan.max_position, lists=eng.step_lists)
         if ent is not None:
             self.graphs.move_to_end(key)
             build_step_batch(entries, starts, tables, slots, dev_buffer=ent["buffer"], **build)

@@ -100,12 +100,19 @@ class Scheduler:
         if len(request.prompt) > self.max_position:
             self._finish(request, "too_long")
             return
-        # the longest the request can get must fit in an empty pool
+        # The longest the request can get must fit in an empty pool: all of it in a group that
+        # keeps every key; in a group with a window, the window and a token more, with the pages
+        # at both ends cut (portions are shortened to the room there is).  State of fixed size
+        # needs no such check: every request slot has its state allocated from the start.
         most = min(self.max_position, len(request.prompt) + request.params.max_tokens)
-        if any(-(-most // self.cache.page_size) > g.pool.count for g in self.cache.groups
-               if g.spec.window is None):
-            self._finish(request, "too_long")
-            return
+        ps = self.cache.page_size
+        for g in self.cache.groups:
+            need = -(-most // ps)
+            if g.spec.window is not None:
+                need = min(need, -(-(g.spec.window + 1) // ps) + 1)
+            if need > g.pool.count:
+                self._finish(request, "too_long")
+                return
         self.waiting.append(request)
 
     def has_work(self) -> bool:

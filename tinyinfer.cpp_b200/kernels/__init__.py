@@ -1,5 +1,5 @@
 """Bindings of the hand-written CUDA kernels (sm_100a)."""
-from .build import BuildError, build_all, build_library, load_library
+from .build import BuildError, build_all, build_library, load_library, register_library
 from .cuda_ops import CudaOps, KernelError
 
 _OPS: dict[str, CudaOps] = {}
@@ -14,4 +14,4 @@ def cuda_ops(device) -> CudaOps:
 
 
 __all__ = ["BuildError", "CudaOps", "KernelError", "build_all", "build_library", "cuda_ops",
-           "load_library"]
+           "load_library", "register_library"]

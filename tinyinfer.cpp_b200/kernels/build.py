@@ -27,6 +27,35 @@ LIBRARIES = {
              "gemm_tcgen05_few.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],
 }
 
+# libraries that parts bring themselves: name -> (absolute source paths, include folders)
+_EXTRA: dict[str, tuple[list[str], list[str]]] = {}
+
+
+def register_library(name: str, sources: list[str], include_dirs: list[str] = ()) -> None:
+    """Make ``load_library(name)`` build and load CUDA sources that live outside ``csrc/``: a part
+    with kernels of its own registers them from its module and binds the entry points itself.
+    The sources may include the headers of ``csrc/`` (``common.cuh`` and the rest); they are
+    compiled with the same flags, for sm_100a, into the same build folder."""
+    if name in LIBRARIES:
+        raise ValueError(f"library name {name!r} is taken by the engine's own kernels")
+    paths = [os.path.abspath(p) for p in sources]
+    for p in paths:
+        if not os.path.isfile(p):
+            raise BuildError(f"library {name!r}: source {p} does not exist")
+    _EXTRA[name] = (paths, [os.path.abspath(d) for d in include_dirs])
+    _LOADED.pop(name, None)
+
+
+def _sources_of(name: str) -> tuple[list[str], list[str]]:
+    """Absolute source paths and extra include folders of a library."""
+    if name in LIBRARIES:
+        return [os.path.join(CSRC, s) for s in LIBRARIES[name]], []
+    if name in _EXTRA:
+        return _EXTRA[name]
+    known = ", ".join(sorted(list(LIBRARIES) + list(_EXTRA)))
+    raise BuildError(f"no kernel library is named {name!r}; known: {known}")
+
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -66,13 +95,15 @@ def build_dir() -> str:
     raise BuildError("no writable folder for the compiled kernels: tried " + ", ".join(cands))
 
 
-def _digest(sources: list[str]) -> str:
+def _digest(sources: list[str], include_dirs: list[str]) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    headers = sorted(n for n in os.listdir(CSRC) if n.endswith((".cuh", ".h")))
-    for name in list(sources) + headers:
-        h.update(name.encode())
-        with open(os.path.join(CSRC, name), "rb") as fh:
+    headers = []
+    for d in [CSRC, *include_dirs]:
+        headers += sorted(os.path.join(d, n) for n in os.listdir(d) if n.endswith((".cuh", ".h")))
+    for path in list(sources) + headers:
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as fh:
             h.update(fh.read())
     return h.hexdigest()
 
@@ -108,11 +139,11 @@ def _run_all(cmds: dict[str, list[str]], what: str) -> None:
 
 def build_library(name: str, verbose: bool = True) -> str:
     """Make sure ``lib<name>`` is built and current; returns the path of the ``.so``."""
-    sources = LIBRARIES[name]
+    sources, include_dirs = _sources_of(name)
     out_dir = build_dir()
     so_path = os.path.join(out_dir, f"libtinyinfer_b200_{name}.so")
     stamp = so_path + ".sha256"
-    digest = _digest(sources)
+    digest = _digest(sources, include_dirs)
     with open(os.path.join(out_dir, f".{name}.lock"), "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
@@ -127,10 +158,14 @@ def build_library(name: str, verbose: bool = True) -> str:
             t0 = time.time()
             objs = {}
             cmds = {}
-            for src in sources:
+            includes = [x for d in [CSRC, *include_dirs] for x in ("-I", d)]
+            if name not in LIBRARIES:                  # ti_fail and friends live in common.cu
+                sources = [os.path.join(CSRC, "common.cu"), *sources]
+            for path in sources:
+                src = os.path.basename(path)
                 obj = os.path.join(out_dir, f"{name}_{os.path.splitext(src)[0]}.o")
                 objs[src] = obj
-                cmds[src] = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+                cmds[src] = [nvcc, *NVCC_FLAGS, *includes, "-c", path, "-o", obj]
             _run_all(cmds, f"'{name}' kernels")
             tmp = so_path + f".tmp{os.getpid()}"
             _run_all({"link": [nvcc, "-shared", "-o", tmp, *objs.values()]},

@@ -13,10 +13,14 @@ embed(table, token_ids, out)                 out[t] = float32(table[token_ids[t]
 rmsnorm(x, weight, eps, out, rows=None)      out[r] = norm(x[rows[r]] or x[r]), rounded to out.dtype
 linear(a, w, out, accumulate=False)          out (+)= a @ w.T in float32
 gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
-qk_norm_rope_store(...)                      q/k head norm, rotation, k/v into pages, q out
-qkv_rope_store(h, w, ...)                    the QKV product followed by qk_norm_rope_store, in one
+qk_norm_rope_store(qkv, ..., rotation, ...)  q/k head norm, rotation, k/v into pages, q out
+qkv_rope_store(h, w, ..., rotation, ...)     the QKV product followed by qk_norm_rope_store, in one
                                              launch where the kernels can (step.scratch holds what
-                                             they derive from the step, for one forward pass)
+                                             they derive from the step, for one forward pass).
+                                             ``rotation`` is what the position part answers
+                                             (parts.rope.Rotation); kinds without a kernel are
+                                             refused unless register_rotation gave a handler
+step_lists(act_dtype)                        the host-built lists its kernels want of every step
 paged_attention(...)                         causal attention over the pages of each token's request
 argmax(logits, out) / sample(...)            next token per row
 """
@@ -83,6 +87,10 @@ class CudaOps:
         self.few_tc_min_bytes = 1 << 25
         self._few_tickets = None
         self._retired = []                # outgrown counter buffers that captured graphs may still use
+        # rotation kind -> handler(ops, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
+        # num_heads, num_kv_heads, head_dim) that norms, rotates and stores the heads of a float32
+        # product; "neox" and "none" run on the kernels of csrc/, others are brought by parts
+        self._rotations = {"neox": CudaOps._rotate_builtin, "none": CudaOps._rotate_builtin}
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -99,7 +107,7 @@ class CudaOps:
         c.ti_argmax_sliced.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _vp]
         c.ti_gemm_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]
         c.ti_qk_norm_rope_store.argtypes = [
-            _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
+            _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
             _vp, _i, _vp, _vp]
         c.ti_paged_attention_simple.argtypes = [
             _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]
@@ -136,12 +144,31 @@ class CudaOps:
             b.ti_attn_prefill_tc_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_prefill_tc.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                              _f, _vp, _vp, _vp]
-            from ..engine.batch import PREFILL_TILE_ROWS, PREFILL_TILE_ROWS_BIG
-            if (b.ti_attn_prefill_tile_rows() != PREFILL_TILE_ROWS or
-                    b.ti_attn_prefill_tc_tile_rows() != PREFILL_TILE_ROWS_BIG):
-                raise KernelError("the attention kernel's tile height and the batch builder's differ")
+            self._tile_rows = (int(b.ti_attn_prefill_tile_rows()), int(b.ti_attn_prefill_tc_tile_rows()))
             self._bf16 = b
         return self._bf16
+
+    def step_lists(self, act_dtype):
+        """The host-built integer lists (``engine.batch.StepList``) that the attention kernels of
+        this kernel set want in every step of an engine with activations of ``act_dtype``: the
+        single-token rows, the rows of prompt portions, and the portions cut into tiles of each
+        prompt-attention kernel's own height.  The 32-bit kernels need none."""
+        if act_dtype != torch.bfloat16:
+            return []
+        from .step_lists import attention_lists
+        self.bf16
+        return attention_lists(self._tile_rows)
+
+    def stream(self) -> int:
+        """The CUDA stream (as an integer handle) on which the engine's kernels are launched; a
+        part with kernels of its own launches on it too."""
+        return self._stream()
+
+    def launched(self, rc: int = 0, message: str = "") -> None:
+        """Account for a launch made by a part's own library (and raise if it reports failure)."""
+        self.launches += 1
+        if rc != 0:
+            raise KernelError(message or f"a part's kernel returned {rc}")
 
     def _stream(self) -> int:
         return torch._C._cuda_getCurrentRawStream(self._device_index)
@@ -295,33 +322,61 @@ class CudaOps:
                                      _code(out, "swiglu"), self._stream()))
 
     # ---- attention -----------------------------------------------------------------------
-    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+    def register_rotation(self, kind: str, handler) -> None:
+        """Teach the kernel set a rotation kind of a position part: ``handler(ops, qkv, q_weight,
+        k_weight, eps, rotation, step, cache, q_out, num_heads, num_kv_heads, head_dim)`` gets the
+        float32 QKV product and does what ``qk_norm_rope_store`` does for the built-in kinds."""
+        self._rotations[kind] = handler
+
+    def _rotation_handler(self, rotation):
+        try:
+            return self._rotations[rotation.kind]
+        except KeyError:
+            raise KernelError(
+                f"no kernel rotates heads the way {rotation.kind!r} asks; known kinds: "
+                f"{', '.join(sorted(self._rotations))} (a part that brings its own registers a "
+                f"handler with ops.register_rotation)") from None
+
+    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                            num_heads, num_kv_heads, head_dim):
+        self._rotation_handler(rotation)(self, qkv, q_weight, k_weight, eps, rotation, step, cache,
+                                         q_out, num_heads, num_kv_heads, head_dim)
+
+    def _rotate_builtin(self, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
+                        num_heads, num_kv_heads, head_dim):
         t = qkv.shape[0]
         _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1, "qk_norm_rope_store: qkv float32")
         _need(qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim,
               "qk_norm_rope_store: qkv width does not match the head counts")
-        _need(inv_freq.shape[0] == head_dim // 2 and inv_freq.dtype == torch.float32,
-              "qk_norm_rope_store: the rotation table must hold head_dim/2 float32 values")
+        rot, inv_freq = int(rotation.rotary_dim), rotation.inv_freq
+        _need(0 <= rot <= head_dim and rot % 2 == 0,
+              f"qk_norm_rope_store: rotated width {rot} must be even and at most head_dim {head_dim}")
+        _need(rot == 0 or (inv_freq is not None and inv_freq.shape[0] == rot // 2
+                           and inv_freq.dtype == torch.float32),
+              "qk_norm_rope_store: the rotation table must hold rotary_dim/2 float32 values")
         pages, bt = cache.pages, cache.block_table
         _need(pages.is_contiguous() and tuple(pages.shape[1:]) ==
               (2, num_kv_heads, cache.page_size, head_dim), "qk_norm_rope_store: page layout")
         _need(bt.dtype == torch.int32 and bt.stride(1) == 1, "qk_norm_rope_store: block table int32")
         self._ok(self.core.ti_qk_norm_rope_store(
             qkv.data_ptr(), qkv.stride(0), q_weight.data_ptr(), k_weight.data_ptr(), float(eps),
-            inv_freq.data_ptr(), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
+            _ptr(inv_freq) if rot else None, step.positions.data_ptr(), step.req_of_tok.data_ptr(),
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
-            cache.page_size, int(bool(cache.writes)), t, num_heads, num_kv_heads, head_dim,
+            cache.page_size, int(bool(cache.writes)), t, num_heads, num_kv_heads, head_dim, rot,
             q_out.data_ptr(), _code(q_out, "q"), self.status.data_ptr(), self._stream()))
 
-    def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+    def qkv_rope_store(self, h, w_qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                        num_heads, num_kv_heads, head_dim):
-        """``qk_norm_rope_store`` of ``h @ w_qkv.T``.  Prompt portions with head size 128 run as
-        one tcgen05 product whose epilogue norms, rotates and stores each head, so the float32
-        product never reaches memory."""
+        """``qk_norm_rope_store`` of ``h @ w_qkv.T``.  Prompt portions with head size 128 and a
+        NeoX rotation over the whole head run as one tcgen05 product whose epilogue norms, rotates
+        and stores each head, so the float32 product never reaches memory."""
         t = q_out.shape[0]
         pages, bt = cache.pages, cache.block_table
+        self._rotation_handler(rotation)            # refuse an unknown kind before any launch
+        inv_freq = rotation.inv_freq
         fused = (self.fuse_qkv_epilogue and t > 64 and head_dim == 128 and w_qkv.dtype == torch.bfloat16
+                 and rotation.kind == "neox" and rotation.rotary_dim == head_dim
+                 and self._rotations["neox"] is CudaOps._rotate_builtin
                  and q_out.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
                  and h.dtype == torch.bfloat16
                  and w_qkv.stride(1) == 1 and w_qkv.stride(0) % 8 == 0 and w_qkv.shape[1] % 8 == 0
@@ -330,7 +385,7 @@ class CudaOps:
         if not fused:
             qkv = torch.empty((t, w_qkv.shape[0]), dtype=torch.float32, device=q_out.device)
             self.linear(h, w_qkv, qkv)
-            self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, inv_freq, step, cache, q_out,
+            self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                                     num_heads, num_kv_heads, head_dim)
             return
         n, k = w_qkv.shape
@@ -339,7 +394,7 @@ class CudaOps:
         _need(tuple(pages.shape[1:]) == (2, num_kv_heads, cache.page_size, head_dim),
               "qkv_rope_store: page layout")
         _need(bt.dtype == torch.int32 and bt.stride(1) == 1, "qkv_rope_store: block table int32")
-        _need(inv_freq.shape[0] == head_dim // 2 and inv_freq.dtype == torch.float32,
+        _need(inv_freq is not None and inv_freq.shape[0] == head_dim // 2 and inv_freq.dtype == torch.float32,
               "qkv_rope_store: the rotation table must hold head_dim/2 float32 values")
         key = ("rope_table", inv_freq.data_ptr())
         table = step.scratch.get(key)
@@ -379,10 +434,15 @@ class CudaOps:
               (2, num_kv_heads, cache.page_size, head_dim), "paged_attention: page layout")
         win = int(window or 0)
         rows, n_rows = None, q.shape[0]
-        n_dec = step.decode_rows.shape[0]
-        if (n_dec and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and
-                self.bf16.ti_attn_decode_supported(head_dim, num_heads // num_kv_heads,
-                                                   cache.page_size)):
+        lists = step.lists
+        tensor_cores = q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
+        if tensor_cores and "single_rows" not in lists:
+            raise KernelError("paged_attention: the step was built without this kernel set's lists "
+                              "(pass lists=ops.step_lists(dtype) to build_step_batch)")
+        single = lists["single_rows"] if tensor_cores else None
+        n_dec = single.shape[0] if tensor_cores else 0
+        if (n_dec and self.bf16.ti_attn_decode_supported(head_dim, num_heads // num_kv_heads,
+                                                         cache.page_size)):
             splits = self.decode_splits(n_dec, num_kv_heads, step.max_position or step.max_ctx_len, head_dim)
             part_o = torch.empty((n_dec, num_heads, splits, head_dim), dtype=torch.float32,
                                  device=q.device)
@@ -392,35 +452,36 @@ class CudaOps:
                 # zero once; every launch leaves its counters at zero again
                 self._counters = self._grown(self._counters, n_dec * num_kv_heads, q.device)
             self._ok(self.bf16.ti_attn_decode_fused(
-                q.data_ptr(), step.decode_rows.data_ptr(), n_dec, step.positions.data_ptr(),
+                q.data_ptr(), single.data_ptr(), n_dec, step.positions.data_ptr(),
                 step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
                 pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
                 float(scale), splits, part_o.data_ptr(), part_ml.data_ptr(),
                 self._counters.data_ptr(), out.data_ptr(), self.status.data_ptr(),
                 self._stream()), self.bf16)
-            rows, n_rows = step.chunk_rows, step.chunk_rows.shape[0]
+            rows, n_rows = lists["portion_rows"], lists["portion_rows"].shape[0]
             if n_rows == 0:
                 return
-        n_tiles = step.chunk_tiles.shape[0]
-        if (n_tiles and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and
-                self.bf16.ti_attn_prefill_supported(head_dim, cache.page_size)):
-            big = getattr(step, "chunk_tiles_big", None)
-            if (self.use_tc_attention and big is not None and self.bf16.ti_attn_prefill_tc_supported(
-                    head_dim, cache.page_size, num_heads, num_kv_heads)):
+        small, big = self._tile_rows if tensor_cores else (0, 0)
+        tiles = lists[f"portion_tiles_{small}"] if tensor_cores else None
+        n_tiles = tiles.shape[0] if tensor_cores else 0
+        if n_tiles and self.bf16.ti_attn_prefill_supported(head_dim, cache.page_size):
+            if self.use_tc_attention and self.bf16.ti_attn_prefill_tc_supported(
+                    head_dim, cache.page_size, num_heads, num_kv_heads):
+                tiles = lists[f"portion_tiles_{big}"]
                 self._ok(self.bf16.ti_attn_prefill_tc(
-                    q.data_ptr(), q.shape[0], big.data_ptr(), big.shape[0],
+                    q.data_ptr(), q.shape[0], tiles.data_ptr(), tiles.shape[0],
                     step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
                     pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
                     float(scale), out.data_ptr(), self.status.data_ptr(), self._stream()), self.bf16)
             else:
                 self._ok(self.bf16.ti_attn_prefill(
-                    q.data_ptr(), step.chunk_tiles.data_ptr(), n_tiles, step.positions.data_ptr(),
+                    q.data_ptr(), tiles.data_ptr(), n_tiles, step.positions.data_ptr(),
                     bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size,
                     num_heads, num_kv_heads, head_dim, win, float(scale), out.data_ptr(),
                     self.status.data_ptr(), self._stream()), self.bf16)
             if rows is not None:          # the single-token rows went through the decode kernel
                 return
-            rows, n_rows = step.decode_rows, n_dec
+            rows, n_rows = single, n_dec
             if n_rows == 0:
                 return
         self._ok(self.core.ti_paged_attention_simple(

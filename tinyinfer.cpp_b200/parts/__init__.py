@@ -8,10 +8,10 @@ from .embed_head import Embedding, LMHead
 from .mlp import SwiGLU
 from .model import CausalLM
 from .norm import RMSNorm
-from .rope import RopeNeox
+from .rope import NoPosition, RopeNeox, Rotation
 
 __all__ = [
-    "Attention", "CausalLM", "Embedding", "FixedStateSpec", "LMHead", "MATRIX", "NORM_WEIGHT",
-    "PagedKVSpec", "Part", "PreNormBlock", "RMSNorm", "RopeNeox", "SwiGLU", "WeightSpec",
+    "Attention", "CausalLM", "Embedding", "FixedStateSpec", "LMHead", "MATRIX", "NORM_WEIGHT", "NoPosition",
+    "PagedKVSpec", "Part", "PreNormBlock", "RMSNorm", "RopeNeox", "Rotation", "SwiGLU", "WeightSpec",
     "build_part", "register_part",
 ]

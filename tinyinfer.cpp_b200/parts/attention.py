@@ -2,8 +2,9 @@
 
 Reference order (src/inference.cu:41-55, src/cuda/attention.cu:12-87,107-198):
 ``qkv = h Wqkv^T`` (no bias; Wqkv = [Wq; Wk; Wv] on rows) -> per head RMSNorm of q
-and k with one ``[head_dim]`` weight each, before the rotation -> NeoX rotation of
-q and k at the token's position -> k, v rounded to the cache dtype and written at
+and k with one ``[head_dim]`` weight each, before the rotation -> rotation of q and k at
+the token's position as the position part describes it (NeoX pairs in the reference)
+-> k, v rounded to the cache dtype and written at
 the token's place -> for query head ``i``, kv head ``i // (heads / kv_heads)``,
 scores ``(q . k_p) * scale`` over ``p <= pos`` (and ``p > pos - window`` if the
 layer has a window), float32 softmax, weighted sum of v -> ``residual += attn Wo^T``.
@@ -69,8 +70,9 @@ class Attention(Part):
     def forward(self, ops, h, residual, step, cache):
         t, dev, act = h.shape[0], h.device, h.dtype
         q = torch.empty((t, self.nq), dtype=act, device=dev)
-        ops.qkv_rope_store(h, self.w_qkv, self.q_norm, self.k_norm, self.eps, self.position.table(dev),
-                           step, cache, q, self.num_heads, self.num_kv_heads, self.head_dim)
+        ops.qkv_rope_store(h, self.w_qkv, self.q_norm, self.k_norm, self.eps,
+                           self.position.rotation(dev), step, cache, q, self.num_heads,
+                           self.num_kv_heads, self.head_dim)
         out = torch.empty((t, self.nq), dtype=act, device=dev)
         ops.paged_attention(q, step, cache, out, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.window, self.scale)

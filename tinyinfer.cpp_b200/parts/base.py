@@ -10,7 +10,8 @@ configuration, its layer index or its checkpoint names.
 Interfaces
 ----------
 norm      ``forward(ops, x, out_dtype) -> h``; ``forward_rows(ops, x, rows, out_dtype)``.
-position  ``table(device)``: what the mixer's kernels need to rotate a head at a position.
+position  ``rotation(device) -> Rotation``: the pairing rule, rotated width and table that the
+          mixer hands on to the kernel that norms, rotates and stores its heads.
 mixer     ``cache_spec()``: what it keeps per request (``PagedKVSpec``, ``FixedStateSpec`` or
           None); ``forward(ops, h, residual, step, cache)``: adds its output to ``residual``.
 ffn       ``forward(ops, h, residual, step)``: adds its output to ``residual``.
@@ -62,6 +63,11 @@ class Part:
 
     def load_weights(self, tensors: Mapping[str, torch.Tensor], ops: Any) -> None:
         """Take the tensors named in ``weight_specs`` (already on the device, dtype as stored)."""
+
+    def step_lists(self) -> list:
+        """Integer lists (``engine.batch.StepList``) that this part wants built on the host for
+        every step and handed to it as ``step.lists[name]``."""
+        return []
 
     def shared_weights(self) -> dict[str, torch.Tensor]:
         """Tensors another part may alias (for instance the embedding table for a tied head)."""

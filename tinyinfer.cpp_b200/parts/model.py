@@ -64,6 +64,14 @@ class CausalLM:
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding)
 
+    def step_lists(self) -> list:
+        """The host-built lists that the model's parts ask of every step, each name once."""
+        found: dict = {}
+        for _, part in self._named:
+            for sl in part.step_lists():
+                found.setdefault(sl.name, sl)
+        return list(found.values())
+
     # ---- cache ---------------------------------------------------------------------------
     def cache_specs(self) -> list[PagedKVSpec | FixedStateSpec | None]:
         """What each cache slot of the schedule holds (from the mixer that writes it)."""
