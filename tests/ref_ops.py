@@ -92,6 +92,13 @@ class RefOps:
         self.qk_norm_rope_store(qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
                                 num_heads, num_kv_heads, head_dim)
 
+    def qkv_attention(self, h, w_qkv, q_weight, k_weight, eps, rotation, step, cache, out,
+                      num_heads, num_kv_heads, head_dim, window, scale):
+        q = torch.empty((h.shape[0], num_heads * head_dim), dtype=h.dtype, device=h.device)
+        self.qkv_rope_store(h, w_qkv, q_weight, k_weight, eps, rotation, step, cache, q,
+                            num_heads, num_kv_heads, head_dim)
+        self.paged_attention(q, step, cache, out, num_heads, num_kv_heads, head_dim, window, scale)
+
     def paged_attention(self, q, step, cache, out, num_heads, num_kv_heads, head_dim, window,
                         scale):
         t = q.shape[0]

@@ -420,6 +420,49 @@ def test_qkv_product_with_norm_rotation_and_store_in_its_epilogue(ops, geom, wri
     assert (q_out != q_two).float().mean().item() < 0.02
 
 
+@pytest.mark.parametrize("geom", [(16, 8, 128, 16), (8, 1, 128, 64), (4, 4, 64, 16), (6, 2, 64, 32), (32, 8, 128, 16)])
+@pytest.mark.parametrize("window", [None, 40])
+@pytest.mark.parametrize("writes", [True, False])
+def test_decoding_rows_from_the_raw_qkv_product(ops, geom, window, writes):
+    """A step of single-token rows: flash-decoding takes the float32 QKV product, norms, rotates
+    and stores by itself.  Against the plain statement and against the separate kernels; contexts
+    that end at the edges of tiles, pages and splits."""
+    heads, kv, hd, ps = geom
+    k = 96
+    ctx = [1, 2, 31, 32, 33, 64, 65, 129, 500, 1024, 1025, 3000, 17]
+    step, cache, _ = _paged_case(heads, kv, hd, ps, ctx, [1] * len(ctx), torch.bfloat16)
+    cache.writes = writes
+    t = len(ctx)
+    h = _rand((t, k), torch.bfloat16, seed=7)
+    w = _rand(((heads + 2 * kv) * hd, k), torch.bfloat16, seed=8, scale=2.0 / math.sqrt(k))
+    qw, kw = 1 + _rand((hd,), seed=4, scale=0.1), 1 + _rand((hd,), seed=5, scale=0.1)
+    rotation = _rotation(hd)
+    scale = 1.0 / math.sqrt(hd)
+    results = {}
+    for name in ("fused", "separate", "plain"):
+        c = SimpleNamespace(**vars(cache))
+        c.pages = cache.pages.clone()
+        out = torch.zeros((t, heads * hd), dtype=torch.bfloat16, device=DEV)
+        keep = ops.fuse_decode_rope
+        ops.fuse_decode_rope = name == "fused"
+        before = ops.launches
+        try:
+            (RefOps() if name == "plain" else ops).qkv_attention(
+                h, w, qw, kw, 1e-6, rotation, step, c, out, heads, kv, hd, window, scale)
+        finally:
+            ops.fuse_decode_rope = keep
+        results[name] = (out, c.pages, ops.launches - before)
+    ops.check_status()
+    assert results["fused"][2] == 2 and results["separate"][2] == 3          # one launch less
+    _close(results["fused"][0], results["plain"][0], 1.5e-2, f"fused decoding {geom} window={window}")
+    _close(results["fused"][1], results["plain"][1], 8e-3, "pages after the fused store")
+    # the same arithmetic in the same order as the separate kernels: the same bits
+    assert torch.equal(results["fused"][1], results["separate"][1]), "stored keys and values differ"
+    assert torch.equal(results["fused"][0], results["separate"][0]), "attention output differs"
+    if not writes:
+        assert torch.equal(results["fused"][1], cache.pages)
+
+
 @pytest.mark.parametrize("vocab", [151936, 1009, 16384])
 def test_argmax_first_maximum_wins(ops, vocab):
     logits = _rand((5, vocab))

@@ -22,6 +22,8 @@ qkv_rope_store(h, w, ..., rotation, ...)     the QKV product followed by qk_norm
                                              refused unless register_rotation gave a handler
 step_lists(act_dtype)                        the host-built lists its kernels want of every step
 paged_attention(...)                         causal attention over the pages of each token's request
+qkv_attention(h, w, ..., out, ...)           qkv_rope_store followed by paged_attention, for a mixer
+                                             that wants both at once
 argmax(logits, out) / sample(...)            next token per row
 """
 from __future__ import annotations
@@ -81,6 +83,10 @@ class CudaOps:
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
         self.fuse_qkv_epilogue = True     # the prompt QKV product norms, rotates and stores its heads
+        # steps of single tokens: flash-decoding norms, rotates and stores by itself, one launch less
+        # per layer.  Off: measured equal to the separate kernels within 1 % at batch 8 and 4 %
+        # slower at batch 1 (the work moves onto the attention kernel's own critical path)
+        self.fuse_decode_rope = False
         # few-rows products on tcgen05 with K split over blocks: for weights of at least this many
         # bytes (None: never), below which the direct-to-register kernel's shorter chain wins
         # (measured: 4096 x 4096 is even at 16 rows, larger weights gain 15-50 %)
@@ -130,6 +136,9 @@ class CudaOps:
             b.ti_attn_decode_blocks_per_sm.argtypes = [_i]
             b.ti_attn_decode_fused.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i,
                                                _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
+            b.ti_attn_decode_qkv_supported.argtypes = [_i, _i, _i]
+            b.ti_attn_decode_qkv.argtypes = [_vp, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i,
+                                             _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
             b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
@@ -413,6 +422,49 @@ class CudaOps:
                     pages.data_ptr(), pages.shape[0], cache.page_size, int(bool(cache.writes)),
                     num_heads, num_kv_heads, q_out.data_ptr(), self.status.data_ptr(), self._stream()),
                  self.bf16)
+
+    def qkv_attention(self, h, w_qkv, q_weight, k_weight, eps, rotation, step, cache, out,
+                      num_heads, num_kv_heads, head_dim, window, scale):
+        """The whole front of an attention mixer: ``out = attention(rotate(norm(h @ w_qkv.T)))``
+        with the new keys and values stored on the way (``qkv_rope_store`` followed by
+        ``paged_attention``).  In a step of single-token rows the flash-decoding kernel takes the
+        float32 product as it is and norms, rotates and stores by itself: one launch less."""
+        t = h.shape[0]
+        pages, bt = cache.pages, cache.block_table
+        single = step.lists.get("single_rows")
+        group = num_heads // num_kv_heads
+        fused = (self.fuse_decode_rope and t > 0 and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                 and pages.dtype == torch.bfloat16 and single is not None and single.shape[0] == t
+                 and rotation.kind == "neox" and rotation.rotary_dim == head_dim
+                 and self._rotations["neox"] is CudaOps._rotate_builtin
+                 and rotation.inv_freq is not None and rotation.inv_freq.dtype == torch.float32
+                 and q_weight.dtype == torch.float32 and k_weight.dtype == torch.float32
+                 and pages.is_contiguous() and out.is_contiguous()
+                 and tuple(pages.shape[1:]) == (2, num_kv_heads, cache.page_size, head_dim)
+                 and bt.dtype == torch.int32 and bt.stride(1) == 1
+                 and self.bf16.ti_attn_decode_qkv_supported(head_dim, group, cache.page_size))
+        if not fused:
+            q = torch.empty((t, num_heads * head_dim), dtype=h.dtype, device=h.device)
+            self.qkv_rope_store(h, w_qkv, q_weight, k_weight, eps, rotation, step, cache, q,
+                                num_heads, num_kv_heads, head_dim)
+            self.paged_attention(q, step, cache, out, num_heads, num_kv_heads, head_dim, window, scale)
+            return
+        width = w_qkv.shape[0]
+        _need(width == (num_heads + 2 * num_kv_heads) * head_dim, "qkv_attention: weight rows")
+        qkv = torch.empty((t, width), dtype=torch.float32, device=h.device)
+        self.linear(h, w_qkv, qkv)
+        splits = self.decode_splits(t, num_kv_heads, step.max_position or step.max_ctx_len, head_dim)
+        part_o = torch.empty((t, num_heads, splits, head_dim), dtype=torch.float32, device=h.device)
+        part_ml = torch.empty((t, num_heads, splits, 2), dtype=torch.float32, device=h.device)
+        if self._counters is None or self._counters.numel() < t * num_kv_heads:
+            self._counters = self._grown(self._counters, t * num_kv_heads, h.device)
+        self._ok(self.bf16.ti_attn_decode_qkv(
+            qkv.data_ptr(), width, q_weight.data_ptr(), k_weight.data_ptr(), float(eps),
+            rotation.inv_freq.data_ptr(), single.data_ptr(), t, step.positions.data_ptr(),
+            step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0],
+            cache.page_size, int(bool(cache.writes)), num_heads, num_kv_heads, head_dim, int(window or 0),
+            float(scale), splits, part_o.data_ptr(), part_ml.data_ptr(), self._counters.data_ptr(),
+            out.data_ptr(), self.status.data_ptr(), self._stream()), self.bf16)
 
     def decode_splits(self, rows: int, num_kv_heads: int, max_position: int, head_dim: int = 128) -> int:
         """In how many blocks the keys of a decoding row are cut, per kv head.  It depends on

@@ -69,13 +69,10 @@ class Attention(Part):
 
     def forward(self, ops, h, residual, step, cache):
         t, dev, act = h.shape[0], h.device, h.dtype
-        q = torch.empty((t, self.nq), dtype=act, device=dev)
-        ops.qkv_rope_store(h, self.w_qkv, self.q_norm, self.k_norm, self.eps,
-                           self.position.rotation(dev), step, cache, q, self.num_heads,
-                           self.num_kv_heads, self.head_dim)
         out = torch.empty((t, self.nq), dtype=act, device=dev)
-        ops.paged_attention(q, step, cache, out, self.num_heads, self.num_kv_heads,
-                            self.head_dim, self.window, self.scale)
+        ops.qkv_attention(h, self.w_qkv, self.q_norm, self.k_norm, self.eps, self.position.rotation(dev),
+                          step, cache, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                          self.window, self.scale)
         ops.linear(out, self.w_o, residual, accumulate=True)
 
 
