@@ -1,17 +1,19 @@
 """Command line in the reference's manner (src/main.cpp:136-158, report at :300-310).
 
-    python -m tinyinfer_b200.cli -m MODEL_DIR -n 128 -p "1 2 3" [-p ...] [-f prompts.txt]
-        [-t temp] [--top-k K] [--top-p P] [--seed S] [--max-seq N] [--cuda-graph] [--verbose]
+    python -m tinyinfer_b200.cli -m MODEL -n 128 -p "text" [-p ...] [-f prompts.txt]
+        [-t temp] [--top-k K] [--top-p P] [--seed S] [--max-seq N] [--cuda-graph] [--verbose] [--chat]
 
-Options keep the reference's names, meanings and defaults: ``-m`` model (here a folder with
-config.json and model.safetensors), ``-n`` new tokens per prompt (128), ``-p`` a prompt
-(repeatable), ``-f`` a file with one prompt per non-empty line, ``-t`` temperature (0 =
-greedy), ``--top-k`` (0 = off), ``--top-p`` (1.0), ``--seed`` (42), ``--max-seq`` context per
-request (2048), ``--cuda-graph`` replay decode steps from CUDA graphs, ``--verbose``.
+Options keep the reference's names, meanings and defaults: ``-m`` model (a folder with
+config.json and model.safetensors, or a GGUF file as the reference takes), ``-n`` new tokens
+per prompt (128), ``-p`` a prompt (repeatable), ``-f`` a file with one prompt per non-empty
+line, ``-t`` temperature (0 = greedy), ``--top-k`` (0 = off), ``--top-p`` (1.0), ``--seed`` (42),
+``--max-seq`` context per request (2048), ``--cuda-graph`` replay steps from CUDA graphs,
+``--verbose``, ``--chat`` (wrap each prompt in the Qwen3 chat form with an empty think block).
 
-The engine works on token ids.  A prompt is text if the model folder holds a
-``tokenizer.json`` (read with the ``tokenizers`` library); otherwise it is a list of token
-ids separated by spaces or commas.  Added options: ``--dtype``, ``--chunk``,
+The engine works on token ids.  A prompt is text if the model brings a tokenizer (a GGUF file's
+``tokenizer.ggml.*`` metadata, a folder's ``tokenizer.json``; read by this package's own
+byte-level BPE tokenizer); otherwise, and always with ``--tokens``, it is a list of token ids
+separated by spaces or commas.  Added options: ``--tokens``, ``--dtype``, ``--chunk``,
 ``--max-batched-tokens``, ``--max-num-seqs``, ``--page-size``, ``--kv-tokens``, and
 ``--random-weights CONFIG.json`` to run a configuration with seeded random weights.
 """
@@ -44,6 +46,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-seq", type=int, default=2048)
     ap.add_argument("--cuda-graph", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--chat", action="store_true", help="wrap prompts in the Qwen3 chat form")
+    ap.add_argument("--tokens", action="store_true", help="prompts are token ids, also when the model has a tokenizer")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
     ap.add_argument("--chunk", type=int, default=None, help="longest prompt portion per step")
     ap.add_argument("--max-batched-tokens", type=int, default=2048)
@@ -71,21 +75,23 @@ def main(argv=None) -> int:
 
     from . import LLM, SamplingParams
 
+    from .tokenizer import Tokenizer, TokenizerError, chat_wrap
     tokenizer = None
-    tok_path = os.path.join(args.model, "tokenizer.json") if args.model else None
-    if tok_path and os.path.isfile(tok_path):
-        from tokenizers import Tokenizer
-        tokenizer = Tokenizer.from_file(tok_path)
+    if args.model and not args.tokens:
+        try:
+            tokenizer = Tokenizer.for_model(args.model)
+        except (TokenizerError, OSError, ValueError) as exc:
+            print(f"main: cannot read the model's tokenizer: {exc}", file=sys.stderr)
+            return 1
     token_lists = []
     for s, text in enumerate(prompts):
         if tokenizer is not None:
-            ids = tokenizer.encode(text).ids
+            ids = tokenizer.encode(chat_wrap(text) if args.chat else text, parse_special=args.chat)
         else:
             try:
                 ids = [int(x) for x in text.replace(",", " ").split()]
             except ValueError:
-                print("main: no tokenizer.json in the model folder; give prompts as token ids",
-                      file=sys.stderr)
+                print("main: the model brings no tokenizer; give prompts as token ids", file=sys.stderr)
                 return 1
         if args.verbose:
             print(f"prompt {s} tokens: {len(ids)}", file=sys.stderr)
@@ -102,15 +108,17 @@ def main(argv=None) -> int:
             llm = LLM(config=json.load(fh), seed=args.seed, **kwargs)
     else:
         llm = LLM(args.model, **kwargs)
+    stop = () if tokenizer is None or tokenizer.eos_token_id is None else (tokenizer.eos_token_id,)
     params = SamplingParams(temperature=args.temp, top_k=args.top_k, top_p=args.top_p,
-                            seed=args.seed, max_tokens=args.n_predict)
+                            seed=args.seed, max_tokens=args.n_predict, stop_token_ids=stop)
     t0 = time.perf_counter()
     outs = llm.generate(token_lists, params, log_steps=args.verbose)
     seconds = time.perf_counter() - t0
     for s, (text, gen) in enumerate(zip(prompts, outs)):
         print(f"==================== prompt {s} ====================")
         print(f"[prompt] {text}")
-        shown = tokenizer.decode(gen.tokens) if tokenizer else " ".join(map(str, gen.tokens))
+        made = gen.tokens[:-1] if gen.finish_reason == "stop" and tokenizer else gen.tokens
+        shown = tokenizer.decode(made) if tokenizer else " ".join(map(str, gen.tokens))
         print(f"[output] {shown}")
     st = llm.stats
     print(f"main: {st.steps} steps, {st.prompt_tokens} prompt tokens, {st.decode_tokens} decode "

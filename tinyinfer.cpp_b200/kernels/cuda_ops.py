@@ -82,6 +82,7 @@ class CudaOps:
         self._counters = None
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
+        self.pair_min_tiles = torch.cuda.get_device_properties(self.device).multi_processor_count // 2
         self.fuse_qkv_epilogue = True     # the prompt QKV product norms, rotates and stores its heads
         # steps of single tokens: flash-decoding norms, rotates and stores by itself, one launch less
         # per layer.  Off: measured equal to the separate kernels within 1 % at batch 8 and 4 %
@@ -209,7 +210,7 @@ class CudaOps:
     def _tc_gemm(self, m: int, n: int):
         """The tcgen05 product to use: on pairs of SMs when every pair gets a 256 x 256 tile."""
         tiles = -(-m // 256) * -(-n // 256)
-        if self.use_2sm_gemm and tiles >= self.num_sms // 2:
+        if self.use_2sm_gemm and tiles >= self.pair_min_tiles:
             return self.bf16.ti_gemm_tcgen05_2sm
         return self.bf16.ti_gemm_tcgen05
 
