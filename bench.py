@@ -18,7 +18,12 @@ prefill    one request's 2,048-token prompt in one step: tokens a second and the
            flops / time / bf16 peak;
 roofline   the bytes a decode step has to read (every weight once, and the keys and values of
            the live requests) / its time, against the copy bandwidth;
-points     decode tokens a second at batch 1 and 64.
+points     decode tokens a second at batch 1 and 64, the same steps without a CUDA graph, a mixed
+           step (63 requests decoding beside a 512-token portion); then, as `page16_*`, `8b_*` and
+           `32b_*`, the page size of 16 tokens and the Qwen3-8B and Qwen3-32B shapes (decode at
+           batch 1, 8, 64, the 2,048-token prefill, the 8B mixed step);
+points_frac  for each point its fraction of its roofline (decode: bytes / time / copy bandwidth;
+           prefill: flops / time / the bf16 peak, the sustained one for steps over 5 ms).
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on this pool (6.65 TB/s, 1.59 PFLOP/s), and the fractions say which.  The working
@@ -67,7 +72,8 @@ QWEN3_32B = dict(QWEN3_0_6B, num_hidden_layers=64, hidden_size=5120, num_attenti
 SHAPES = {"0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "8b": ("Qwen3-8B shape", QWEN3_8B),
           "32b": ("Qwen3-32B shape", QWEN3_32B)}
 PAGE = 64
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+MAX_POSITION = 40960           # the longest context of the published models of this architecture
 
 
 def peaks():
@@ -75,9 +81,18 @@ def peaks():
     try:
         with open(path) as fh:
             p = json.load(fh)
-        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"]))}, "measured"
     except (OSError, KeyError, ValueError, TypeError):
         return dict(FALLBACK_PEAKS), "fallback"
+
+
+def flops_peak(pk, ms):
+    """The bf16 peak a step of `ms` milliseconds is held against: the burst figure for a short
+    step, the figure sustained under the power cap for one of more than a few milliseconds."""
+    if ms > 5.0:
+        return pk["bf16_tflops_sustained"], "sustained"
+    return pk["bf16_tflops"], "burst"
 
 
 class ClockSampler:
@@ -231,17 +246,21 @@ def decode_e2e(llm, batch, context, steps, warmup, torch):
     for _ in range(warmup):
         session.step()
     torch.cuda.synchronize()
+    buckets = llm.engine._graphs.buckets
+    copied = sum(bk.copied_ints for bk in buckets.values())
     t0 = time.perf_counter()
     for _ in range(steps):
         made = session.step()
         assert len(made) == batch
     torch.cuda.synchronize()
     sec = time.perf_counter() - t0
+    copied = sum(bk.copied_ints for bk in buckets.values()) - copied
     while not session.done:
         session.step()
     session.finish()
-    bk = llm.engine._graphs.buckets[max(llm.engine._graphs.buckets)]
-    return sec / steps * 1e3, bk.total * 4, batch * 4
+    # what a step copies: its tokens, positions, lengths and slots, and the block-table entries
+    # its requests gained (a mean over the timed steps), not the whole table
+    return sec / steps * 1e3, round(copied * 4 / steps), batch * 4
 
 
 def measure_decode(engine, batch, context, steps, warmup, torch):
@@ -346,6 +365,42 @@ def measure_chains(engine, batch, torch):
         torch.cuda.synchronize()
         out[name] = round(start.elapsed_time(stop) / 20 / n * 1e3, 2)
     return out
+
+
+def shape_points(shape_key, page_size, context, steps, warmup, batches, prefill, mixed, pk, torch, prefix):
+    """Decode at the given batches, the 2,048-token prefill and the mixed step for another shape
+    or page size, each with its fraction of its roofline.  Returns (points, fractions)."""
+    import gc
+    from tinyinfer_b200 import LLM
+    shape_name, shape_cfg = SHAPES[shape_key]
+    cfg = dict(shape_cfg, max_position_embeddings=MAX_POSITION)
+    nums = model_numbers(cfg)
+    max_batch = max(list(batches) + ([64] if mixed else []) + [1])
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", page_size=page_size, max_seq=context,
+              max_num_seqs=max_batch + 1, kv_tokens=max_batch * context, cuda_graph=True)
+    engine = llm.engine
+    points, fracs = {}, {}
+    try:
+        for b in batches:
+            n = min(steps, 32)
+            ms, _, _ = measure_decode(engine, b, context, n, warmup, torch)
+            points[f"{prefix}decode_b{b}"] = round(b / (ms * 1e-3), 1)
+            step_bytes = nums["weight_bytes"] + b * (context - n // 2) * nums["kv_bytes_per_token"]
+            fracs[f"{prefix}decode_b{b}"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        if prefill:
+            ms = measure_prefill(engine, 2048, 3, torch)
+            peak, which = flops_peak(pk, ms)
+            points[f"{prefix}prefill_2048"] = round(2048 / (ms * 1e-3), 1)
+            fracs[f"{prefix}prefill_2048"] = round(prefill_flops(cfg, 2048) / (ms * 1e-3) / (peak * 1e12), 4)
+            fracs[f"{prefix}prefill_2048_peak"] = which
+        if mixed:
+            ms = measure_mixed(engine, 63, 512, context, torch)
+            points[f"{prefix}mixed_63_decoding_512_portion"] = round((63 + 512) / (ms * 1e-3), 1)
+    finally:
+        del engine, llm
+        gc.collect()
+        torch.cuda.empty_cache()
+    return points, fracs
 
 
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
@@ -490,7 +545,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
     ap.add_argument("--shape", choices=list(SHAPES), default="0.6b", help="layer sizes of the model")
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the other shapes")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the 8B and 32B shapes and the page-16 run")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per cache page")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
@@ -508,7 +564,7 @@ def main() -> int:
 
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
-    cfg["max_position_embeddings"] = max(args.context, 2048)
+    cfg["max_position_embeddings"] = max(args.context, MAX_POSITION)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -542,11 +598,14 @@ def main() -> int:
     step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
-    points = {}
+    points, fracs = {}, {}
     if not args.no_points:
         for b in (1, 64):
-            pms, _, _ = measure_decode(engine, b, args.context, min(args.steps, 32), warmup, torch)
+            n = min(args.steps, 32)
+            pms, _, _ = measure_decode(engine, b, args.context, n, warmup, torch)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            b_bytes = nums["weight_bytes"] + b * (args.context - n // 2) * nums["kv_bytes_per_token"]
+            fracs[f"decode_b{b}"] = round(b_bytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         eager_ms = decode_eager_timed(engine, args.batch, args.context, min(args.steps, 32), warmup, torch)
         points[f"decode_b{args.batch}_no_graph"] = round(args.batch / (eager_ms * 1e-3), 1)
         # chunked prefill under load: 63 requests decode beside a 512-token portion of a prompt
@@ -555,7 +614,25 @@ def main() -> int:
 
     pf_tokens = 2048
     pf_ms = measure_prefill(engine, pf_tokens, 3, torch)
-    pf_frac = prefill_flops(cfg, pf_tokens) / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+    pf_peak, pf_which = flops_peak(pk, pf_ms)
+    pf_frac = prefill_flops(cfg, pf_tokens) / (pf_ms * 1e-3) / (pf_peak * 1e12)
+
+    if not args.no_points and not args.no_shapes and args.shape == "0.6b" and not args.layers:
+        # the page size and the two larger shapes that the baseline names, as points of their own
+        import gc
+        del engine, llm
+        gc.collect()
+        torch.cuda.empty_cache()
+        for key, page, batches, pre, mix, prefix in (
+                ("0.6b", 16, (8,), True, False, "page16_"),
+                ("8b", args.page_size, (1, 8, 64), True, True, "8b_"),
+                ("32b", args.page_size, (1, 8, 64), True, False, "32b_")):
+            try:
+                p2, f2 = shape_points(key, page, args.context, args.steps, warmup, batches, pre, mix, pk, torch, prefix)
+            except Exception as exc:                    # a point that fails must not lose the line
+                p2, f2 = {f"{prefix}error": f"{type(exc).__name__}: {str(exc)[:120]}"}, {}
+            points.update(p2)
+            fracs.update(f2)
 
     value = args.batch / (ms * 1e-3)
     line = {
@@ -570,18 +647,19 @@ def main() -> int:
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"], "global_batch": args.batch,
-            "seq_len": args.context, "page_size": args.page_size, "parallelism": "single GPU",
-            "cuda_graph": True, "l2": "working set > L2, no flush", "peaks": pk_kind,
+            "seq_len": args.context, "page_size": args.page_size, "max_position": cfg["max_position_embeddings"],
+            "parallelism": "single GPU", "cuda_graph": True, "l2": "working set > L2, no flush", "peaks": pk_kind,
         },
         "clocks": clocks,
         "e2e": {"value": round(args.batch / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "prefill": {"value": round(pf_tokens / (pf_ms * 1e-3), 1), "tokens": pf_tokens,
-                    "ms": round(pf_ms, 3), "frac": round(pf_frac, 4)},
+                    "ms": round(pf_ms, 3), "frac": round(pf_frac, 4), "peak": pf_which},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "points_frac": fracs,
     }
     print(json.dumps(line))
     return 0
