@@ -135,12 +135,12 @@ def test_linear_few_rows_on_tcgen05(ops, m, nk):
 
 
 def test_large_weights_go_to_the_split_k_kernel(ops):
-    """The dispatch: at least 32 MiB of weights and at most 64 rows."""
-    w = _rand((4096, 4096), torch.bfloat16, seed=1, scale=0.05)
+    """The dispatch: more than 32 MiB of weights and at most 64 rows."""
+    w = _rand((6144, 4096), torch.bfloat16, seed=1, scale=0.05)
     a = _rand((8, 4096), torch.bfloat16)
-    out = torch.empty((8, 4096), device=DEV)
+    out = torch.empty((8, 6144), device=DEV)
     ops.linear(a, w, out)
-    _close(out, a.double() @ w.double().T, _sum_rtol(4096), "4096 x 4096 at 8 rows")
+    _close(out, a.double() @ w.double().T, _sum_rtol(4096), "6144 x 4096 at 8 rows")
     keep = ops.few_tc_min_bytes
     try:
         ops.few_tc_min_bytes = None
@@ -148,6 +148,17 @@ def test_large_weights_go_to_the_split_k_kernel(ops):
         ops.linear(a, w, other)
         assert not torch.equal(out, other), "both runs took the same kernel"
         _close(other, out, _sum_rtol(4096), "the two few-rows kernels")
+    finally:
+        ops.few_tc_min_bytes = keep
+    # exactly 32 MiB stays with the other kernel: both settings give the same bits
+    w = w[:4096]
+    out = torch.empty((8, 4096), device=DEV)
+    ops.linear(a, w, out)
+    try:
+        ops.few_tc_min_bytes = None
+        other = torch.empty_like(out)
+        ops.linear(a, w, other)
+        assert torch.equal(out, other), "32 MiB of weights took the split-K kernel"
     finally:
         ops.few_tc_min_bytes = keep
     ops.check_status()

@@ -213,18 +213,37 @@ gemm_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             epilogue_sync();
             if (*ticket_slot != splits - 1) continue;
             __threadfence();
-            const float* first = ws + (size_t)tile * splits * NTOK * BW;
-#pragma unroll 1
-            for (int t0 = 0; t0 < NTOK && t0 < m; t0 += 16) {
-                float v[16];
+            // Other blocks wrote the partial sums, so every load is a round trip to L2 of most of
+            // a microsecond, and this merge is the exposed tail of the tile: the loads of several
+            // splits (as many as the registers hold) are all requested before any is added, and
+            // the additions then follow in ascending order of the split.
+            const float* first = ws + (size_t)tile * splits * NTOK * BW + row_in_tile;
+            constexpr int AT_ONCE = NTOK == 16 ? 8 : NTOK == 32 ? 3 : 1;
+            float acc[NTOK];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.0f;
-                for (int s = 0; s < splits; ++s) {
-                    const float* p = first + ((size_t)s * NTOK + t0) * BW + row_in_tile;
+            for (int i = 0; i < NTOK; ++i) acc[i] = 0.0f;
+            for (int s0 = 0; s0 < splits; s0 += AT_ONCE) {
+                float got[AT_ONCE][NTOK];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] += __ldcg(p + (size_t)i * BW);
+                for (int j = 0; j < AT_ONCE; ++j) {
+                    // a split past the last one is read from the last one and counts as zero
+                    const int sj = s0 + j < splits ? s0 + j : splits - 1;
+                    const float* p = first + (size_t)sj * NTOK * BW;
+#pragma unroll
+                    for (int i = 0; i < NTOK; ++i) got[j][i] = __ldcg(p + (size_t)i * BW);
                 }
-                finish16(v, t0, n_row, lane, c, out_act, m, n, ldc, ld_act, mode);
+#pragma unroll
+                for (int j = 0; j < AT_ONCE; ++j) {
+                    const bool live = s0 + j < splits;
+#pragma unroll
+                    for (int i = 0; i < NTOK; ++i) acc[i] += live ? got[j][i] : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int t0 = 0; t0 < NTOK; t0 += 16) {
+                if (t0 < m)
+                    finish16(*reinterpret_cast<const float(*)[16]>(&acc[t0]), t0, n_row, lane, c, out_act, m, n,
+                             ldc, ld_act, mode);
             }
             if (warp == 2 && lane == 0) tickets[tile] = 0;
         }

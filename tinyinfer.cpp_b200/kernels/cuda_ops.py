@@ -88,9 +88,10 @@ class CudaOps:
         # per layer.  Off: measured equal to the separate kernels within 1 % at batch 8 and 4 %
         # slower at batch 1 (the work moves onto the attention kernel's own critical path)
         self.fuse_decode_rope = False
-        # few-rows products on tcgen05 with K split over blocks: for weights of at least this many
-        # bytes (None: never), below which the direct-to-register kernel's shorter chain wins
-        # (measured: 4096 x 4096 is even at 16 rows, larger weights gain 15-50 %)
+        # few-rows products on tcgen05 with K split over blocks: for weights of more than this many
+        # bytes (None: never); up to it the direct-to-register kernel's shorter chain wins (measured:
+        # a 4096 x 4096 weight takes 8.7 against 11.1 us at one row and 21 against 31 us at 64,
+        # larger weights gain 15-50 % on tcgen05)
         self.few_tc_min_bytes = 1 << 25
         self._few_tickets = None
         self._retired = []                # outgrown counter buffers that captured graphs may still use
@@ -218,7 +219,7 @@ class CudaOps:
         """Runs the split-K tcgen05 product for few rows if it applies to these operands."""
         m, k = a.shape
         n = w.shape[0]
-        if (self.few_tc_min_bytes is None or m > 64 or n * k * 2 < self.few_tc_min_bytes
+        if (self.few_tc_min_bytes is None or m > 64 or n * k * 2 <= self.few_tc_min_bytes
                 or a.data_ptr() % 16 or w.data_ptr() % 16
                 or not self.bf16.ti_gemm_tcgen05_few_supported(m, n, k, a.stride(0), w.stride(0), mode)):
             return False
