@@ -177,7 +177,8 @@ def plan_text(passes: list[dict], max_seq: int) -> str:
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("--reference", default=os.environ.get("TINYINFER_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("TINYINFER_REFERENCE", os.path.join(ROOT, "baseline", "_ref", "src")),
+                    help="the reference's tree (default: $TINYINFER_REFERENCE, else baseline/_ref/src)")
     ap.add_argument("--check", action="store_true", help="compare with the stored files instead of writing")
     ap.add_argument("--asan", action="store_true", help="build with the address sanitizer")
     ap.add_argument("--keep", action="store_true", help="keep the temporary folder and print its path")

@@ -13,7 +13,7 @@ from tinyinfer_b200.tokenizer import (TOKEN_CONTROL, TOKEN_NORMAL, Tokenizer, by
 from tinyinfer_b200.weights import write_gguf
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE = os.environ.get("TINYINFER_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("TINYINFER_REFERENCE", os.path.join(os.path.dirname(HERE), "baseline", "_ref", "src"))
 
 CORPUS = ("the quick brown fox jumps over the lazy dog. The dog didn't mind; it's the fox's habit!\n"
           "numbers 12345 and 3.14159, tabs\tand  double  spaces, CamelCase and snake_case words\n"
