@@ -37,7 +37,10 @@ class RefOps:
         inv = torch.rsqrt((src * src).mean(dim=-1, keepdim=True) + eps)
         out.copy_((src * inv * weight.to(F32)).to(out.dtype))
 
-    def linear(self, a, w, out, accumulate=False):
+    def flush(self):
+        pass
+
+    def linear(self, a, w, out, accumulate=False, may_defer=False):
         prod = a.to(F32) @ w.to(F32).T
         if accumulate:
             out.add_(prod)
@@ -49,6 +52,11 @@ class RefOps:
         gu = h.to(F32) @ w_gate_up.to(F32).T
         gate, up = gu[:, :inter], gu[:, inter:]
         out.copy_((gate / (1.0 + torch.exp(-gate)) * up).to(out.dtype))
+
+    def swiglu_ffn(self, h, w_gate_up, w_down, residual):
+        y = torch.empty((h.shape[0], w_down.shape[1]), dtype=h.dtype, device=h.device)
+        self.gate_up_swiglu(h, w_gate_up, y)
+        self.linear(y, w_down, residual, accumulate=True)
 
     # ---- attention -----------------------------------------------------------------------
     def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,

@@ -164,6 +164,147 @@ def test_large_weights_go_to_the_split_k_kernel(ops):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("sizes", [(1024, 3072), (256, 640), (512, 1536), (2048, 2048)])
+def test_decode_feed_forward_in_one_launch(ops, m, sizes):
+    """gate/up, SwiGLU and down projection of a decode step as one launch (weights copied to
+    shared memory ahead of the dependency wait): the same bits as the two launches, also when
+    launched many times in a row (the arrival counters return to zero), and the plain formula."""
+    from ref_ops import RefOps
+    hidden, inter = sizes
+    gate = _rand((inter, hidden), torch.bfloat16, seed=1, scale=0.05)
+    up = _rand((inter, hidden), torch.bfloat16, seed=2, scale=0.05)
+    down = _rand((hidden, inter), torch.bfloat16, seed=3, scale=0.05)
+    x = _rand((m, hidden), torch.bfloat16, seed=4)
+    res = _rand((m, hidden), torch.float32, seed=5)
+    w_gu = ops.pack_gate_up(gate, up)
+    assert ops.bf16.ti_ffn_decode_supported(m, hidden, inter, hidden, hidden, inter, inter, hidden)
+    keep = ops.fuse_decode_ffn
+    try:
+        ops.fuse_decode_ffn = False
+        want = res.clone()
+        ops.swiglu_ffn(x, w_gu, down, want)
+        ops.fuse_decode_ffn = True
+        for _ in range(5):
+            got = res.clone()
+            ops.swiglu_ffn(x, w_gu, down, got)
+            assert torch.equal(got, want), "the fused feed-forward differs from the two launches"
+    finally:
+        ops.fuse_decode_ffn = keep
+    assert int(ops._ffn_counters[:2].view(torch.int64).item()) % ops.num_sms == 0, "a block did not arrive"
+    r = RefOps()
+    ref = res.clone()
+    r.swiglu_ffn(x, r.pack_gate_up(gate, up), down, ref)
+    _close(got, ref, 1e-2, f"fused feed-forward m={m} {sizes}")
+    ops.check_status()
+
+
+def _tail_inputs(m, hidden, inter, nq):
+    return dict(
+        attn=_rand((m, nq), torch.bfloat16, seed=6),
+        w_o=_rand((hidden, nq), torch.bfloat16, seed=7, scale=0.05),
+        norm_w=1.0 + 0.1 * _rand((hidden,), torch.float32, seed=8),
+        gate=_rand((inter, hidden), torch.bfloat16, seed=1, scale=0.05),
+        up=_rand((inter, hidden), torch.bfloat16, seed=2, scale=0.05),
+        down=_rand((hidden, inter), torch.bfloat16, seed=3, scale=0.05),
+        res=_rand((m, hidden), torch.float32, seed=5))
+
+
+def _run_tail(o, t, w_gu, eps):
+    """A mixer's last product, the norm and the feed-forward, as a block asks for them."""
+    res = t["res"].clone()
+    o.linear(t["attn"], t["w_o"], res, accumulate=True, may_defer=True)
+    h = torch.empty(res.shape, dtype=torch.bfloat16, device=res.device)
+    o.rmsnorm(res, t["norm_w"], eps, h)
+    o.swiglu_ffn(h, w_gu, t["down"], res)
+    o.flush()
+    return res
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("sizes", [(1024, 3072, 2048), (256, 640, 384), (512, 1536, 512), (1024, 2048, 1024)])
+def test_decode_tail_in_one_launch(ops, m, sizes):
+    """Output projection into the residual, norm of the residual and feed-forward as one launch:
+    the same bits as the four launches (the norm adds its squares in the order of the
+    block-per-row kernel), repeatedly, and the plain formula."""
+    from ref_ops import RefOps
+    hidden, inter, nq = sizes
+    t = _tail_inputs(m, hidden, inter, nq)
+    eps = 1e-5
+    w_gu = ops.pack_gate_up(t["gate"], t["up"])
+    assert ops.bf16.ti_attn_out_ffn_decode_supported(m, hidden, inter, nq, nq, nq, hidden, inter, inter, hidden)
+    keep = ops.fuse_decode_tail, ops.fuse_decode_ffn
+    try:
+        ops.fuse_decode_tail = ops.fuse_decode_ffn = False
+        want = _run_tail(ops, t, w_gu, eps)
+        ops.fuse_decode_ffn = True
+        assert torch.equal(_run_tail(ops, t, w_gu, eps), want), "the fused feed-forward differs"
+        ops.fuse_decode_tail = True
+        before = ops.launches
+        for _ in range(4):
+            got = _run_tail(ops, t, w_gu, eps)
+            assert torch.equal(got, want), "the fused tail differs from the separate launches"
+        assert ops.launches - before == 4, "the tail did not run as one launch"
+    finally:
+        ops.fuse_decode_tail, ops.fuse_decode_ffn = keep
+    r = RefOps()
+    ref = _run_tail(r, t, r.pack_gate_up(t["gate"], t["up"]), eps)
+    _close(got, ref, 1e-2, f"fused tail m={m} {sizes}")
+    ops.check_status()
+
+
+def test_a_held_back_product_is_launched_by_whatever_comes_next(ops):
+    """``linear(..., may_defer=True)`` may be held back; any other operation, ``flush()`` and
+    ``stream()`` launch it, with the norm that was held back behind it."""
+    m, hidden, inter, nq = 4, 256, 640, 384
+    t = _tail_inputs(m, hidden, inter, nq)
+    want = t["res"] + t["attn"].float() @ t["w_o"].float().T
+    for how in ("flush", "stream", "linear", "norm of something else", "norm then linear"):
+        res = t["res"].clone()
+        ops.linear(t["attn"], t["w_o"], res, accumulate=True, may_defer=True)
+        h = torch.empty((m, hidden), dtype=torch.bfloat16, device=DEV)
+        if how == "flush":
+            ops.flush()
+        elif how == "stream":
+            ops.stream()
+        elif how == "linear":
+            other = torch.zeros((m, hidden), device=DEV)
+            ops.linear(t["attn"], t["w_o"], other)
+        elif how == "norm of something else":
+            ops.rmsnorm(t["res"], t["norm_w"], 1e-5, h)
+        else:
+            ops.rmsnorm(res, t["norm_w"], 1e-5, h)                    # held back too
+            other = torch.zeros((m, hidden), device=DEV)
+            ops.linear(t["attn"], t["w_o"], other)                    # launches both, in order
+            x = res.double()
+            normed = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5) * t["norm_w"].double()
+            _close(h, normed, 1e-2, "the held-back norm")
+        assert ops._pending is None
+        _close(res, want, _sum_rtol(nq) * 4, f"held-back product launched by {how}")
+    ops.check_status()
+
+
+def test_decode_feed_forward_falls_back(ops):
+    """More than 16 rows, or weights that do not fit into shared memory, take the two launches."""
+    assert not ops.bf16.ti_ffn_decode_supported(17, 1024, 3072, 1024, 1024, 3072, 3072, 1024)
+    assert not ops.bf16.ti_ffn_decode_supported(8, 4096, 12288, 4096, 4096, 12288, 12288, 4096)
+    assert not ops.bf16.ti_ffn_decode_supported(8, 1000, 3072, 1000, 1000, 3072, 3072, 1000)
+    from ref_ops import RefOps
+    hidden, inter, m = 256, 640, 20
+    gate = _rand((inter, hidden), torch.bfloat16, seed=1, scale=0.05)
+    up = _rand((inter, hidden), torch.bfloat16, seed=2, scale=0.05)
+    down = _rand((hidden, inter), torch.bfloat16, seed=3, scale=0.05)
+    x = _rand((m, hidden), torch.bfloat16, seed=4)
+    res = _rand((m, hidden), torch.float32, seed=5)
+    got = res.clone()
+    ops.swiglu_ffn(x, ops.pack_gate_up(gate, up), down, got)
+    r = RefOps()
+    ref = res.clone()
+    r.swiglu_ffn(x, r.pack_gate_up(gate, up), down, ref)
+    _close(got, ref, 1e-2, "feed-forward of 20 rows")
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [65, 128, 129, 300, 1000])
 @pytest.mark.parametrize("nk", [(128, 64), (136, 72), (4096, 1024), (1024, 3072), (1000, 520), (331, 128)])
 def test_linear_many_rows_bf16(ops, m, nk):

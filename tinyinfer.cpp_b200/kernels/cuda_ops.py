@@ -94,6 +94,15 @@ class CudaOps:
         # larger weights gain 15-50 % on tcgen05)
         self.few_tc_min_bytes = 1 << 25
         self._few_tickets = None
+        # the feed-forward of a decode step of at most 16 rows as one launch, when a layer's
+        # feed-forward weights fit into the GPU's shared memory (csrc/ffn_decode.cu); same bits as
+        # the two products it replaces
+        self.fuse_decode_ffn = True
+        # ... and with the product in front of it that adds to the same residual (a mixer's output
+        # projection, asked for with ``linear(..., may_defer=True)``) and the norm between them
+        self.fuse_decode_tail = True
+        self._ffn_counters = None
+        self._pending = None              # a held-back ``out += a w^T`` (and the norm of ``out`` after it)
         self._retired = []                # outgrown counter buffers that captured graphs may still use
         # rotation kind -> handler(ops, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
         # num_heads, num_kv_heads, head_dim) that norms, rotates and stores the heads of a float32
@@ -129,6 +138,11 @@ class CudaOps:
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_gemm_skinny.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_ffn_decode_supported.argtypes = [_i] * 8
+            b.ti_ffn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp] + [_i] * 8 + [_vp, _vp, _vp]
+            b.ti_attn_out_ffn_decode_supported.argtypes = [_i] * 10
+            b.ti_attn_out_ffn_decode.argtypes = ([_vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp] + [_i] * 10
+                                                 + [_vp, _vp, _vp])
             b.ti_gemm_tcgen05_few_supported.argtypes = [_i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_few_scratch.argtypes = [_i, _i, _i, ctypes.POINTER(ctypes.c_longlong),
                                                       ctypes.POINTER(ctypes.c_int)]
@@ -195,8 +209,11 @@ class CudaOps:
         code = int(self.status.item())
         if code:
             self.status.zero_()
+            if self._ffn_counters is not None:        # a wait that ran out leaves its round incomplete
+                self._ffn_counters.zero_()
             meaning = {1: "a block-table entry named a page outside the pool",
-                       2: "a wait on a shared-memory barrier ran out (a tensor-core kernel gave up "
+                       2: "a bounded wait ran out (on a shared-memory barrier of a tensor-core kernel or "
+                          "on the arrival counter of the fused feed-forward; the kernel gave up "
                           "instead of hanging; its output is not valid)"}.get(code, "unknown code")
             raise KernelError(f"a kernel reported device status {code}: {meaning}")
 
@@ -262,6 +279,14 @@ class CudaOps:
                                     self._stream()))
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
+        p = self._pending
+        if p is not None:
+            if (p.get("norm") is None and rows is None and x is p["out"] and out.dtype == torch.bfloat16
+                    and weight.dtype == torch.float32 and weight.shape[0] == x.shape[1] == out.shape[1]
+                    and x.is_contiguous() and out.is_contiguous() and out.shape[0] == x.shape[0]):
+                p["norm"] = (weight, eps, out)
+                return
+            self.flush()
         _need(x.dtype == torch.float32 and x.is_contiguous(), "rmsnorm: x must be float32")
         _need(weight.dtype == torch.float32 and weight.shape[0] == x.shape[1],
               "rmsnorm: weight must be float32 of the row length")
@@ -274,10 +299,32 @@ class CudaOps:
                                       x.shape[1], float(eps), out.data_ptr(),
                                       _code(out, "rmsnorm"), self._stream()))
 
-    def linear(self, a, w, out, accumulate=False):
-        """out (+)= a @ w.T"""
+    def flush(self) -> None:
+        """Launch what ``linear(..., may_defer=True)`` and a norm after it have held back."""
+        p, self._pending = self._pending, None
+        if p is None:
+            return
+        self.linear(p["a"], p["w"], p["out"], accumulate=True)
+        if p.get("norm") is not None:
+            weight, eps, normed = p["norm"]
+            self.rmsnorm(p["out"], weight, eps, normed)
+
+    def linear(self, a, w, out, accumulate=False, may_defer=False):
+        """out (+)= a @ w.T.  With ``may_defer`` (and ``accumulate``) the kernel set may hold the
+        product back and run it in one launch with a norm of ``out`` and a feed-forward into ``out``
+        that follow immediately; any other operation of the kernel set, ``stream()`` and
+        ``flush()`` launch it first.  The caller must not touch ``a`` or ``out`` by other means
+        until then."""
+        if self._pending is not None:
+            self.flush()
         m, k = a.shape
         n = w.shape[0]
+        if (may_defer and accumulate and self.fuse_decode_tail and self.fuse_decode_ffn and m <= 16 and n <= 1024
+                and a.dtype == w.dtype == torch.bfloat16 and out.dtype == torch.float32
+                and w.shape[1] == k and tuple(out.shape) == (m, n)
+                and a.stride(1) == w.stride(1) == out.stride(1) == 1):
+            self._pending = {"a": a, "w": w, "out": out}
+            return
         _need(w.shape[1] == k and tuple(out.shape) == (m, n), "linear: shapes do not agree")
         _need(out.dtype == torch.float32, "linear: out must be float32")
         _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
@@ -331,6 +378,52 @@ class CudaOps:
         self.linear(h, w_gate_up, gu)
         self._ok(self.core.ti_swiglu(gu.data_ptr(), m, inter, int(interleaved), out.data_ptr(),
                                      _code(out, "swiglu"), self._stream()))
+
+    def swiglu_ffn(self, h, w_gate_up, w_down, residual):
+        """residual += (silu(h Wgate^T) * (h Wup^T)) Wdown^T, with ``w_gate_up`` from pack_gate_up."""
+        m, k = h.shape
+        inter = w_down.shape[1]
+        _need(w_gate_up.shape == (2 * inter, k) and w_down.shape[0] == residual.shape[1] == k
+              and residual.shape[0] == m, "swiglu_ffn: shapes do not agree")
+        y = torch.empty((m, inter), dtype=h.dtype, device=h.device)
+        p = self._pending
+        if p is not None:
+            norm = p.get("norm")
+            a, w_o = p["a"], p["w"]
+            if (norm is not None and h is norm[2] and residual is p["out"]
+                    and bool(getattr(w_gate_up, "_ti_interleaved", False))
+                    and w_gate_up.dtype == w_down.dtype == torch.bfloat16
+                    and w_gate_up.stride(1) == w_down.stride(1) == 1
+                    and self.bf16.ti_attn_out_ffn_decode_supported(
+                        m, k, inter, a.shape[1], a.stride(0), w_o.stride(0), w_gate_up.stride(0),
+                        w_down.stride(0), y.stride(0), residual.stride(0))):
+                self._pending = None
+                if self._ffn_counters is None:
+                    self._ffn_counters = self._grown(None, 4, h.device)
+                self._ok(self.bf16.ti_attn_out_ffn_decode(
+                    a.data_ptr(), w_o.data_ptr(), norm[0].data_ptr(), float(norm[1]), w_gate_up.data_ptr(),
+                    w_down.data_ptr(), y.data_ptr(), residual.data_ptr(), m, k, inter, a.shape[1],
+                    a.stride(0), w_o.stride(0), w_gate_up.stride(0), w_down.stride(0), y.stride(0),
+                    residual.stride(0), self._ffn_counters.data_ptr(), self.status.data_ptr(),
+                    self._stream()), self.bf16)
+                return
+            self.flush()
+        if (self.fuse_decode_ffn and m <= 16 and bool(getattr(w_gate_up, "_ti_interleaved", False))
+                and h.dtype == w_gate_up.dtype == w_down.dtype == torch.bfloat16
+                and residual.dtype == torch.float32
+                and h.stride(1) == w_gate_up.stride(1) == w_down.stride(1) == residual.stride(1) == 1
+                and self.bf16.ti_ffn_decode_supported(m, k, inter, h.stride(0), w_gate_up.stride(0),
+                                                      w_down.stride(0), y.stride(0), residual.stride(0))):
+            if self._ffn_counters is None:
+                self._ffn_counters = self._grown(None, 4, h.device)
+            self._ok(self.bf16.ti_ffn_decode(
+                h.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), y.data_ptr(), residual.data_ptr(),
+                m, k, inter, h.stride(0), w_gate_up.stride(0), w_down.stride(0), y.stride(0),
+                residual.stride(0), self._ffn_counters.data_ptr(), self.status.data_ptr(),
+                self._stream()), self.bf16)
+            return
+        self.gate_up_swiglu(h, w_gate_up, y)
+        self.linear(y, w_down, residual, accumulate=True)
 
     # ---- attention -----------------------------------------------------------------------
     def register_rotation(self, kind: str, handler) -> None:
@@ -569,3 +662,22 @@ class CudaOps:
         self._ok(self.core.ti_sample(logits.data_ptr(), rows, logits.shape[1],
                                      temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
                                      uniform.data_ptr(), out.data_ptr(), self._stream()))
+
+
+def _flush_first(fn):
+    """Other operations launch what ``linear(..., may_defer=True)`` has held back before they run."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(self, *args, **kwargs):
+        if self._pending is not None:
+            self.flush()
+        return fn(self, *args, **kwargs)
+    return wrapper
+
+
+for _name, _fn in list(vars(CudaOps).items()):
+    if (isinstance(_fn, type(_flush_first)) and not _name.startswith("_")
+            and _name not in ("flush", "linear", "rmsnorm", "swiglu_ffn")):
+        setattr(CudaOps, _name, _flush_first(_fn))
+del _name, _fn

@@ -73,7 +73,7 @@ class Attention(Part):
         ops.qkv_attention(h, self.w_qkv, self.q_norm, self.k_norm, self.eps, self.position.rotation(dev),
                           step, cache, out, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.window, self.scale)
-        ops.linear(out, self.w_o, residual, accumulate=True)
+        ops.linear(out, self.w_o, residual, accumulate=True, may_defer=True)
 
 
 register_part("mixer", "attention", Attention)

@@ -35,9 +35,7 @@ class SwiGLU(Part):
         self.w_down = ops.pack_linear(tensors["down_proj.weight"])
 
     def forward(self, ops, h, residual, step):
-        y = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        ops.gate_up_swiglu(h, self.w_gate_up, y)
-        ops.linear(y, self.w_down, residual, accumulate=True)
+        ops.swiglu_ffn(h, self.w_gate_up, self.w_down, residual)
 
 
 register_part("ffn", "swiglu", SwiGLU)

@@ -95,6 +95,7 @@ class CausalLM:
         for entry in self.plan.schedule:
             cache = cache_views[(entry.cache_slot, entry.writes_cache)]
             self.blocks[entry.layer].forward(ops, x, step, cache)
+        ops.flush()                        # nothing a part asked for may still be held back
         if step.num_logit_rows == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=x.device)
         h = self.final_norm.forward_rows(ops, x, step.logit_rows, step.act_dtype)
