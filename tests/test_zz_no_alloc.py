@@ -95,7 +95,12 @@ def test_no_alloc_entry_point_matches_twice_and_refuses_too_much():
     # a second call of another shape reuses the array and what the first call left in it
     second = _run_both(lib, 2, heads=8, kv_heads=2, hd=64, page=32,
                        contexts=[300, 17, 65], splits=4, window=40)
+    # one split: the block writes the result itself (no partial result goes through memory)
+    # where ti_attn_decode, without counters, still writes one and merges it in a second launch
+    third = _run_both(lib, 4, heads=16, kv_heads=8, hd=128, page=64,
+                      contexts=[1, 33, 500, 1025, 64], splits=1, window=0)
     assert torch.isfinite(first.float()).all() and torch.isfinite(second.float()).all()
+    assert torch.isfinite(third.float()).all()
     # 64 rows x 64 heads x 64 splits x (128 + 2) floats is far more than 8 MiB
     q, positions, req, table, pages = _case(3, 64, 8, 128, 16, [40] * 64)
     out = torch.zeros_like(q)

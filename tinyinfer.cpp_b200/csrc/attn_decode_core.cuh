@@ -381,6 +381,23 @@ __device__ __forceinline__ void decode_item(
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
+    if (num_splits == 1 && counters != nullptr) {
+        // One block has all keys of the row: what the merge would make of its single partial
+        // result (weight 2^0, the sum's reciprocal) is computed here, without the round trip
+        // through global memory, the fence and the ticket.
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int head = g + 8 * r;
+            if (head >= group) continue;
+            const float inv = 1.0f / l_run[r];
+            bf16* dst = out + ((size_t)t * num_heads + (size_t)kvh * group + head) * HD;
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i)
+                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + tq * 2) =
+                    __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int head = g + 8 * r;
