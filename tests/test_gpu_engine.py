@@ -55,7 +55,7 @@ def test_decoding_with_every_few_rows_product_on_the_split_k_kernel(tmp_path_fac
     ref = plain_forward(cfg, w, toks, emulate_bf16=True)
     ref_other = plain_forward(cfg, w, other, emulate_bf16=True)
     eng = _engine(d, "bfloat16")
-    keep = eng.ops.few_tc_min_bytes                  # the kernel set is shared by every engine of the device
+    keep = eng.ops.few_tc_min_bytes                  # (the engine has a kernel set of its own)
     eng.ops.few_tc_min_bytes = 0
     before = eng.ops.launches
     try:

@@ -59,8 +59,9 @@ class Engine:
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         if ops is None:
-            from ..kernels import cuda_ops
-            ops = cuda_ops(self.device)
+            # a kernel set of its own: its switches and what it holds back belong to this engine
+            from ..kernels import CudaOps
+            ops = CudaOps(self.device)
         self.ops = ops
         gguf_file = None
         if model_dir is not None and os.path.isfile(model_dir):

@@ -6,7 +6,9 @@ _OPS: dict[str, CudaOps] = {}
 
 
 def cuda_ops(device) -> CudaOps:
-    """The kernel set for ``device``; raises if CUDA or the compiled library is missing."""
+    """A kernel set for ``device`` that callers share (tests of single kernels, tools); an engine
+    makes its own ``CudaOps``, so that its switches are its own.  Raises if CUDA or the compiled
+    library is missing."""
     key = str(device)
     if key not in _OPS:
         _OPS[key] = CudaOps(device)

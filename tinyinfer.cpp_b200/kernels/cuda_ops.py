@@ -107,7 +107,7 @@ class CudaOps:
         # rotation kind -> handler(ops, qkv, q_weight, k_weight, eps, rotation, step, cache, q_out,
         # num_heads, num_kv_heads, head_dim) that norms, rotates and stores the heads of a float32
         # product; "neox" and "none" run on the kernels of csrc/, others are brought by parts
-        self._rotations = {"neox": CudaOps._rotate_builtin, "none": CudaOps._rotate_builtin}
+        self._rotations = CudaOps._ROTATIONS          # kinds are known to every kernel set
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # kernels launched so far: entry points called eagerly, plus, for every graph replay,
@@ -427,7 +427,8 @@ class CudaOps:
 
     # ---- attention -----------------------------------------------------------------------
     def register_rotation(self, kind: str, handler) -> None:
-        """Teach the kernel set a rotation kind of a position part: ``handler(ops, qkv, q_weight,
+        """Teach the kernel sets (all of them: the table belongs to the class) a rotation kind of a
+        position part: ``handler(ops, qkv, q_weight,
         k_weight, eps, rotation, step, cache, q_out, num_heads, num_kv_heads, head_dim)`` gets the
         float32 QKV product and does what ``qk_norm_rope_store`` does for the built-in kinds."""
         self._rotations[kind] = handler
@@ -662,6 +663,9 @@ class CudaOps:
         self._ok(self.core.ti_sample(logits.data_ptr(), rows, logits.shape[1],
                                      temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
                                      uniform.data_ptr(), out.data_ptr(), self._stream()))
+
+
+CudaOps._ROTATIONS = {"neox": CudaOps._rotate_builtin, "none": CudaOps._rotate_builtin}
 
 
 def _flush_first(fn):
