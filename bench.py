@@ -442,7 +442,10 @@ def reference_gguf(cfg, seed, path):
     arch = architecture_of(cfg)
     typed = arch.from_dict(cfg)
     model = CausalLM(arch.build_plan(typed))
-    tensors = {gguf_tensor_name(n): random_tensor(seed, n, spec) for n, spec in model.expected_tensors().items()}
+    # drawn on the GPU when there is one (the generator gives the same bits there, much sooner)
+    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+    tensors = {gguf_tensor_name(n): random_tensor(seed, n, spec, device=dev).cpu()
+               for n, spec in model.expected_tensors().items()}
     meta = gguf_metadata(Qwen3Config.from_dict(cfg))
     letters = [chr(ord("a") + i) for i in range(26)]
     meta["tokenizer.ggml.tokens"] = letters

@@ -312,3 +312,26 @@ def test_command_line(tmp_path_factory):
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "tinyinfer"), "-m", d],
                          capture_output=True, text=True, timeout=120)
     assert bad.returncode == 1 and "usage" in bad.stderr
+
+
+def test_engine_from_configuration_and_seed_equals_the_written_model(tmp_path):
+    """Random weights are a function of (seed, tensor name, element): drawn on the GPU they have
+    the bits of the folder written on the host, so the two engines give the same logits."""
+    from tinyinfer_b200 import Engine, StepEntry, write_random_model
+    from tinyinfer_b200.parts.base import MATRIX, WeightSpec
+    from tinyinfer_b200.weights.random_init import random_tensor
+    from util import TINY, random_tokens
+    spec = WeightSpec((300, 70), MATRIX)
+    host = random_tensor(11, "some.weight", spec, dtype=torch.float32)
+    assert torch.equal(host, random_tensor(11, "some.weight", spec, device="cuda:0", dtype=torch.float32).cpu())
+    cfg = TINY["D"]
+    folder = str(tmp_path / "written")
+    write_random_model(folder, cfg, seed=21)
+    toks = random_tokens(cfg["vocab_size"], 40, seed=2)
+    for dtype in ("float32", "bfloat16"):
+        a = Engine(folder, dtype=dtype, max_tokens=256, max_requests=2)
+        b = Engine(config=cfg, seed=21, dtype=dtype, max_tokens=256, max_requests=2)
+        la = a.step([StepEntry("r", toks, list(range(40)))])
+        lb = b.step([StepEntry("r", toks, list(range(40)))])
+        assert torch.equal(la, lb), f"{dtype}: weights drawn on the device differ from the written ones"
+        a.ops.check_status()

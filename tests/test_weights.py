@@ -153,3 +153,26 @@ def test_no_safetensors_file(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(TINY_A))
     with pytest.raises(SafetensorsError, match="no .safetensors"):
         load_model_weights(_model(TINY_A), str(tmp_path), "cpu", RefOps())
+
+
+def test_random_weights_are_a_function_of_seed_name_and_index():
+    """The generator is counter-based: pieces of a stream equal the stream, a tensor does not
+    depend on the others, and the values are close to a normal distribution."""
+    from tinyinfer_b200.parts.base import MATRIX, NORM_WEIGHT, WeightSpec
+    from tinyinfer_b200.weights.random_init import random_tensor, standard_normal
+    whole = standard_normal(99, 0, 5000)
+    assert torch.equal(standard_normal(99, 1234, 700), whole[1234:1934])
+    assert not torch.equal(standard_normal(98, 0, 5000), whole)
+    big = standard_normal(7, 0, 1 << 20)
+    assert abs(big.mean().item()) < 5e-3 and abs(big.std().item() - 1.0) < 5e-3
+    assert 2.8 < (big ** 4).mean().item() < 3.1 and big.abs().max().item() <= 6.0
+    spec = WeightSpec((33, 17), MATRIX)
+    a = random_tensor(5, "x.weight", spec)
+    assert a.dtype == torch.bfloat16 and tuple(a.shape) == (33, 17)
+    assert torch.equal(a, random_tensor(5, "x.weight", spec))
+    assert not torch.equal(a, random_tensor(5, "y.weight", spec))
+    assert not torch.equal(a, random_tensor(6, "x.weight", spec))
+    # the bfloat16 tensor is the rounded float32 draw
+    assert torch.equal(a, random_tensor(5, "x.weight", spec, dtype=torch.float32).to(torch.bfloat16))
+    n = random_tensor(5, "n.weight", WeightSpec((64,), NORM_WEIGHT))
+    assert n.dtype == torch.float32 and abs(n.mean().item() - 1.0) < 0.02

@@ -20,7 +20,10 @@
 // reset (a reset would put one more round trip to L2 on the step's critical path): a launch waits
 // for the next multiple of the grid size.  The wait is bounded; when it runs out the block
 // records status 2 and returns.  All blocks are resident at once by construction: the grid has
-// one block per SM, and a block's shared memory admits one block per SM.
+// one block per SM, and a block's shared memory admits one block per SM.  (Two launches of this
+// kernel that run at the same time on different streams could each hold a part of the SMs and
+// wait for the rest; their waits then run out and both report status 2.  An engine launches on
+// one stream; who steps several engines concurrently on one GPU turns this kernel off.)
 #include "sm100.cuh"
 
 namespace {
