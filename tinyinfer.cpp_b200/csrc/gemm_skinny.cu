@@ -91,6 +91,19 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
             }
         }
     }
+    // What this thread will add to, requested now: the reads return while the partial sums are
+    // exchanged (read one by one between the stores below, each would wait a round trip to L2).
+    constexpr int OUT_STEP = WARPS * 32 / ROWS;                 // tokens a pass of the block covers
+    float old_c[8 * NT / OUT_STEP > 0 ? 8 * NT / OUT_STEP : 1];
+    if (mode == MODE_ACCUMULATE) {
+        if (chunks <= warp) pdl_wait();
+        const int i = threadIdx.x % ROWS;
+#pragma unroll
+        for (int it = 0; it < (int)(sizeof(old_c) / sizeof(float)); ++it) {
+            const int tok = threadIdx.x / ROWS + it * OUT_STEP;
+            old_c[it] = tok < m && n0 + i < n ? __ldcg(c + (size_t)tok * ldc + n0 + i) : 0.0f;
+        }
+    }
     // acc[j]: [0],[1] = W row g, tokens 8j + 2tq (+1); [2],[3] = W row g + 8
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -121,14 +134,14 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
         }
     } else {
         const int i = threadIdx.x % ROWS;
-        for (int tok = threadIdx.x / ROWS; tok < m; tok += WARPS * 32 / ROWS) {
+#pragma unroll
+        for (int it = 0; it < (int)(sizeof(old_c) / sizeof(float)); ++it) {
+            const int tok = threadIdx.x / ROWS + it * OUT_STEP;
+            if (tok >= m) break;
             float sum = 0.0f;
 #pragma unroll
             for (int wp = 0; wp < WARPS; ++wp) sum += part[wp][i][tok];
-            if (n0 + i < n) {
-                float* p = c + (size_t)tok * ldc + n0 + i;
-                *p = mode == MODE_ACCUMULATE ? *p + sum : sum;
-            }
+            if (n0 + i < n) c[(size_t)tok * ldc + n0 + i] = mode == MODE_ACCUMULATE ? old_c[it] + sum : sum;
         }
     }
 }

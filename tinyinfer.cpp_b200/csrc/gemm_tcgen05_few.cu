@@ -71,12 +71,19 @@ __device__ __forceinline__ void finish16(const float (&v)[16], int tok0, int n_r
             }
         }
     } else if (n_row < n) {
+        // When adding to C, all old values are requested before the first sum is stored: written
+        // one after the other, every read would wait behind the store before it (the compiler
+        // cannot tell that the addresses differ), a round trip to L2 per row (the down projection
+        // of the 8B shape at 64 rows: 55 -> 34 microseconds).
+        float old[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            old[i] = mode == MODE_ACCUMULATE && tok0 + i < m ? __ldcg(c + (size_t)(tok0 + i) * ldc + n_row) : 0.0f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int tok = tok0 + i;
             if (tok >= m) break;
-            float* p = c + (size_t)tok * ldc + n_row;
-            *p = mode == MODE_ACCUMULATE ? *p + v[i] : v[i];
+            c[(size_t)tok * ldc + n_row] = old[i] + v[i];
         }
     }
 }
