@@ -104,6 +104,27 @@ def test_prompt_of_2048_tokens_in_one_step(page_size):
     bf.ops.check_status()
 
 
+def test_long_prompt_with_two_heads_per_attention_block():
+    """Prompts with several (head, tile) pairs per SM take the attention kernel that walks the keys
+    once for two heads of a kv group; here a 2,048-token prompt is sent through it (forced) in two
+    portions, the second one seeing the first through the cache, eagerly and from the graph."""
+    from tinyinfer_b200 import StepEntry
+    bf, fp = _engines(2 * 2048, 2, step_graphs=True)
+    bf.ops.tc_attention_pairs_from = 0
+    want_at = [0, 5, 127, 128, 700, 1023]
+    before = bf.ops.launches
+    for i in range(3):
+        toks = _tokens(2048, seed=60 + i)
+        for part in (toks[:1024], toks[1024:]):
+            want = fp.step([StepEntry("p", part, want_at)])
+            got = bf.step([StepEntry("p", part, want_at)]).clone()
+            _check(got, want, f"2,048-token prompt in two portions, two heads per block, pass {i}")
+        fp.finish("p")
+        bf.finish("p")
+    assert bf.ops.launches > before
+    bf.ops.check_status()
+
+
 @pytest.mark.parametrize("batch", [8, 64])
 def test_batches_decoding_after_computed_prompts(batch):
     """Batch 8 and 64: prompts of 600 to 900 tokens run through the engine (several requests

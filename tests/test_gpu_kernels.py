@@ -447,6 +447,18 @@ def test_prompt_attention_on_tcgen05_matches_the_mma_kernel_and_the_plain_statem
     RefOps().paged_attention(q, step, cache, ref, heads, kv, hd, window, scale)
     _close(mma, ref, 1.5e-2, f"mma attention {geom} window={window}")
     _close(got, ref, 1.5e-2, f"tcgen05 attention {geom} window={window}")
+    # the kernel with two heads of a kv group per block (for long prompts), forced on this case
+    if ops.bf16.ti_attn_prefill_tc2_supported(hd, ps, heads, kv):
+        keep = ops.tc_attention_pairs_from
+        ops.tc_attention_pairs_from = 0
+        try:
+            pairs = torch.zeros_like(q)
+            before = ops.launches
+            ops.paged_attention(q, step, cache, pairs, heads, kv, hd, window, scale)
+            ops.check_status()
+        finally:
+            ops.tc_attention_pairs_from = keep
+        _close(pairs, ref, 1.5e-2, f"tcgen05 attention, two heads per block {geom} window={window}")
 
 
 def test_decode_attention_finds_a_far_key(ops):

@@ -24,7 +24,8 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 LIBRARIES = {
     "core": ["common.cu", "rowwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
     "bf16": ["common.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2sm.cu",
-             "gemm_tcgen05_few.cu", "ffn_decode.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],
+             "gemm_tcgen05_few.cu", "ffn_decode.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu",
+             "attn_prefill_tc2.cu"],
 }
 
 # libraries that parts bring themselves: name -> (absolute source paths, include folders)

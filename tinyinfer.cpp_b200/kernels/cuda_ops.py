@@ -94,6 +94,9 @@ class CudaOps:
         # larger weights gain 15-50 % on tcgen05)
         self.few_tc_min_bytes = 1 << 25
         self._few_tickets = None
+        # prompt attention with two heads per block (csrc/attn_prefill_tc2.cu) from this many
+        # (head, tile) pairs per SM on (None: never)
+        self.tc_attention_pairs_from = 3
         # the feed-forward of a decode step of at most 16 rows as one launch, when a layer's
         # feed-forward weights fit into the GPU's shared memory (csrc/ffn_decode.cu); same bits as
         # the two products it replaces
@@ -169,6 +172,8 @@ class CudaOps:
             b.ti_attn_prefill_tc_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_prefill_tc.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                              _f, _vp, _vp, _vp]
+            b.ti_attn_prefill_tc2_supported.argtypes = [_i, _i, _i, _i]
+            b.ti_attn_prefill_tc2.argtypes = b.ti_attn_prefill_tc.argtypes
             self._tile_rows = (int(b.ti_attn_prefill_tile_rows()), int(b.ti_attn_prefill_tc_tile_rows()))
             self._bf16 = b
         return self._bf16
@@ -616,7 +621,13 @@ class CudaOps:
             if self.use_tc_attention and self.bf16.ti_attn_prefill_tc_supported(
                     head_dim, cache.page_size, num_heads, num_kv_heads):
                 tiles = lists[f"portion_tiles_{big}"]
-                self._ok(self.bf16.ti_attn_prefill_tc(
+                # many tiles per SM: the kernel that takes two heads of a kv group per block
+                two = (self.tc_attention_pairs_from is not None
+                       and tiles.shape[0] * num_heads >= self.tc_attention_pairs_from * self.num_sms
+                       and self.bf16.ti_attn_prefill_tc2_supported(head_dim, cache.page_size, num_heads,
+                                                                   num_kv_heads))
+                kernel = self.bf16.ti_attn_prefill_tc2 if two else self.bf16.ti_attn_prefill_tc
+                self._ok(kernel(
                     q.data_ptr(), q.shape[0], tiles.data_ptr(), tiles.shape[0],
                     step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
                     pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
