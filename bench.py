@@ -551,6 +551,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the other shapes")
     ap.add_argument("--no-shapes", action="store_true", help="skip the 8B and 32B shapes and the page-16 run")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per cache page")
+    ap.add_argument("--prefill-tokens", type=int, default=2048,
+                    help="with --only prefill: the length of the prompt (the default run's is 2,048)")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
@@ -574,8 +576,9 @@ def main() -> int:
     pk, pk_kind = peaks()
     nums = model_numbers(cfg)
     max_batch = max(args.batch, 1 if (args.no_points or args.only not in (None, "mixed")) else 64)
-    llm = LLM(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size, max_seq=args.context,
-              max_num_seqs=max_batch + 1, kv_tokens=max_batch * args.context, cuda_graph=True)
+    longest = max(args.context, args.prefill_tokens + args.page_size if args.only == "prefill" else 0)
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size, max_seq=longest,
+              max_num_seqs=max_batch + 1, kv_tokens=max(max_batch * args.context, longest), cuda_graph=True)
     engine = llm.engine
 
     if args.only == "decode":
@@ -592,8 +595,8 @@ def main() -> int:
         print(json.dumps({"only": "mixed", "decoding": 63, "portion": 512, "ms": round(mx_ms, 3)}))
         return 0
     if args.only == "prefill":
-        pf_ms = measure_prefill(engine, 2048, max(1, args.steps), torch)
-        print(json.dumps({"only": "prefill", "tokens": 2048, "ms": round(pf_ms, 3)}))
+        pf_ms = measure_prefill(engine, args.prefill_tokens, max(1, min(args.steps, 8)), torch)
+        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "ms": round(pf_ms, 3)}))
         return 0
     ms, clocks, launches = measure_decode(engine, args.batch, args.context, args.steps, warmup, torch)
     e2e_ms, h2d, d2h = decode_e2e(llm, args.batch, args.context, args.steps, warmup, torch)
