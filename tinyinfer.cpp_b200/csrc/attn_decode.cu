@@ -22,7 +22,7 @@ namespace {
 
 using namespace attn_decode_core;
 
-template <int HD>
+template <int HD, bool SINGLE>
 __global__ void __launch_bounds__(32)
 attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
                    const int* __restrict__ positions, const int* __restrict__ req_of_tok,
@@ -36,7 +36,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
     const int kvh = blockIdx.y, row = blockIdx.z;
     const int t = rows ? rows[row] : row;
     const int group = num_heads / num_kv_heads;
-    decode_item<HD, true>(smem, q + ((size_t)t * num_heads + (size_t)kvh * group) * HD, nullptr, nullptr,
+    decode_item<HD, true, NoPrologue, SINGLE>(smem, q + ((size_t)t * num_heads + (size_t)kvh * group) * HD, nullptr, nullptr,
                           blockIdx.x, gridDim.x, kvh, row, t, positions[t],
                           block_table + (size_t)req_of_tok[t] * bt_stride, pages, num_pages, page_size,
                           num_heads, num_kv_heads, window, scale_log2, part_o, part_ml, counters, out,
@@ -200,15 +200,22 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
     constexpr int SMEM = STAGES * 2 * TILE * (HD * 2 + 16);
     static TiPerDevice configured;
     if (configured.first_use()) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_decode_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return ti_fail("attn_decode: %s", cudaGetErrorString(e));
         configured.mark();
     }
     dim3 grid(num_splits, num_kv_heads, num_rows);
-    ti_launch_pdl(attn_decode_kernel<HD>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,
-                  block_table, bt_stride, pages, num_pages, page_size, num_heads, num_kv_heads, window,
-                  scale * LOG2E, part_o, part_ml, counters, out, status);
+    if (num_splits == 1 && counters != nullptr)      // nothing to merge: the kernel without that code
+        ti_launch_pdl(attn_decode_kernel<HD, true>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,
+                      block_table, bt_stride, pages, num_pages, page_size, num_heads, num_kv_heads, window,
+                      scale * LOG2E, part_o, part_ml, counters, out, status);
+    else
+        ti_launch_pdl(attn_decode_kernel<HD, false>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,
+                      block_table, bt_stride, pages, num_pages, page_size, num_heads, num_kv_heads, window,
+                      scale * LOG2E, part_o, part_ml, counters, out, status);
     if (int rc = ti_check_launch("attn_decode")) return rc;
     if (counters) return 0;
     attn_decode_merge_kernel<<<(num_rows * num_heads + 3) / 4, 128, 0, s>>>(

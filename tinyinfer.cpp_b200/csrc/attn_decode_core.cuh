@@ -54,9 +54,10 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // out[:] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s, by one warp, over the splits
 // in ascending order, for H heads at once (1 or 2).  Other blocks of the same launch wrote the
 // partial results, so every load is a round trip to L2, and the merge is the exposed tail of the
-// kernel: all (m, l) pairs and the first eight partial outputs of every head are requested
-// together, before anything is computed (one round trip instead of two per head).  `wbuf` holds
-// H * MAX_SPLITS floats of shared memory.
+// kernel: all (m, l) pairs and the first sixteen partial outputs of every head are requested
+// together, before anything is computed, and further splits sixteen at a time for all heads at
+// once (a round trip per sixteen splits, not per eight and head: 64 splits of two heads took 14
+// round trips after the first, now 3).  `wbuf` holds H * MAX_SPLITS floats of shared memory.
 template <int H>
 __device__ __forceinline__ void merge_heads(const float* part_o, const float* part_ml, const size_t (&base)[H],
                                             int num_splits, int head_dim, bf16* const (&out)[H], int lane,
@@ -64,12 +65,13 @@ __device__ __forceinline__ void merge_heads(const float* part_o, const float* pa
     constexpr int PER_LANE = MAX_SPLITS / 32;                 // (m, l) pairs a lane holds per head
     const int d0 = lane * 4;                                  // dims lane*4 .. lane*4 + 3
     const bool has_dims = d0 < head_dim;
-    float4 v[H][8];
+    constexpr int W = 16;                                     // splits per round
+    float4 v[H][W];
     float2 ml[H][PER_LANE];
 #pragma unroll
     for (int h = 0; h < H; ++h) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < W; ++u)
             if (has_dims && u < num_splits)
                 v[h][u] = __ldcg(reinterpret_cast<const float4*>(part_o + (base[h] + u) * head_dim + d0));
 #pragma unroll
@@ -100,29 +102,37 @@ __device__ __forceinline__ void merge_heads(const float* part_o, const float* pa
     }
     __syncwarp();
     if (has_dims) {
+        float acc[H][4];
 #pragma unroll
-        for (int h = 0; h < H; ++h) {
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const float* src = part_o + base[h] * head_dim + d0;
-            const float* wgts = wbuf + h * MAX_SPLITS;
-            for (int s = 0; s < num_splits; s += 8) {
-                if (s > 0) {                                      // the next eight, again all at once
+        for (int h = 0; h < H; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.0f;
+        for (int s = 0; s < num_splits; s += W) {
+            if (s > 0) {                                          // the next sixteen of every head, all at once
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
+                for (int h = 0; h < H; ++h) {
+                    const float* src = part_o + base[h] * head_dim + d0;
+#pragma unroll
+                    for (int u = 0; u < W; ++u)
                         if (s + u < num_splits)
                             v[h][u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s + u) * head_dim));
                 }
+            }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+            for (int h = 0; h < H; ++h) {
+                const float* wgts = wbuf + h * MAX_SPLITS;
+#pragma unroll
+                for (int u = 0; u < W; ++u) {
                     if (s + u >= num_splits) break;
                     const float wgt = wgts[s + u];
-                    acc[0] = fmaf(v[h][u].x, wgt, acc[0]); acc[1] = fmaf(v[h][u].y, wgt, acc[1]);
-                    acc[2] = fmaf(v[h][u].z, wgt, acc[2]); acc[3] = fmaf(v[h][u].w, wgt, acc[3]);
+                    acc[h][0] = fmaf(v[h][u].x, wgt, acc[h][0]); acc[h][1] = fmaf(v[h][u].y, wgt, acc[h][1]);
+                    acc[h][2] = fmaf(v[h][u].z, wgt, acc[h][2]); acc[h][3] = fmaf(v[h][u].w, wgt, acc[h][3]);
                 }
             }
+        }
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
             const float inv = 1.0f / total[h];
-            *reinterpret_cast<__nv_bfloat162*>(out[h] + d0) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-            *reinterpret_cast<__nv_bfloat162*>(out[h] + d0 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(out[h] + d0) = __floats2bfloat162_rn(acc[h][0] * inv, acc[h][1] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(out[h] + d0 + 2) = __floats2bfloat162_rn(acc[h][2] * inv, acc[h][3] * inv);
         }
     }
     __syncwarp();                                             // wbuf may be reused for the next heads
@@ -173,7 +183,9 @@ struct NoPrologue {
 // `prologue()` runs once, by the whole warp, right after the wait for the kernel before and before
 // the queries (and `new_k`, `new_v`) are read: a caller whose queries come out of that kernel
 // unnormed prepares them there.
-template <int HD, bool PDL, class Prologue = NoPrologue>
+// SINGLE: the caller knows that the row's keys are not split (num_splits == 1 and counters given):
+// the code of the merge is then left out, and its registers do not weigh on the key loop.
+template <int HD, bool PDL, class Prologue = NoPrologue, bool SINGLE = false>
 __device__ __forceinline__ void decode_item(
         unsigned char* smem, const bf16* qbase, const bf16* new_k, const bf16* new_v,
         int split, int num_splits, int kvh, int row, int t, int pos,
@@ -381,7 +393,7 @@ __device__ __forceinline__ void decode_item(
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
-    if (num_splits == 1 && counters != nullptr) {
+    if (SINGLE || (num_splits == 1 && counters != nullptr)) {
         // One block has all keys of the row: what the merge would make of its single partial
         // result (weight 2^0, the sum's reciprocal) is computed here, without the round trip
         // through global memory, the fence and the ticket.
@@ -398,6 +410,7 @@ __device__ __forceinline__ void decode_item(
         }
         return;
     }
+    if constexpr (!SINGLE) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int head = g + 8 * r;
@@ -440,6 +453,7 @@ __device__ __forceinline__ void decode_item(
         bf16* const dst[1] = {out + ((size_t)t * num_heads + h) * HD};
         merge_heads<1>(part_o, part_ml, base, active, HD, dst, lane, wbuf);
     }
+    }   // not SINGLE
 }
 
 }  // namespace attn_decode_core
