@@ -659,6 +659,45 @@ def test_sample_matches_sorted_statement(ops):
                for i, (k, o) in enumerate(zip(top_k.tolist(), out.tolist())) if temp[i] > 0)
 
 
+@pytest.mark.parametrize("vocab", [151936, 5000, 700])
+def test_sample_ways_agree_with_the_sorted_statement(ops, vocab):
+    """Every way through the sampling kernel against the sorted statement: few survivors (listed
+    in shared memory), top-p alone on a peaked and on a flat row, more survivors than the list
+    holds (a large k, ties at the k-th place), and no filter at all."""
+    g = torch.Generator(device=DEV).manual_seed(vocab)
+    cases = []                                   # (logits row, k, p)
+    peaked = torch.randn(vocab, generator=g, device=DEV) * 4.0
+    flat = torch.randn(vocab, generator=g, device=DEV) * 0.01
+    tied = peaked.clone()
+    tied[torch.randperm(vocab, generator=torch.Generator().manual_seed(1))[:min(vocab, 3000)].to(DEV)] = 7.5
+    for k, p in ((40, 0.9), (1, 1.0), (5, 0.5), (1000, 0.95), (0, 0.9), (0, 0.5), (0, 1.0), (3000, 0.9),
+                 (vocab - 1, 0.99)):
+        cases.append((peaked, k, p))
+    cases += [(flat, 0, 0.9), (flat, 50, 0.3), (tied, 10, 0.9), (tied, 10, 1.0), (tied, 0, 0.999)]
+    rows = len(cases) * 3
+    logits = torch.stack([c[0] for c in cases] * 3)
+    top_k = torch.tensor([c[1] for c in cases] * 3, dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([c[2] for c in cases] * 3, device=DEV)
+    temp = torch.tensor([0.8] * len(cases) + [1.0] * len(cases) + [0.3] * len(cases), device=DEV)
+    u = torch.rand(rows, generator=torch.Generator().manual_seed(3)).to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ref = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, top_k, top_p, u, out)
+    again = torch.empty_like(out)
+    ops.sample(logits, temp, top_k, top_p, u, again)
+    assert torch.equal(out, again), "two runs of the sampler differ"
+    RefOps().sample(logits, temp, top_k, top_p, u, ref)
+    wrong = [(i, int(o), int(r)) for i, (o, r) in enumerate(zip(out.tolist(), ref.tolist())) if o != r]
+    # float32 sums against float64 ones: a row may differ where u * total meets a boundary, not often
+    assert len(wrong) <= max(1, rows // 20), f"rows that differ from the sorted statement: {wrong}"
+    for i, o, r in wrong:                        # ... and then the two tokens are neighbours among the kept ones
+        x = logits[i].double()
+        kept = torch.exp((x - x.max()) / float(temp[i]))
+        lo, hi = min(o, r), max(o, r)
+        between = kept[lo + 1:hi]
+        assert float(between.sum()) <= 1e-4 * float(kept.sum()), f"row {i}: {o} against {r}"
+
+
 def test_sample_follows_the_distribution(ops):
     vocab, n = 50, 4000
     base = _rand((1, vocab), scale=1.5)
