@@ -1,8 +1,10 @@
 // Matrix product on the 5th-generation tensor cores: C[M,N] (+)= A[M,K] * W[N,K]^T, bfloat16
 // operands, float32 accumulation in tensor memory.  This is the prefill product (M > 64).
 //
-// The kernel is persistent: one block per SM walks over 128 x BN tiles of C (BN = 256, or 128
-// when the output is too narrow to give every SM a wide tile).  Warp 0 feeds a ring of
+// The kernel is persistent: one block per SM walks over 128 x BN tiles of C (BN = 256; 128 when
+// the output is too narrow to give every SM a wide tile; 64 when even those leave more than half
+// of the SMs without one: a portion of 128 rows and N = 1,024 then has 16 tiles instead of 8; a
+// prefill of 100 to 256 tokens at the 0.6B sizes is 1 to 5 % shorter for it).  Warp 0 feeds a ring of
 // shared-memory stages with TMA tile loads (64 elements of K = one 128-byte swizzled row per
 // matrix row); warp 1 issues tcgen05.mma (128 x BN x 16, both operands K-major from shared
 // memory) into one of two accumulators in TMEM and hands each stage back with tcgen05.commit;
@@ -26,7 +28,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 320;       // TMA warp, MMA warp, eight epilogue warps
 
 template <int BN> struct Tile {
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : 8;
     static constexpr int STAGE_A = BM * BK * 2, STAGE_B = BN * BK * 2;
     static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 /* alignment */ + 256 /* barriers */;
     static constexpr unsigned TMEM_COLS = 2 * BN;     // two accumulators
@@ -145,9 +147,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const int row = m0 + quarter * 32 + lane;
             // narrow tiles that add to C fetch C's old values while the products still run
-            constexpr int OLD = BN == 128 ? BN / 8 : 1;
+            constexpr int OLD = BN <= 128 ? BN / 8 : 1;
             float4 old[OLD];
-            if constexpr (BN == 128) {
+            if constexpr (BN <= 128) {
                 if (mode == MODE_ACCUMULATE) {
                     const float* src = c + (size_t)row * ldc + n0 + col_half * (BN / 2);
 #pragma unroll
@@ -213,7 +215,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const bool second = col + i + 4 < n;
                         if (mode == MODE_ACCUMULATE) {
                             float4 was, was2 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                            if constexpr (BN == 128) {
+                            if constexpr (BN <= 128) {
                                 was = old[cc * 8 + i / 4];
                                 was2 = old[cc * 8 + i / 4 + 1];
                             } else {
@@ -261,15 +263,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     table[(size_t)t * 2 * half + half + k] = sn;
 }
 
+// width: the tiles' columns, 256, 128 or 64
 int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c, void* out_act, int m, int n,
-                 int k, int lda, int ldw, int ldc, int ld_act, int mode, bool wide, int* status, void* stream) {
+                 int k, int lda, int ldw, int ldc, int ld_act, int mode, int width, int* status, void* stream) {
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     const int tiles_m = (m + BM - 1) / BM;
     CUtensorMap map_a, map_w;
     if (int rc = make_map_bf16(&map_a, a, m, k, lda, BM, "gemm_tcgen05")) return rc;
-    if (int rc = make_map_bf16(&map_w, w, n, k, ldw, wide ? 256 : 128, "gemm_tcgen05")) return rc;
+    if (int rc = make_map_bf16(&map_w, w, n, k, ldw, width, "gemm_tcgen05")) return rc;
     static TiPerDevice configured;
     if (configured.first_use()) {
         cudaError_t e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,
@@ -277,16 +280,23 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
         if (e2 == cudaSuccess)
             e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Tile<128>::SMEM);
+        if (e2 == cudaSuccess)
+            e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<64>::SMEM);
         if (e2 != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e2));
         configured.mark();
     }
-    if (wide) {
+    if (width == 256) {
         const int tiles = tiles_m * ((n + 255) / 256);
         ti_launch_pdl(gemm_tcgen05_kernel<256>, tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
-    } else {
+    } else if (width == 128) {
         const int tiles = tiles_m * ((n + 127) / 128);
         ti_launch_pdl(gemm_tcgen05_kernel<128>, tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM,
+                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+    } else {
+        const int tiles = tiles_m * ((n + 63) / 64);
+        ti_launch_pdl(gemm_tcgen05_kernel<64>, tiles < sms ? tiles : sms, THREADS, Tile<64>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
     }
     return ti_check_launch("gemm_tcgen05");
@@ -316,9 +326,11 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    // wide tiles when they still give every SM one; else twice as many narrow ones
-    const bool wide = ((m + BM - 1) / BM) * ((n + 255) / 256) >= sms;
-    return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, wide, status, stream);
+    // wide tiles when they still give every SM one; else twice as many narrow ones; else, when
+    // those still leave more than half of the SMs idle, four times as many of 64 columns
+    const int tiles_m = (m + BM - 1) / BM;
+    const int width = tiles_m * ((n + 255) / 256) >= sms ? 256 : tiles_m * ((n + 127) / 128) * 2 >= sms ? 128 : 64;
+    return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, width, status, stream);
 }
 
 // The QKV product of a prompt portion with the epilogue of qkv_epilogue.cuh (head size 128), on
@@ -338,7 +350,7 @@ extern "C" int ti_gemm_tcgen05_qkv(const void* a, const void* w, int m, int k, i
                (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned, q_out and the pages 32-byte");
     const qkv::Epilogue e{q_weight, k_weight, eps, table, positions, req_of_tok, block_table, bt_stride,
                           (bf16*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, (bf16*)q_out};
-    return launch_tiles(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, true, status, stream);
+    return launch_tiles(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, 256, status, stream);
 }
 
 // table [num_tokens][2][half] float32: cosines then sines of positions[t] * inv_freq[k].
