@@ -10,12 +10,11 @@
 // and P never touches it.  Roles:
 //   warp 0     TMA: the two query tiles once, then key and value tiles into two-stage rings (runs
 //              of tokens that lie in one page, as in attn_prefill_tc.cu).
-//   warp 1     tcgen05.mma: S_g = Q_g K^T for g = 0, 1 (128 x 128 x 128, operands K-major from
-//              shared memory) into head g's score buffer, as soon as the last P V of that head
-//              has read the P that lies in it.
-//   warp 2     tcgen05.mma: O_g += P_g V, P as the A operand from tensor memory (where the softmax
-//              left it, over the scores it was made from), V from shared memory with its rows
-//              along N.
+//   warp 1     tcgen05.mma, one issuing thread: S_g = Q_g K^T (128 x 128 x 128, operands K-major
+//              from shared memory) into head g's score buffer and O_g += P_g V (P as the A operand
+//              from tensor memory, where the softmax left it over the scores it was made from; V
+//              from shared memory with its rows along N), a head's next scores right behind its
+//              P V.
 //   warps 4-7  softmax of head 0, warps 8-11 of head 1, one thread per query row: while one head's
 //              threads wait on the exponential unit or write P, the other head's products and
 //              softmax run.  A thread reads its row's 128 scores with tcgen05.ld into registers
@@ -42,7 +41,6 @@ constexpr int SMEM_Q = 0, SMEM_K = 4 * SUB, SMEM_V = SMEM_K + 4 * SUB;      // t
 constexpr int SMEM_BARS = SMEM_V + 4 * SUB;           // (P lives in tensor memory)
 constexpr int SMEM_BYTES = SMEM_BARS + 256 + 1024;
 constexpr int THREADS = 384;                          // three warpgroups: control, softmax of head 0, of head 1
-constexpr int PV_WARP = 2;
 constexpr int CONTROL_REGS = 40, SOFTMAX_REGS = 224;  // (4 * 40 + 8 * 224) * 32 <= 65,536
 constexpr unsigned TMEM_COLS = 512;                   // scores of head 0, head 1; outputs of head 0, head 1
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of a block");
@@ -191,35 +189,37 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
         }
     } else if (warp == 1) {
+        // One thread issues all products, per key tile in the order P V of head 0, next scores of
+        // head 0, P V of head 1, next scores of head 1.  A head's next scores follow its P V at
+        // once (the tensor core runs a thread's products in the order of issue, so they cannot
+        // overtake the P V that still reads P from the same columns), and because head 0 is served
+        // first, head 1 falls half a period behind and stays there: one head's softmax runs while
+        // the other's products do.  (Issued as P V 0, P V 1, scores 0, scores 1 both heads'
+        // softmaxes ended together and each waited for three products: 4,770 cycles a tile.)
         if (lane == 0) {
             const unsigned idesc_s = umma_idesc(BM, BN);
-            ok = mbar_wait(q_full, 0);
-            for (int n = 0; n < num_kt && ok; ++n) {
-                const int st = n & 1;
-                ok = mbar_wait(&k_full[st], (n >> 1) & 1);
-                const unsigned char* kbuf = smem + SMEM_K + st * 2 * SUB;
-                for (int g = 0; g < 2 && ok; ++g) {
-                    // head g's buffer holds P of tile n - 1 until that tile's P V has read it
-                    if (n >= 1) ok = mbar_wait(&p_empty[g], (n - 1) & 1);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks) {
-                        const int sub = ks >> 2, kk = ks & 3;
-                        umma_bf16(tmem_base + g * BN,
-                                  umma_desc(smem + SMEM_Q + g * 2 * SUB + sub * SUB) + (unsigned long long)(kk * 2),
-                                  umma_desc(kbuf + sub * SUB) + (unsigned long long)(kk * 2), idesc_s, ks != 0);
-                    }
-                    umma_commit(&s_full[g]);
-                }
-                if (ok) umma_commit(&k_empty[st]);
-            }
-        }
-    } else if (warp == PV_WARP) {
-        if (lane == 0) {
             const unsigned idesc_o = umma_idesc(BM, HD, /*b_mn_major=*/true);
+            auto issue_scores = [&](int g, int st) {
+                const unsigned char* kbuf = smem + SMEM_K + st * 2 * SUB;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const int sub = ks >> 2, kk = ks & 3;
+                    umma_bf16(tmem_base + g * BN,
+                              umma_desc(smem + SMEM_Q + g * 2 * SUB + sub * SUB) + (unsigned long long)(kk * 2),
+                              umma_desc(kbuf + sub * SUB) + (unsigned long long)(kk * 2), idesc_s, ks != 0);
+                }
+                umma_commit(&s_full[g]);
+            };
+            ok = mbar_wait(q_full, 0);
+            if (ok) ok = mbar_wait(&k_full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_scores(0, 0);
+                issue_scores(1, 0);
+                umma_commit(&k_empty[0]);
+            }
             for (int j = 0; j < num_kt && ok; ++j) {
-                const int st = j & 1;
+                const int st = j & 1, nst = (j + 1) & 1;
                 ok = mbar_wait(&v_full[st], (j >> 1) & 1);
                 const unsigned char* vbuf = smem + SMEM_V + st * 2 * SUB;
                 for (int g = 0; g < 2 && ok; ++g) {
@@ -235,8 +235,15 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                                          umma_desc(vbuf + ks * 2048, SUB, 1024), idesc_o, j >= 1 || ks != 0);
                     }
                     umma_commit(&p_empty[g]);
+                    if (g == 1) umma_commit(&v_empty[st]);
+                    if (j + 1 < num_kt) {
+                        if (g == 0) ok = mbar_wait(&k_full[nst], ((j + 1) >> 1) & 1);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_scores(g, nst);
+                        if (g == 1) umma_commit(&k_empty[nst]);
+                    }
                 }
-                if (ok) umma_commit(&v_empty[st]);
             }
         }
     } else if (warp >= 4) {
