@@ -553,6 +553,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per cache page")
     ap.add_argument("--prefill-tokens", type=int, default=2048,
                     help="with --only prefill: the length of the prompt (the default run's is 2,048)")
+    ap.add_argument("--mixed-decoders", type=int, default=63,
+                    help="with --only mixed: the number of decoding requests beside the 512-token portion")
+    ap.add_argument("--attention-in-turn", action="store_true",
+                    help="with --only mixed: flash-decoding behind the prompt attention kernel, not beside it")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
@@ -591,8 +595,10 @@ def main() -> int:
                           measure_chains(engine, args.batch, torch)}))
         return 0
     if args.only == "mixed":
-        mx_ms = measure_mixed(engine, 63, 512, args.context, torch)
-        print(json.dumps({"only": "mixed", "decoding": 63, "portion": 512, "ms": round(mx_ms, 3)}))
+        engine.ops.attention_side_by_side = not args.attention_in_turn
+        mx_ms = measure_mixed(engine, args.mixed_decoders, 512, args.context, torch)
+        print(json.dumps({"only": "mixed", "decoding": args.mixed_decoders, "portion": 512, "ms": round(mx_ms, 3),
+                          "attention": "in turn" if args.attention_in_turn else "side by side"}))
         return 0
     if args.only == "prefill":
         pf_ms = measure_prefill(engine, args.prefill_tokens, max(1, min(args.steps, 8)), torch)

@@ -22,7 +22,12 @@ namespace {
 
 using namespace attn_decode_core;
 
-template <int HD, bool SINGLE>
+// LATE_WAIT: the kernel before this one needs none of this kernel's results and this kernel none
+// of its, and that kernel released its dependents only after its own wait had returned, so
+// everything a block reads here was complete when the block started.  The blocks run beside that
+// kernel without waiting for it; one block waits for it at its end (the others leave their SMs to
+// blocks still to come), so that whoever waits for this kernel has waited for both.
+template <int HD, bool SINGLE, bool LATE_WAIT = false>
 __global__ void __launch_bounds__(32)
 attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
                    const int* __restrict__ positions, const int* __restrict__ req_of_tok,
@@ -36,11 +41,14 @@ attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
     const int kvh = blockIdx.y, row = blockIdx.z;
     const int t = rows ? rows[row] : row;
     const int group = num_heads / num_kv_heads;
-    decode_item<HD, true, NoPrologue, SINGLE>(smem, q + ((size_t)t * num_heads + (size_t)kvh * group) * HD, nullptr, nullptr,
-                          blockIdx.x, gridDim.x, kvh, row, t, positions[t],
-                          block_table + (size_t)req_of_tok[t] * bt_stride, pages, num_pages, page_size,
-                          num_heads, num_kv_heads, window, scale_log2, part_o, part_ml, counters, out,
-                          status);
+    decode_item<HD, true, NoPrologue, SINGLE, LATE_WAIT>(
+        smem, q + ((size_t)t * num_heads + (size_t)kvh * group) * HD, nullptr, nullptr,
+        blockIdx.x, gridDim.x, kvh, row, t, positions[t],
+        block_table + (size_t)req_of_tok[t] * bt_stride, pages, num_pages, page_size,
+        num_heads, num_kv_heads, window, scale_log2, part_o, part_ml, counters, out, status);
+    if constexpr (LATE_WAIT) {
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) pdl_wait();
+    }
 }
 
 // Head norm and NeoX rotation of a head vector of which a lane holds the elements k0, k0 + 1 of both
@@ -196,7 +204,7 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
                   const int* req_of_tok, const int* block_table, int bt_stride, const bf16* pages,
                   int num_pages, int page_size, int num_heads, int num_kv_heads, int window,
                   float scale, int num_splits, float* part_o, float* part_ml, unsigned* counters,
-                  bf16* out, int* status, cudaStream_t s) {
+                  bf16* out, int* status, int late_wait, cudaStream_t s) {
     constexpr int SMEM = STAGES * 2 * TILE * (HD * 2 + 16);
     static TiPerDevice configured;
     if (configured.first_use()) {
@@ -208,14 +216,34 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
         configured.mark();
     }
     dim3 grid(num_splits, num_kv_heads, num_rows);
-    if (num_splits == 1 && counters != nullptr)      // nothing to merge: the kernel without that code
-        ti_launch_pdl(attn_decode_kernel<HD, true>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,
-                      block_table, bt_stride, pages, num_pages, page_size, num_heads, num_kv_heads, window,
-                      scale * LOG2E, part_o, part_ml, counters, out, status);
-    else
-        ti_launch_pdl(attn_decode_kernel<HD, false>, grid, 32, SMEM, s, q, rows, positions, req_of_tok,
-                      block_table, bt_stride, pages, num_pages, page_size, num_heads, num_kv_heads, window,
-                      scale * LOG2E, part_o, part_ml, counters, out, status);
+    const bool single = num_splits == 1 && counters != nullptr;     // nothing to merge: the kernel without that code
+#define LAUNCH(KERNEL)                                                                                   \
+    ti_launch_pdl(KERNEL, grid, 32, SMEM, s, q, rows, positions, req_of_tok, block_table, bt_stride, pages, \
+                  num_pages, page_size, num_heads, num_kv_heads, window, scale * LOG2E, part_o, part_ml,    \
+                  counters, out, status)
+    if (late_wait) {
+        if constexpr (HD == 128) {
+            static TiPerDevice late_configured;
+            if (late_configured.first_use()) {
+                cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, false, true>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+                if (e == cudaSuccess)
+                    e = cudaFuncSetAttribute(attn_decode_kernel<HD, true, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+                if (e != cudaSuccess) return ti_fail("attn_decode: %s", cudaGetErrorString(e));
+                late_configured.mark();
+            }
+            if (single) LAUNCH((attn_decode_kernel<HD, true, true>));
+            else LAUNCH((attn_decode_kernel<HD, false, true>));
+        } else {
+            return ti_fail("attn_decode: a late wait is built for head_dim 128 only, not %d", HD);
+        }
+    } else if (single) {
+        LAUNCH((attn_decode_kernel<HD, true>));
+    } else {
+        LAUNCH((attn_decode_kernel<HD, false>));
+    }
+#undef LAUNCH
     if (int rc = ti_check_launch("attn_decode")) return rc;
     if (counters) return 0;
     attn_decode_merge_kernel<<<(num_rows * num_heads + 3) / 4, 128, 0, s>>>(
@@ -270,7 +298,7 @@ extern "C" int ti_attn_decode_fused(const void* q, const int* rows, int num_rows
                                     const void* pages, int num_pages, int page_size, int num_heads,
                                     int num_kv_heads, int head_dim, int window, float scale,
                                     int num_splits, float* part_o, float* part_ml,
-                                    unsigned* counters, void* out, int* status, void* stream);
+                                    unsigned* counters, void* out, int* status, int late_wait, void* stream);
 
 extern "C" int ti_attn_decode(const void* q, const int* rows, int num_rows, const int* positions,
                               const int* req_of_tok, const int* block_table, int bt_stride,
@@ -280,7 +308,7 @@ extern "C" int ti_attn_decode(const void* q, const int* rows, int num_rows, cons
                               int* status, void* stream) {
     return ti_attn_decode_fused(q, rows, num_rows, positions, req_of_tok, block_table, bt_stride,
                                 pages, num_pages, page_size, num_heads, num_kv_heads, head_dim,
-                                window, scale, num_splits, part_o, part_ml, nullptr, out, status,
+                                window, scale, num_splits, part_o, part_ml, nullptr, out, status, 0,
                                 stream);
 }
 
@@ -289,8 +317,9 @@ extern "C" int ti_attn_decode_fused(const void* q, const int* rows, int num_rows
                                     const void* pages, int num_pages, int page_size, int num_heads,
                                     int num_kv_heads, int head_dim, int window, float scale,
                                     int num_splits, float* part_o, float* part_ml,
-                                    unsigned* counters, void* out, int* status, void* stream) {
+                                    unsigned* counters, void* out, int* status, int late_wait, void* stream) {
     if (num_rows == 0) return 0;
+    TI_REQUIRE(!late_wait || counters != nullptr, "attn_decode: a late wait needs the merge in the same launch");
     TI_REQUIRE(num_heads % num_kv_heads == 0, "attn_decode: %d heads over %d kv heads", num_heads,
                num_kv_heads);
     TI_REQUIRE(ti_attn_decode_supported(head_dim, num_heads / num_kv_heads, page_size),
@@ -304,7 +333,7 @@ extern "C" int ti_attn_decode_fused(const void* q, const int* rows, int num_rows
         return launch_decode<HD>((const bf16*)q, rows, num_rows, positions, req_of_tok,            \
                                  block_table, bt_stride, (const bf16*)pages, num_pages, page_size, \
                                  num_heads, num_kv_heads, window, scale, num_splits, part_o,       \
-                                 part_ml, counters, (bf16*)out, status, (cudaStream_t)stream)
+                                 part_ml, counters, (bf16*)out, status, late_wait, (cudaStream_t)stream)
     switch (head_dim) {
         CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     }

@@ -185,7 +185,7 @@ struct NoPrologue {
 // unnormed prepares them there.
 // SINGLE: the caller knows that the row's keys are not split (num_splits == 1 and counters given):
 // the code of the merge is then left out, and its registers do not weigh on the key loop.
-template <int HD, bool PDL, class Prologue = NoPrologue, bool SINGLE = false>
+template <int HD, bool PDL, class Prologue = NoPrologue, bool SINGLE = false, bool LATE_WAIT = false>
 __device__ __forceinline__ void decode_item(
         unsigned char* smem, const bf16* qbase, const bf16* new_k, const bf16* new_v,
         int split, int num_splits, int kvh, int row, int t, int pos,
@@ -260,17 +260,24 @@ __device__ __forceinline__ void decode_item(
                 ++early;
             }
         }
-        if (PDL) pdl_wait();
+        if (PDL && !LATE_WAIT) pdl_wait();
         prologue();
         // queries of the group as the A operand: row r of the tile is head kvh*group + r
         unsigned qa[KSTEPS][4];
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             const int k0 = ks * 16 + tq * 2;
-            qa[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0) : 0u;
-            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0) : 0u;
-            qa[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0 + 8) : 0u;
-            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0 + 8) : 0u;
+            // (with LATE_WAIT they lie in global memory and are read from L2: this block has not
+            // itself waited for the kernel that wrote them; otherwise they may lie in shared memory)
+            auto ld = [&](const bf16* p) {
+                const unsigned* u = reinterpret_cast<const unsigned*>(p);
+                if constexpr (LATE_WAIT) return __ldcg(u);
+                else return *u;
+            };
+            qa[ks][0] = g < group ? ld(qbase + (size_t)g * HD + k0) : 0u;
+            qa[ks][1] = g + 8 < group ? ld(qbase + (size_t)(g + 8) * HD + k0) : 0u;
+            qa[ks][2] = g < group ? ld(qbase + (size_t)g * HD + k0 + 8) : 0u;
+            qa[ks][3] = g + 8 < group ? ld(qbase + (size_t)(g + 8) * HD + k0 + 8) : 0u;
         }
 
 #pragma unroll
@@ -384,7 +391,7 @@ __device__ __forceinline__ void decode_item(
         }
         cp_async_wait<0>();
     } else {
-        if (PDL) pdl_wait();
+        if (PDL && !LATE_WAIT) pdl_wait();
         prologue();
     }
     // the sums of a row live in the four lanes of a quad

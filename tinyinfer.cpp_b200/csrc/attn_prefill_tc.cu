@@ -48,7 +48,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ tiles, const int* __restrict__ positions,
                        const int* __restrict__ block_table, int bt_stride, int num_pages, int page_size,
                        int num_heads, int num_kv_heads, int window, int run, float scale_log2,
-                       bf16* __restrict__ out, int* __restrict__ status) {
+                       bf16* __restrict__ out, int* __restrict__ status, int hold_dependents) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* bars = (unsigned long long*)(smem + SMEM_BARS);
@@ -86,12 +86,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-    pdl_launch();
+    // `hold_dependents`: the next kernel is released only when this block's wait has returned, so
+    // that it may run beside this one on what this one waited for, without a wait of its own
+    if (!hold_dependents) pdl_launch();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_wait();        // queries, keys and values come from the kernel before
+    if (hold_dependents) pdl_launch();
     const unsigned tmem_o = tmem_base + 256;
 
     bool ok = true;
@@ -338,7 +341,7 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
                                   const int* positions, const int* block_table, int bt_stride,
                                   const void* pages, int num_pages, int page_size, int num_heads,
                                   int num_kv_heads, int head_dim, int window, float scale, void* out,
-                                  int* status, void* stream) {
+                                  int* status, int hold_dependents, void* stream) {
     if (num_tiles == 0) return 0;
     TI_REQUIRE(ti_attn_prefill_tc_supported(head_dim, page_size, num_heads, num_kv_heads),
                "attn_prefill_tc: head_dim %d (128), page size %d (multiple of 16) or heads %d/%d "
@@ -365,6 +368,6 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
     dim3 grid(num_heads, num_tiles);
     ti_launch_pdl(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,
                   tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads, num_kv_heads,
-                  window, run, scale * LOG2E, (bf16*)out, status);
+                  window, run, scale * LOG2E, (bf16*)out, status, hold_dependents);
     return ti_check_launch("attn_prefill_tc");
 }

@@ -22,6 +22,8 @@ qkv_rope_store(h, w, ..., rotation, ...)     the QKV product followed by qk_norm
                                              refused unless register_rotation gave a handler
 step_lists(act_dtype)                        the host-built lists its kernels want of every step
 paged_attention(...)                         causal attention over the pages of each token's request
+                                             (single-token rows by flash-decoding, prompt portions by
+                                             a prompt kernel, side by side where both are there)
 qkv_attention(h, w, ..., out, ...)           qkv_rope_store followed by paged_attention, for a mixer
                                              that wants both at once
 argmax(logits, out) / sample(...)            next token per row
@@ -97,6 +99,9 @@ class CudaOps:
         # prompt attention with two heads per block (csrc/attn_prefill_tc2.cu) from this many
         # (head, tile) pairs per SM on (None: never)
         self.tc_attention_pairs_from = 3
+        # a step's single-token rows and its prompt portions: flash-decoding beside the tcgen05
+        # prompt kernel instead of behind it
+        self.attention_side_by_side = True
         # the feed-forward of a decode step of at most 16 rows as one launch, when a layer's
         # feed-forward weights fit into the GPU's shared memory (csrc/ffn_decode.cu); same bits as
         # the two products it replaces
@@ -154,7 +159,7 @@ class CudaOps:
             b.ti_attn_decode_supported.argtypes = [_i, _i, _i]
             b.ti_attn_decode_blocks_per_sm.argtypes = [_i]
             b.ti_attn_decode_fused.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i,
-                                               _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
+                                               _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]
             b.ti_attn_decode_qkv_supported.argtypes = [_i, _i, _i]
             b.ti_attn_decode_qkv.argtypes = [_vp, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i,
                                              _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
@@ -171,7 +176,7 @@ class CudaOps:
                                           _vp, _vp, _vp]
             b.ti_attn_prefill_tc_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_prefill_tc.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                             _f, _vp, _vp, _vp]
+                                             _f, _vp, _vp, _i, _vp]
             b.ti_attn_prefill_tc2_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_prefill_tc2.argtypes = b.ti_attn_prefill_tc.argtypes
             self._tile_rows = (int(b.ti_attn_prefill_tile_rows()), int(b.ti_attn_prefill_tc_tile_rows()))
@@ -594,8 +599,21 @@ class CudaOps:
                               "(pass lists=ops.step_lists(dtype) to build_step_batch)")
         single = lists["single_rows"] if tensor_cores else None
         n_dec = single.shape[0] if tensor_cores else 0
-        if (n_dec and self.bf16.ti_attn_decode_supported(head_dim, num_heads // num_kv_heads,
-                                                         cache.page_size)):
+        decode = bool(n_dec) and bool(self.bf16.ti_attn_decode_supported(
+            head_dim, num_heads // num_kv_heads, cache.page_size))
+        small, big = self._tile_rows if tensor_cores else (0, 0)
+        tiles = lists[f"portion_tiles_{small}"] if tensor_cores else None
+        prompt = (tensor_cores and tiles.shape[0] > 0
+                  and bool(self.bf16.ti_attn_prefill_supported(head_dim, cache.page_size)))
+        prompt_tc = prompt and self.use_tc_attention and bool(self.bf16.ti_attn_prefill_tc_supported(
+            head_dim, cache.page_size, num_heads, num_kv_heads))
+        # Single-token rows beside prompt portions: the two kernels need nothing of one another.
+        # The prompt kernel (tensor-bound, on a part of the SMs) goes first and releases its
+        # dependents only when its own wait has returned; flash-decoding (bound by HBM) then runs
+        # beside it on what that wait covered and waits for the prompt kernel at its end.
+        beside = decode and prompt_tc and self.attention_side_by_side
+
+        def run_decode():
             splits = self.decode_splits(n_dec, num_kv_heads, step.max_position or step.max_ctx_len, head_dim)
             part_o = torch.empty((n_dec, num_heads, splits, head_dim), dtype=torch.float32,
                                  device=q.device)
@@ -609,17 +627,17 @@ class CudaOps:
                 step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
                 pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
                 float(scale), splits, part_o.data_ptr(), part_ml.data_ptr(),
-                self._counters.data_ptr(), out.data_ptr(), self.status.data_ptr(),
+                self._counters.data_ptr(), out.data_ptr(), self.status.data_ptr(), int(beside),
                 self._stream()), self.bf16)
+
+        if decode and not beside:
+            run_decode()
+        if decode:
             rows, n_rows = lists["portion_rows"], lists["portion_rows"].shape[0]
             if n_rows == 0:
                 return
-        small, big = self._tile_rows if tensor_cores else (0, 0)
-        tiles = lists[f"portion_tiles_{small}"] if tensor_cores else None
-        n_tiles = tiles.shape[0] if tensor_cores else 0
-        if n_tiles and self.bf16.ti_attn_prefill_supported(head_dim, cache.page_size):
-            if self.use_tc_attention and self.bf16.ti_attn_prefill_tc_supported(
-                    head_dim, cache.page_size, num_heads, num_kv_heads):
+        if prompt:
+            if prompt_tc:
                 tiles = lists[f"portion_tiles_{big}"]
                 # many tiles per SM: the kernel that takes two heads of a kv group per block
                 two = (self.tc_attention_pairs_from is not None
@@ -631,10 +649,13 @@ class CudaOps:
                     q.data_ptr(), q.shape[0], tiles.data_ptr(), tiles.shape[0],
                     step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
                     pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
-                    float(scale), out.data_ptr(), self.status.data_ptr(), self._stream()), self.bf16)
+                    float(scale), out.data_ptr(), self.status.data_ptr(), int(beside), self._stream()),
+                    self.bf16)
+                if beside:
+                    run_decode()
             else:
                 self._ok(self.bf16.ti_attn_prefill(
-                    q.data_ptr(), tiles.data_ptr(), n_tiles, step.positions.data_ptr(),
+                    q.data_ptr(), tiles.data_ptr(), tiles.shape[0], step.positions.data_ptr(),
                     bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size,
                     num_heads, num_kv_heads, head_dim, win, float(scale), out.data_ptr(),
                     self.status.data_ptr(), self._stream()), self.bf16)
