@@ -195,6 +195,7 @@ def test_decoding_rows_run_beside_a_portion_with_the_same_bits(decoders):
     assert eng.ops.attention_side_by_side
     logits = {}
     try:
+        eng.ops.split_prompt_keys = False       # (whether a tile's keys are cut depends on the order)
         for beside in (False, True):
             eng.ops.attention_side_by_side = beside
             for lo in range(0, decoders, 4):
@@ -211,7 +212,7 @@ def test_decoding_rows_run_beside_a_portion_with_the_same_bits(decoders):
                 eng.finish(r)
             eng._step_graphs = type(eng._step_graphs)(eng)      # captured with this order of launches
     finally:
-        eng.ops.attention_side_by_side = True
+        eng.ops.attention_side_by_side = eng.ops.split_prompt_keys = True
     eng.ops.check_status()
     eng.cache.check()
     assert torch.isfinite(logits[True]).all()

@@ -406,6 +406,43 @@ def _paged_case(num_heads, num_kv, hd, page_size, ctx_lens, q_lens, dtype, seed=
     return step, cache, q
 
 
+@pytest.mark.parametrize("case", [(4096, 512), (700, 128), (5000, 300), (1300, 1024), (129, 2)])
+@pytest.mark.parametrize("window", [None, 600])
+def test_prompt_attention_with_the_keys_of_a_tile_cut_into_runs(ops, case, window):
+    """A step with fewer (tile, head) pairs than SMs cuts every tile's keys into runs of key tiles,
+    a block each, and adds them in a second launch: against the plain statement, and close to
+    the uncut kernel (they differ by the rounding of the partial sums only)."""
+    from ref_ops import RefOps
+    ctx, ql = case
+    heads, kv, hd, ps = 8, 4, 128, 64
+    step, cache, q = _paged_case(heads, kv, hd, ps, [ctx], [ql], torch.bfloat16, seed=4)
+    # one key far back gets a large score for one query row: a lost run of keys would show
+    far = 3 if window is None else max(0, ctx - ql - window + 5)
+    page = int(cache.block_table[0, far // ps])
+    cache.pages[page, 0, 1, far % ps] *= 6.0
+    q[ql - 1, 2 * hd:3 * hd] = cache.pages[page, 0, 1, far % ps].to(q.dtype)
+    scale = 1.0 / math.sqrt(hd)
+    n_tiles = step.lists["portion_tiles_128"].shape[0]
+    runs = ops.bf16.ti_attn_prefill_tc_splits(n_tiles, heads)
+    assert runs == min(8, max(1, ops.num_sms // (n_tiles * heads)))
+    out = {}
+    keep = ops.split_prompt_keys
+    try:
+        for split in (False, True):
+            ops.split_prompt_keys = split
+            out[split] = torch.zeros_like(q)
+            ops.paged_attention(q, step, cache, out[split], heads, kv, hd, window, scale)
+    finally:
+        ops.split_prompt_keys = keep
+    ops.check_status()
+    ref = torch.zeros_like(q)
+    RefOps().paged_attention(q, step, cache, ref, heads, kv, hd, window, scale)
+    _close(out[True], ref, 1.5e-2, f"cut into {runs} runs, context {ctx}, portion {ql}, window {window}")
+    _close(out[True], out[False], 1e-2, "cut against uncut")
+    if runs > 1:
+        assert not torch.equal(out[True], out[False]) or ql <= 2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("geom", [(4, 2, 16, 16), (3, 1, 48, 16), (16, 8, 128, 16), (8, 1, 64, 32),
                                   (6, 3, 80, 16), (32, 2, 32, 16), (5, 5, 144, 16), (2, 1, 256, 64)])

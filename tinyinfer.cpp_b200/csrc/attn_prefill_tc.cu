@@ -16,6 +16,10 @@
 //              shared memory in the swizzled layout the MMA reads.  The output accumulator is
 //              rescaled in tensor memory only when a row's maximum has grown by more than 2^8
 //              since the last rescale (exact arithmetic: the reference maximum may lag behind).
+// When a step has fewer (tile, head) pairs than the GPU has SMs (a portion of a long prompt: few
+// tiles with long rows of keys), the keys of every tile are cut into `gridDim.z` equal runs of
+// key tiles, one block each: a block then leaves its output unnormalised in a float32 workspace
+// with its rows' reference maxima and sums, and a second kernel adds the runs.
 // Every wait on an mbarrier is bounded; on a timeout the block records status 2, frees its tensor
 // memory and returns.
 #include "sm100.cuh"
@@ -48,7 +52,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ tiles, const int* __restrict__ positions,
                        const int* __restrict__ block_table, int bt_stride, int num_pages, int page_size,
                        int num_heads, int num_kv_heads, int window, int run, float scale_log2,
-                       bf16* __restrict__ out, int* __restrict__ status, int hold_dependents) {
+                       bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       int* __restrict__ status, int hold_dependents) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* bars = (unsigned long long*)(smem + SMEM_BARS);
@@ -71,8 +76,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int nrows = tiles[tile_id * 3 + 2];
     const int pos_first = positions[tok0], pos_last = pos_first + nrows - 1;
     const int kv_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
-    const int kt_lo = kv_lo / BN;
-    const int num_kt = pos_last / BN + 1 - kt_lo;
+    // this block's run of the tile's key tiles (all of them without a split; none if there are
+    // more blocks than key tiles)
+    const int splits = gridDim.z, split = blockIdx.z;
+    const int kt_first = kv_lo / BN, kt_all = pos_last / BN + 1 - kt_first;
+    const int kt_lo = kt_first + (int)((long long)kt_all * split / splits);
+    const int num_kt = kt_first + (int)((long long)kt_all * (split + 1) / splits) - kt_lo;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -107,7 +116,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int* table = block_table + (size_t)req * bt_stride;
         const int oob_row = num_pages * 2 * num_kv_heads * page_size;          // outside the tensor: zeros
         const int to_v = num_kv_heads * page_size;                             // keys -> values of a page
-        if (lane == 0) {
+        if (lane == 0 && num_kt > 0) {
             mbar_expect_tx(q_full, 2 * SUB);
             tma_load_2d(smem + SMEM_Q, &map_q, q_full, h * HD, tok0);
             tma_load_2d(smem + SMEM_Q + SUB, &map_q, q_full, h * HD + 64, tok0);
@@ -127,7 +136,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             return krow;
         };
-        int krow_next = lookup(0);
+        int krow_next = num_kt > 0 ? lookup(0) : oob_row;
         for (int j = 0; j < num_kt && ok; ++j) {
             const int st = j & 1;
             const int krow = krow_next;
@@ -158,7 +167,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && num_kt > 0) {
             const unsigned idesc_s = umma_idesc(BM, BN);
             const unsigned idesc_o = umma_idesc(BM, HD, /*b_mn_major=*/true);
             auto issue_scores = [&](int buf, int st) {
@@ -290,8 +299,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        if (ok) ok = mbar_wait(p_empty, (num_kt - 1) & 1);
-        if (ok) {
+        if (ok && num_kt > 0) ok = mbar_wait(p_empty, (num_kt - 1) & 1);
+        if (ok && splits > 1) {
+            // this run's share: the output as it stands against m_ref, with m_ref and the sum
+            tc_fence_after();
+            const size_t slot = ((size_t)tile_id * num_heads + h) * splits + split;
+            float* prow = part_o + (slot * BM + row) * HD;
+            if (row < nrows) {
+                part_ml[(slot * BM + row) * 2] = m_ref;
+                part_ml[(slot * BM + row) * 2 + 1] = l_run;
+            }
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                if (num_kt > 0) {
+                    tmem_load32(tmem_o + lane_addr + c * 32, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                }
+                if (row >= nrows) continue;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(prow + c * 32 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            }
+        } else if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l_run;
             bf16* orow = out + ((size_t)(tok0 + row) * num_heads + h) * HD;
@@ -325,6 +357,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// Adds the runs of a split tile: out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M the largest
+// m_s.  A warp per query row, a lane per four elements of the head.
+constexpr int MERGE_ROWS = 16;
+__global__ void __launch_bounds__(MERGE_ROWS * 32)
+attn_prefill_merge_kernel(const int* __restrict__ tiles, const float* __restrict__ part_o,
+                          const float* __restrict__ part_ml, int num_heads, int splits,
+                          bf16* __restrict__ out) {
+    pdl_launch();
+    const int h = blockIdx.x, tile_id = blockIdx.y;
+    const int row = blockIdx.z * MERGE_ROWS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int tok0 = tiles[tile_id * 3 + 1], nrows = tiles[tile_id * 3 + 2];
+    pdl_wait();
+    if (row >= nrows) return;
+    const size_t first = ((size_t)tile_id * num_heads + h) * splits;
+    float big = -INFINITY;
+    for (int s = 0; s < splits; ++s) big = fmaxf(big, part_ml[((first + s) * BM + row) * 2]);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float sum = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = part_ml[((first + s) * BM + row) * 2];
+        if (m == -INFINITY) continue;                     // this run saw no key of the row
+        const float w = exp2f(m - big);
+        sum += w * part_ml[((first + s) * BM + row) * 2 + 1];
+        const float4 o = *reinterpret_cast<const float4*>(part_o + ((first + s) * BM + row) * HD + lane * 4);
+        acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+    }
+    const float inv = 1.0f / sum;
+    bf16* dst = out + ((size_t)(tok0 + row) * num_heads + h) * HD + lane * 4;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+}
+
 }  // namespace
 
 extern "C" int ti_attn_prefill_tc_tile_rows() { return BM; }
@@ -334,13 +398,31 @@ extern "C" int ti_attn_prefill_tc_supported(int head_dim, int page_size, int num
            num_heads % num_kv_heads == 0;
 }
 
+// In how many runs the keys of every tile are cut: so many that the blocks fill the SMs once, and
+// none when there are as many (tile, head) pairs as SMs already.
+constexpr int MAX_SPLITS = 8;
+extern "C" int ti_attn_prefill_tc_splits(int num_tiles, int num_heads) {
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long long pairs = (long long)num_tiles * num_heads;
+    if (pairs <= 0 || sms <= 0) return 1;
+    const long long s = sms / pairs;
+    return (int)(s < 1 ? 1 : s > MAX_SPLITS ? MAX_SPLITS : s);
+}
+
 // q, out: [tokens, num_heads * 128] bfloat16, contiguous.  pages: the cache slot's pool
 // [num_pages, 2, kv_heads, page_size, 128] bfloat16, contiguous.  tiles: int32 [num_tiles, 3] =
-// {request row, first flat token, query rows (<= 128)}.
+// {request row, first flat token, query rows (<= 128)}.  splits: 1, or ti_attn_prefill_tc_splits
+// with part_o [num_tiles, num_heads, splits, 128, 128] and part_ml [num_tiles, num_heads, splits,
+// 128, 2] float32 as scratch; the runs are then added by a second launch, which comes after
+// `between` (may be null: a launch the caller wants between the two, on the same stream; with
+// `hold_dependents` a kernel that runs beside this one and waits for it at its end).
 extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tiles, int num_tiles,
                                   const int* positions, const int* block_table, int bt_stride,
                                   const void* pages, int num_pages, int page_size, int num_heads,
                                   int num_kv_heads, int head_dim, int window, float scale, void* out,
+                                  int splits, float* part_o, float* part_ml,
                                   int* status, int hold_dependents, void* stream) {
     if (num_tiles == 0) return 0;
     TI_REQUIRE(ti_attn_prefill_tc_supported(head_dim, page_size, num_heads, num_kv_heads),
@@ -349,6 +431,9 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
     TI_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)pages % 16 == 0 && (uintptr_t)out % 32 == 0,
                "attn_prefill_tc: tensors must be 16-byte aligned, the output 32-byte");
     TI_REQUIRE(num_tiles <= 65535, "attn_prefill_tc: %d tiles exceed the grid limit", num_tiles);
+    TI_REQUIRE(splits >= 1 && splits <= MAX_SPLITS &&
+               (splits == 1 || (part_o != nullptr && part_ml != nullptr && (uintptr_t)part_o % 16 == 0)),
+               "attn_prefill_tc: %d runs per tile (1..%d) need their 16-byte aligned scratch", splits, MAX_SPLITS);
     const long long pool_rows = (long long)num_pages * 2 * num_kv_heads * page_size;
     TI_REQUIRE(pool_rows < (1LL << 31) - 1, "attn_prefill_tc: the page pool has too many token slots");
     CUtensorMap map_q, map_kv;
@@ -365,9 +450,19 @@ extern "C" int ti_attn_prefill_tc(const void* q, int num_tokens, const int* tile
         if (e != cudaSuccess) return ti_fail("attn_prefill_tc: %s", cudaGetErrorString(e));
         configured.mark();
     }
-    dim3 grid(num_heads, num_tiles);
+    dim3 grid(num_heads, num_tiles, splits);
     ti_launch_pdl(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,
                   tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads, num_kv_heads,
-                  window, run, scale * LOG2E, (bf16*)out, status, hold_dependents);
+                  window, run, scale * LOG2E, (bf16*)out, part_o, part_ml, status, hold_dependents);
     return ti_check_launch("attn_prefill_tc");
+}
+
+// The second launch of a split ti_attn_prefill_tc (same tiles, scratch and output).
+extern "C" int ti_attn_prefill_tc_merge(const int* tiles, int num_tiles, int num_heads, int splits,
+                                        const float* part_o, const float* part_ml, void* out, void* stream) {
+    if (num_tiles == 0 || splits <= 1) return 0;
+    dim3 grid(num_heads, num_tiles, BM / MERGE_ROWS);
+    ti_launch_pdl(attn_prefill_merge_kernel, grid, dim3(MERGE_ROWS * 32), 0, (cudaStream_t)stream, tiles, part_o,
+                  part_ml, num_heads, splits, (bf16*)out);
+    return ti_check_launch("attn_prefill_tc_merge");
 }
