@@ -79,7 +79,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                        const int* __restrict__ tiles, const int* __restrict__ positions,
                        const int* __restrict__ block_table, int bt_stride, int num_pages, int page_size,
                        int num_heads, int num_kv_heads, int window, int run, float scale_log2,
-                       bf16* __restrict__ out, int* __restrict__ status, int hold_dependents) {
+                       bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ status, int hold_dependents) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* bars = (unsigned long long*)(smem + SMEM_BARS);
@@ -101,8 +102,12 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int nrows = tiles[tile_id * 3 + 2];
     const int pos_first = positions[tok0], pos_last = pos_first + nrows - 1;
     const int kv_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
-    const int kt_lo = kv_lo / BN;
-    const int num_kt = pos_last / BN + 1 - kt_lo;
+    // this block's run of the tile's key tiles (see attn_prefill_tc.cu: all of them without a
+    // split; none if there are more blocks than key tiles)
+    const int splits = gridDim.z, split = blockIdx.z;
+    const int kt_first = kv_lo / BN, kt_all = pos_last / BN + 1 - kt_first;
+    const int kt_lo = kt_first + (int)((long long)kt_all * split / splits);
+    const int num_kt = kt_first + (int)((long long)kt_all * (split + 1) / splits) - kt_lo;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -139,7 +144,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int* table = block_table + (size_t)req * bt_stride;
         const int oob_row = num_pages * 2 * num_kv_heads * page_size;          // outside the tensor: zeros
         const int to_v = num_kv_heads * page_size;                             // keys -> values of a page
-        if (lane == 0) {
+        if (lane == 0 && num_kt > 0) {
             mbar_expect_tx(q_full, 4 * SUB);
             for (int g = 0; g < 2; ++g) {
                 tma_load_2d(smem + SMEM_Q + g * 2 * SUB, &map_q, q_full, (h + g) * HD, tok0);
@@ -161,7 +166,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
             return krow;
         };
-        int krow_next = lookup(0);
+        int krow_next = num_kt > 0 ? lookup(0) : oob_row;
         for (int j = 0; j < num_kt && ok; ++j) {
             const int st = j & 1;
             const int krow = krow_next;
@@ -199,7 +204,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // first, head 1 falls half a period behind and stays there: one head's softmax runs while
         // the other's products do.  (Issued as P V 0, P V 1, scores 0, scores 1 both heads'
         // softmaxes ended together and each waited for three products: 4,770 cycles a tile.)
-        if (lane == 0) {
+        if (lane == 0 && num_kt > 0) {
             const unsigned idesc_s = umma_idesc(BM, BN);
             const unsigned idesc_o = umma_idesc(BM, HD, /*b_mn_major=*/true);
             auto issue_scores = [&](int g, int st) {
@@ -332,7 +337,30 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (lane == 0) mbar_arrive(&p_full[group]);
         }
         if (ok && use > 0) ok = mbar_wait(&p_empty[group], (use - 1) & 1);
-        if (ok) {
+        if (ok && splits > 1) {
+            // this run's share: the output as it stands against m_ref, with m_ref and the sum
+            tc_fence_after();
+            const size_t slot = ((size_t)tile_id * num_heads + h + group) * splits + split;
+            float* prow = part_o + (slot * BM + row) * HD;
+            if (row < nrows) {
+                part_ml[(slot * BM + row) * 2] = m_ref;
+                part_ml[(slot * BM + row) * 2 + 1] = l_run;
+            }
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                if (use > 0) {
+                    tmem_load32(tmem_mine + c * 32, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                }
+                if (row >= nrows) continue;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(prow + c * 32 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            }
+        } else if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l_run;
             bf16* orow = out + ((size_t)(tok0 + row) * num_heads + h + group) * HD;
@@ -370,13 +398,18 @@ extern "C" int ti_attn_prefill_tc2_supported(int head_dim, int page_size, int nu
            num_heads % num_kv_heads == 0 && (num_heads / num_kv_heads) % 2 == 0;
 }
 
-// As ti_attn_prefill_tc (attn_prefill_tc.cu), for an even number of query heads per kv head.
+// As ti_attn_prefill_tc (attn_prefill_tc.cu), for an even number of query heads per kv head; the
+// runs of a split are added by ti_attn_prefill_tc_merge as well (the same scratch layout).
 extern "C" int ti_attn_prefill_tc2(const void* q, int num_tokens, const int* tiles, int num_tiles,
                                    const int* positions, const int* block_table, int bt_stride,
                                    const void* pages, int num_pages, int page_size, int num_heads,
                                    int num_kv_heads, int head_dim, int window, float scale, void* out,
+                                   int splits, float* part_o, float* part_ml,
                                    int* status, int hold_dependents, void* stream) {
     if (num_tiles == 0) return 0;
+    TI_REQUIRE(splits >= 1 && splits <= 8 &&
+               (splits == 1 || (part_o != nullptr && part_ml != nullptr && (uintptr_t)part_o % 16 == 0)),
+               "attn_prefill_tc2: %d runs per tile (1..8) need their 16-byte aligned scratch", splits);
     TI_REQUIRE(ti_attn_prefill_tc2_supported(head_dim, page_size, num_heads, num_kv_heads),
                "attn_prefill_tc2: head_dim %d (128), page size %d (multiple of 16) or heads %d/%d (an even "
                "number per kv head) are not supported", head_dim, page_size, num_heads, num_kv_heads);
@@ -399,9 +432,9 @@ extern "C" int ti_attn_prefill_tc2(const void* q, int num_tokens, const int* til
         if (e != cudaSuccess) return ti_fail("attn_prefill_tc2: %s", cudaGetErrorString(e));
         configured.mark();
     }
-    dim3 grid(num_heads / 2, num_tiles);
+    dim3 grid(num_heads / 2, num_tiles, splits);
     ti_launch_pdl(attn_prefill_tc2_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,
                   tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads, num_kv_heads,
-                  window, run, scale * LOG2E, (bf16*)out, status, hold_dependents);
+                  window, run, scale * LOG2E, (bf16*)out, part_o, part_ml, status, hold_dependents);
     return ti_check_launch("attn_prefill_tc2");
 }

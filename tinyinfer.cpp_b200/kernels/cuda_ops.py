@@ -183,8 +183,7 @@ class CudaOps:
             b.ti_attn_prefill_tc_splits.argtypes = [_i, _i]
             b.ti_attn_prefill_tc_merge.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]
             b.ti_attn_prefill_tc2_supported.argtypes = [_i, _i, _i, _i]
-            b.ti_attn_prefill_tc2.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                              _f, _vp, _vp, _i, _vp]
+            b.ti_attn_prefill_tc2.argtypes = b.ti_attn_prefill_tc.argtypes
             self._tile_rows = (int(b.ti_attn_prefill_tile_rows()), int(b.ti_attn_prefill_tc_tile_rows()))
             self._bf16 = b
         return self._bf16
@@ -645,52 +644,52 @@ class CudaOps:
         if prompt:
             if prompt_tc:
                 tiles = lists[f"portion_tiles_{big}"]
+                n_tiles = tiles.shape[0]
+                pairs_ok = bool(self.bf16.ti_attn_prefill_tc2_supported(head_dim, cache.page_size, num_heads,
+                                                                        num_kv_heads))
                 # many tiles per SM: the kernel that takes two heads of a kv group per block
-                two = (self.tc_attention_pairs_from is not None
-                       and tiles.shape[0] * num_heads >= self.tc_attention_pairs_from * self.num_sms
-                       and self.bf16.ti_attn_prefill_tc2_supported(head_dim, cache.page_size, num_heads,
-                                                                   num_kv_heads))
-                if two:
-                    self._ok(self.bf16.ti_attn_prefill_tc2(
-                        q.data_ptr(), q.shape[0], tiles.data_ptr(), tiles.shape[0],
-                        step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
-                        pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
-                        float(scale), out.data_ptr(), self.status.data_ptr(), int(beside), self._stream()),
-                        self.bf16)
-                    if beside:
-                        run_decode()
-                else:
-                    # few tiles with long rows of keys (a portion of a long prompt): every tile's
-                    # keys in as many runs as fill the SMs, added by a second launch
-                    n_tiles = tiles.shape[0]
-                    runs = (int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads))
-                            if self.split_prompt_keys else 1)
+                two = (self.tc_attention_pairs_from is not None and pairs_ok
+                       and n_tiles * num_heads >= self.tc_attention_pairs_from * self.num_sms)
+                # Fewer (tile, head) pairs than SMs (a portion of a long prompt: few tiles with long
+                # rows of keys): every tile's keys in as many runs as fill the SMs, a block each,
+                # added by a second launch.  With two heads per block a run of a tile takes about
+                # 1.5 times as long and there may be twice as many runs; measured, that pays from
+                # four runs on (a 512-token portion at a context of 16,384: 101 -> 87 us), while two
+                # runs of two heads against the uncut one-head kernel lose at short contexts
+                # (1,024 tokens at 2,048: 28 -> 34 us).
+                runs = 1
+                if not two and self.split_prompt_keys and n_tiles * num_heads < self.num_sms:
+                    runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads))
+                    runs2 = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2)) if pairs_ok else 0
+                    if runs2 > 1.5 * runs and runs2 >= 4:
+                        two, runs = True, runs2
                     if beside and runs > 1:
                         # ... unless all of flash-decoding's blocks find room on the SMs that the
-                        # uncut prompt kernel leaves free: then that kernel's time hides behind them
+                        # uncut one-head kernel leaves free: then that kernel's time hides behind them
                         free = ((self.num_sms - n_tiles * num_heads)
                                 * int(self.bf16.ti_attn_decode_blocks_per_sm(head_dim)))
                         if n_dec * num_kv_heads * self.decode_splits(
                                 n_dec, num_kv_heads, step.max_position or step.max_ctx_len, head_dim) <= free:
-                            runs = 1
-                    part_o = part_ml = None
-                    if runs > 1:
-                        part_o = torch.empty((n_tiles, num_heads, runs, big, head_dim), dtype=torch.float32,
-                                             device=q.device)
-                        part_ml = torch.empty((n_tiles, num_heads, runs, big, 2), dtype=torch.float32,
-                                              device=q.device)
-                    self._ok(self.bf16.ti_attn_prefill_tc(
-                        q.data_ptr(), q.shape[0], tiles.data_ptr(), n_tiles,
-                        step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
-                        pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
-                        float(scale), out.data_ptr(), runs, _ptr(part_o), _ptr(part_ml),
-                        self.status.data_ptr(), int(beside), self._stream()), self.bf16)
-                    if beside:
-                        run_decode()               # (its last block waits for the prompt kernel)
-                    if runs > 1:
-                        self._ok(self.bf16.ti_attn_prefill_tc_merge(
-                            tiles.data_ptr(), n_tiles, num_heads, runs, part_o.data_ptr(), part_ml.data_ptr(),
-                            out.data_ptr(), self._stream()), self.bf16)
+                            two, runs = False, 1
+                part_o = part_ml = None
+                if runs > 1:
+                    part_o = torch.empty((n_tiles, num_heads, runs, big, head_dim), dtype=torch.float32,
+                                         device=q.device)
+                    part_ml = torch.empty((n_tiles, num_heads, runs, big, 2), dtype=torch.float32,
+                                          device=q.device)
+                kernel = self.bf16.ti_attn_prefill_tc2 if two else self.bf16.ti_attn_prefill_tc
+                self._ok(kernel(
+                    q.data_ptr(), q.shape[0], tiles.data_ptr(), n_tiles,
+                    step.positions.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(),
+                    pages.shape[0], cache.page_size, num_heads, num_kv_heads, head_dim, win,
+                    float(scale), out.data_ptr(), runs, _ptr(part_o), _ptr(part_ml),
+                    self.status.data_ptr(), int(beside), self._stream()), self.bf16)
+                if beside:
+                    run_decode()                   # (its last block waits for the prompt kernel)
+                if runs > 1:
+                    self._ok(self.bf16.ti_attn_prefill_tc_merge(
+                        tiles.data_ptr(), n_tiles, num_heads, runs, part_o.data_ptr(), part_ml.data_ptr(),
+                        out.data_ptr(), self._stream()), self.bf16)
             else:
                 self._ok(self.bf16.ti_attn_prefill(
                     q.data_ptr(), tiles.data_ptr(), tiles.shape[0], step.positions.data_ptr(),
