@@ -318,13 +318,50 @@ def test_linear_many_rows_bf16(ops, m, nk):
         ops.check_status()
         want = a.double() @ w.double().T + (base.double() if acc else 0)
         _close(out, want, _sum_rtol(k), f"many rows m={m} n={n} k={k} acc={acc}")
-    # a row's result does not depend on how many rows there are (above the few-rows kernel)
+    # a row's result does not depend on how many rows there are (above the few-rows kernel), as
+    # long as K is cut the same way (an output of few tiles has its K cut into runs)
     if m >= 70:
         part = torch.empty((70, n), device=DEV)
         ops.linear(a[m - 70:], w, part)
         full = torch.empty((m, n), device=DEV)
         ops.linear(a, w, full)
-        assert torch.equal(part, full[m - 70:])
+        if ops.bf16.ti_gemm_tcgen05_splits(70, n, k, 0) == ops.bf16.ti_gemm_tcgen05_splits(m, n, k, 0):
+            assert torch.equal(part, full[m - 70:])
+        else:
+            _close(part, full[m - 70:], _sum_rtol(k), "rows alone against rows among others")
+        keep = ops.split_k_portions
+        try:
+            ops.split_k_portions = False
+            ops.linear(a[m - 70:], w, part)
+            ops.linear(a, w, full)
+            assert torch.equal(part, full[m - 70:])
+        finally:
+            ops.split_k_portions = keep
+
+
+@pytest.mark.parametrize("shape", [(512, 1024, 2048), (512, 1024, 3072), (128, 1024, 2048), (300, 1000, 1096),
+                                   (575, 1024, 3072), (100, 2048, 520), (1024, 1024, 2048)])
+def test_linear_with_k_cut_into_runs(ops, shape):
+    """An output of few tiles (a short prompt portion into a narrow output) has its K cut into
+    runs whose sums a second launch adds in ascending order of K: right against float64, store and
+    accumulate, and the same from call to call; outputs of many tiles are not cut."""
+    m, n, k = shape
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1)
+    base = _rand((m, n), seed=2)
+    runs = ops.bf16.ti_gemm_tcgen05_splits(m, n, k, 0)
+    tiles = -(-m // 128) * -(-n // 128)
+    want_runs = min(8, ops.num_sms // tiles, -(-k // 64) // 4)
+    assert runs == (want_runs if want_runs >= 2 else 1)
+    assert ops.bf16.ti_gemm_tcgen05_splits(m, n, k, 2) == 1        # never with the SwiGLU epilogue
+    for acc in (False, True):
+        out = base.clone()
+        ops.linear(a, w, out, accumulate=acc)
+        again = base.clone()
+        ops.linear(a, w, again, accumulate=acc)
+        ops.check_status()
+        assert torch.equal(out, again)
+        want = a.double() @ w.double().T + (base.double() if acc else 0)
+        _close(out, want, _sum_rtol(k), f"K in {runs} runs m={m} n={n} k={k} acc={acc}")
 
 
 @pytest.mark.parametrize("shape", [(2048, 4096, 1024), (1100, 5000, 520), (2048, 6144, 136), (4096, 2560, 64)])

@@ -16,7 +16,11 @@
 // M, N and K are zero-filled by TMA on the way in and skipped on the way out.
 //
 // The k order of the accumulation is fixed (ascending blocks of 64, 16 at a time), so an
-// output element does not depend on M or on the tile around it.  Every wait on an mbarrier
+// output element does not depend on the tile around it, nor on M as long as K is not cut:
+// an output of so few tiles that most SMs would idle (a short prompt portion into a narrow
+// output: 512 rows x 1,024 columns are 32 tiles of 128 x 128) has its K cut into equal runs, a
+// work unit per (tile, run); a unit stores its sums into its run's slab of a float32 workspace,
+// and a second launch adds the slabs in ascending order of K into C.  Every wait on an mbarrier
 // is bounded: on a timeout the block records status 2, frees its tensor memory and returns.
 #include "qkv_epilogue.cuh"
 
@@ -37,12 +41,20 @@ template <int BN> struct Tile {
 enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2, MODE_QKV = 3 };
 enum { TI_ERR_TIMEOUT = 2 };
 
+// Work unit `unit` of a product whose K is cut into `splits` runs: its tile and its k blocks.
+struct Unit { int tile, run, kb_begin, kb_end; };
+__device__ __forceinline__ Unit unit_of(int unit, int splits, int num_kb) {
+    if (splits == 1) return {unit, 0, 0, num_kb};
+    const int tile = unit / splits, run = unit - tile * splits;
+    return {tile, run, num_kb * run / splits, num_kb * (run + 1) / splits};
+}
+
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ qkv::Epilogue qkv_e, float* __restrict__ c,
                     bf16* __restrict__ out_act, int m, int n, int k, int ldc, int ld_act, int mode,
-                    int* __restrict__ status) {
+                    float* __restrict__ ws, int splits, int* __restrict__ status) {
     using T = Tile<BN>;
     constexpr int STAGES = T::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -60,6 +72,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int num_kb = (k + BK - 1) / BK;
     const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
+    // a work unit: tile unit / splits, k blocks [num_kb * r / splits, num_kb * (r + 1) / splits) for r = unit % splits
+    const int num_units = num_tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -84,18 +98,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // The weights do not depend on the kernel before this one: the first ring-full of W
             // tiles is requested before waiting for it; its results (A) follow after the wait.
             int primed = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && primed < STAGES; tile += gridDim.x) {
-                const int n0 = (tile / tiles_m) * BN;
-                for (int kb = 0; kb < num_kb && primed < STAGES; ++kb, ++primed) {
+            for (int unit = blockIdx.x; unit < num_units && primed < STAGES; unit += gridDim.x) {
+                const Unit u = unit_of(unit, splits, num_kb);
+                const int n0 = (u.tile / tiles_m) * BN;
+                for (int kb = u.kb_begin; kb < u.kb_end && primed < STAGES; ++kb, ++primed) {
                     mbar_expect_tx(&full[primed], T::STAGE_A + T::STAGE_B);
                     tma_load_2d(stage_b + primed * T::STAGE_B, &map_w, &full[primed], kb * BK, n0);
                 }
             }
             pdl_wait();
             int it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+                const Unit u = unit_of(unit, splits, num_kb);
+                const int m0 = (u.tile % tiles_m) * BM, n0 = (u.tile / tiles_m) * BN;
+                for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= primed) {
                         ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
@@ -113,13 +129,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
                                    ((unsigned)(BM >> 4) << 24);
             int it = 0, local = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++local) {
+                const Unit u = unit_of(unit, splits, num_kb);
+                const int kb_begin = u.kb_begin, kb_end = u.kb_end;
                 const int buf = local & 1;
                 ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1);   // the epilogue has read it
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&full[s], (it / STAGES) & 1);
                     if (!ok) break;
@@ -130,7 +148,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // 16 elements of K = 32 bytes further inside the swizzled row
                         umma_bf16(tmem_acc, da + (unsigned long long)(kk * UMMA_K * 2 >> 4),
-                                  db + (unsigned long long)(kk * UMMA_K * 2 >> 4), idesc, (kb | kk) != 0);
+                                  db + (unsigned long long)(kk * UMMA_K * 2 >> 4), idesc, kb != kb_begin || kk != 0);
                     }
                     umma_commit(&empty[s]);           // the stage is free once these MMAs have read it
                 }
@@ -142,7 +160,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int col_half = (warp - 2) >> 2;         // two warps share a quarter: half of the columns each
         pdl_wait();                                   // C and what the QKV epilogue reads belong to the chain
         int local = 0;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++local) {
+            const Unit u = unit_of(unit, splits, num_kb);
+            const int tile = u.tile;
+            if (splits > 1) {                     // this run's sums go to its slab of the workspace as they are
+                c = ws + (size_t)u.run * m * n;
+                ldc = n;
+                mode = MODE_STORE;
+            }
             const int buf = local & 1;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const int row = m0 + quarter * 32 + lane;
@@ -263,9 +288,48 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     table[(size_t)t * 2 * half + half + k] = sn;
 }
 
+// c (+)= the sum of the runs' slabs ws[run][m][n], in ascending order of the run (of K).
+__global__ void __launch_bounds__(256)
+gemm_split_merge_kernel(const float* __restrict__ ws, float* __restrict__ c, int m, int n, int ldc, int splits,
+                        int accumulate) {
+    pdl_launch();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // a float4 of the output
+    const int n4 = n / 4;
+    pdl_wait();
+    if (i >= (long long)m * n4) return;
+    const int row = (int)(i / n4), col = (int)(i % n4) * 4;
+    const size_t slab = (size_t)m * n;
+    const float* src = ws + (size_t)row * n + col;
+    float4 was = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (accumulate) was = __ldcg(reinterpret_cast<const float4*>(c + (size_t)row * ldc + col));
+    float4 sum = __ldcg(reinterpret_cast<const float4*>(src));
+    for (int r = 1; r < splits; ++r) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + r * slab));
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    *reinterpret_cast<float4*>(c + (size_t)row * ldc + col) =
+        make_float4(was.x + sum.x, was.y + sum.y, was.z + sum.z, was.w + sum.w);
+}
+
+constexpr int MAX_SPLITS = 8, MIN_RUN_KB = 4, MIN_SPLITS = 2;
+
+// In how many runs K is cut: when the 128 x 128 tiles of the output would leave three quarters
+// of the SMs idle, so many that the (tile, run) units fill them once; never runs of fewer than
+// MIN_RUN_KB k blocks; 1 = not cut.
+int choose_splits(int m, int n, int k, int mode, int sms) {
+    if (mode != MODE_STORE && mode != MODE_ACCUMULATE) return 1;
+    if (n % 4) return 1;
+    const int tiles = ((m + BM - 1) / BM) * ((n + 127) / 128), num_kb = (k + BK - 1) / BK;
+    int s = sms / tiles;
+    if (s > MAX_SPLITS) s = MAX_SPLITS;
+    if (s > num_kb / MIN_RUN_KB) s = num_kb / MIN_RUN_KB;
+    return s >= MIN_SPLITS ? s : 1;
+}
+
 // width: the tiles' columns, 256, 128 or 64
 int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c, void* out_act, int m, int n,
-                 int k, int lda, int ldw, int ldc, int ld_act, int mode, int width, int* status, void* stream) {
+                 int k, int lda, int ldw, int ldc, int ld_act, int mode, int width, float* ws, int splits,
+                 int* status, void* stream) {
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -287,19 +351,29 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
         configured.mark();
     }
     if (width == 256) {
-        const int tiles = tiles_m * ((n + 255) / 256);
+        const int tiles = tiles_m * ((n + 255) / 256) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<256>, tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM,
-                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
+                      splits, status);
     } else if (width == 128) {
-        const int tiles = tiles_m * ((n + 127) / 128);
+        const int tiles = tiles_m * ((n + 127) / 128) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<128>, tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM,
-                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
+                      splits, status);
     } else {
-        const int tiles = tiles_m * ((n + 63) / 64);
+        const int tiles = tiles_m * ((n + 63) / 64) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<64>, tiles < sms ? tiles : sms, THREADS, Tile<64>::SMEM,
-                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, status);
+                      (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
+                      splits, status);
     }
-    return ti_check_launch("gemm_tcgen05");
+    if (int rc = ti_check_launch("gemm_tcgen05")) return rc;
+    if (splits > 1) {
+        const long long quads = (long long)m * (n / 4);
+        ti_launch_pdl(gemm_split_merge_kernel, (unsigned)((quads + 255) / 256), 256, 0, (cudaStream_t)stream,
+                      (const float*)ws, c, m, n, ldc, splits, mode == MODE_ACCUMULATE ? 1 : 0);
+        return ti_check_launch("gemm_split_merge");
+    }
+    return 0;
 }
 
 }  // namespace
@@ -310,10 +384,20 @@ extern "C" int ti_gemm_tcgen05_supported(int m, int n, int k, int lda, int ldw, 
     return n % 4 == 0 && ldc % 4 == 0;
 }
 
+// The runs of K that ti_gemm_tcgen05 would like for these sizes (1: K is not cut); with more than
+// one it wants runs * m * n float32 values of scratch.
+extern "C" int ti_gemm_tcgen05_splits(int m, int n, int k, int mode) {
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return sms > 0 && m > 0 && n > 0 ? choose_splits(m, n, k, mode, sms) : 1;
+}
+
 // mode 0: c = a w^T; 1: c += a w^T; 2: out_act[m, n/2] = SwiGLU over groups of 8 gate + 8 up columns.
+// ws: null, or the scratch for ti_gemm_tcgen05_splits(m, n, k, mode) runs of K (16-byte aligned).
 extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out_act, int m, int n,
-                               int k, int lda, int ldw, int ldc, int ld_act, int mode, int* status,
-                               void* stream) {
+                               int k, int lda, int ldw, int ldc, int ld_act, int mode, float* ws,
+                               int* status, void* stream) {
     if (m == 0 || n == 0) return 0;
     TI_REQUIRE(mode >= MODE_STORE && mode <= MODE_SWIGLU, "gemm_tcgen05: mode %d", mode);
     TI_REQUIRE(ti_gemm_tcgen05_supported(m, n, k, lda, ldw, ldc, mode),
@@ -329,8 +413,15 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     // wide tiles when they still give every SM one; else twice as many narrow ones; else, when
     // those still leave more than half of the SMs idle, four times as many of 64 columns
     const int tiles_m = (m + BM - 1) / BM;
+    const int splits = ws != nullptr ? choose_splits(m, n, k, mode, sms) : 1;
+    if (splits > 1) {
+        TI_REQUIRE((uintptr_t)ws % 16 == 0, "gemm_tcgen05: the scratch must be 16-byte aligned");
+        return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, 128, ws,
+                            splits, status, stream);
+    }
     const int width = tiles_m * ((n + 255) / 256) >= sms ? 256 : tiles_m * ((n + 127) / 128) * 2 >= sms ? 128 : 64;
-    return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, width, status, stream);
+    return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, width, nullptr, 1,
+                        status, stream);
 }
 
 // The QKV product of a prompt portion with the epilogue of qkv_epilogue.cuh (head size 128), on
@@ -350,7 +441,7 @@ extern "C" int ti_gemm_tcgen05_qkv(const void* a, const void* w, int m, int k, i
                (uintptr_t)k_weight % 16 == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned, q_out and the pages 32-byte");
     const qkv::Epilogue e{q_weight, k_weight, eps, table, positions, req_of_tok, block_table, bt_stride,
                           (bf16*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, (bf16*)q_out};
-    return launch_tiles(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, 256, status, stream);
+    return launch_tiles(a, w, e, nullptr, nullptr, m, n, k, lda, ldw, 0, 0, MODE_QKV, 256, nullptr, 1, status, stream);
 }
 
 // table [num_tokens][2][half] float32: cosines then sines of positions[t] * inv_freq[k].

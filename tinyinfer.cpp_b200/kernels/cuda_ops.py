@@ -105,6 +105,9 @@ class CudaOps:
         # a step with fewer (tile, head) pairs of prompt attention than SMs: the keys of every
         # tile cut into runs, one block each, added by a second launch
         self.split_prompt_keys = True
+        # a product of many rows whose output has few tiles (a short prompt portion into a narrow
+        # output): K cut into runs, added by a second launch
+        self.split_k_portions = True
         # the feed-forward of a decode step of at most 16 rows as one launch, when a layer's
         # feed-forward weights fit into the GPU's shared memory (csrc/ffn_decode.cu); same bits as
         # the two products it replaces
@@ -166,7 +169,8 @@ class CudaOps:
             b.ti_attn_decode_qkv_supported.argtypes = [_i, _i, _i]
             b.ti_attn_decode_qkv.argtypes = [_vp, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i,
                                              _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
-            b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
+            b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]
+            b.ti_gemm_tcgen05_splits.argtypes = [_i, _i, _i, _i]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             qkv_args = [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
@@ -246,6 +250,19 @@ class CudaOps:
         if self.use_2sm_gemm and tiles >= self.pair_min_tiles:
             return self.bf16.ti_gemm_tcgen05_2sm
         return self.bf16.ti_gemm_tcgen05
+
+    def _run_tc_gemm(self, a, w, c, out_act, m, n, k, ldc, ld_act, mode) -> None:
+        """The tcgen05 product of many rows; an output of few tiles has its K cut into runs that a
+        second launch adds (the one-SM kernel decides, this side brings the scratch)."""
+        fn = self._tc_gemm(m, n)
+        if fn is self.bf16.ti_gemm_tcgen05_2sm:
+            self._ok(fn(a.data_ptr(), w.data_ptr(), _ptr(c), _ptr(out_act), m, n, k, a.stride(0), w.stride(0),
+                        ldc, ld_act, mode, self.status.data_ptr(), self._stream()), self.bf16)
+            return
+        runs = int(self.bf16.ti_gemm_tcgen05_splits(m, n, k, mode)) if self.split_k_portions else 1
+        ws = torch.empty(runs * m * n, dtype=torch.float32, device=a.device) if runs > 1 else None
+        self._ok(fn(a.data_ptr(), w.data_ptr(), _ptr(c), _ptr(out_act), m, n, k, a.stride(0), w.stride(0),
+                    ldc, ld_act, mode, _ptr(ws), self.status.data_ptr(), self._stream()), self.bf16)
 
     def _few_tc(self, a, w, c, out_act, mode) -> bool:
         """Runs the split-K tcgen05 product for few rows if it applies to these operands."""
@@ -356,10 +373,7 @@ class CudaOps:
             if (m > 64 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and
                     out.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                         m, n, k, a.stride(0), w.stride(0), out.stride(0), mode)):
-                self._ok(self._tc_gemm(m, n)(
-                    a.data_ptr(), w.data_ptr(), out.data_ptr(), None, m, n, k, a.stride(0),
-                    w.stride(0), out.stride(0), 0, mode, self.status.data_ptr(), self._stream()),
-                    self.bf16)
+                self._run_tc_gemm(a, w, out, None, m, n, k, out.stride(0), 0, mode)
                 return
         self._ok(self.core.ti_gemm_simple(
             a.data_ptr(), _code(a, "linear"), w.data_ptr(), _code(w, "linear"), out.data_ptr(),
@@ -384,10 +398,7 @@ class CudaOps:
         if (interleaved and m > 64 and h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
                 and inter % 8 == 0 and out.stride(0) % 8 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                     m, 2 * inter, k, h.stride(0), w_gate_up.stride(0), 0, 2)):
-            self._ok(self._tc_gemm(m, 2 * inter)(
-                h.data_ptr(), w_gate_up.data_ptr(), None, out.data_ptr(), m, 2 * inter, k,
-                h.stride(0), w_gate_up.stride(0), 0, out.stride(0), 2, self.status.data_ptr(),
-                self._stream()), self.bf16)
+            self._run_tc_gemm(h, w_gate_up, None, out, m, 2 * inter, k, 0, out.stride(0), 2)
             return
         gu = torch.empty((m, 2 * inter), dtype=torch.float32, device=h.device)
         self.linear(h, w_gate_up, gu)
