@@ -311,19 +311,29 @@ gemm_split_merge_kernel(const float* __restrict__ ws, float* __restrict__ c, int
         make_float4(was.x + sum.x, was.y + sum.y, was.z + sum.z, was.w + sum.w);
 }
 
-constexpr int MAX_SPLITS = 8, MIN_RUN_KB = 4, MIN_SPLITS = 2;
+constexpr int MAX_SPLITS = 8, MIN_RUN_KB = 4;
 
-// In how many runs K is cut: when the 128 x 128 tiles of the output would leave three quarters
-// of the SMs idle, so many that the (tile, run) units fill them once; never runs of fewer than
-// MIN_RUN_KB k blocks; 1 = not cut.
+// In how many runs K is cut (1 = not at all): the count with the shortest estimated time, if that
+// is a twentieth shorter than the uncut product's.  The estimate, in microseconds, from timings of
+// this kernel on a B200: the (tile, run) units go over the SMs in waves; a wave costs 1.5 plus
+// 0.3 per k block of a run (a 128 x 128 tile takes in 32 KB per k block); the launch that adds
+// the runs costs 2.5 plus the reading of the runs' slabs and of C and the writing of C at 4 TB/s.
+// It depends on the product's sizes and the number of SMs alone.
 int choose_splits(int m, int n, int k, int mode, int sms) {
     if (mode != MODE_STORE && mode != MODE_ACCUMULATE) return 1;
     if (n % 4) return 1;
     const int tiles = ((m + BM - 1) / BM) * ((n + 127) / 128), num_kb = (k + BK - 1) / BK;
-    int s = sms / tiles;
-    if (s > MAX_SPLITS) s = MAX_SPLITS;
-    if (s > num_kb / MIN_RUN_KB) s = num_kb / MIN_RUN_KB;
-    return s >= MIN_SPLITS ? s : 1;
+    const double slab_us = (double)m * n * 4.0 / 4.0e6;
+    int best = 1;
+    double best_us = 0.0, uncut_us = 0.0;
+    for (int s = 1; s <= MAX_SPLITS && (s == 1 || s * MIN_RUN_KB <= num_kb); ++s) {
+        const int waves = (tiles * s + sms - 1) / sms;
+        double us = waves * (1.5 + 0.3 * ((num_kb + s - 1) / s));
+        if (s > 1) us += 2.5 + (s + 2) * slab_us;
+        if (s == 1) uncut_us = us;
+        if (s == 1 || us < best_us) { best = s; best_us = us; }
+    }
+    return best_us <= 0.95 * uncut_us ? best : 1;
 }
 
 // width: the tiles' columns, 256, 128 or 64
