@@ -31,13 +31,13 @@ SHARPEN = 1.4          # factor on q_norm and k_norm: scores spread twice as wid
 SEED = 5
 
 
-def _engines(max_tokens, max_requests, page_size=64, **kw):
+def _engines(max_tokens, max_requests, page_size=64, config=None, **kw):
     """A bfloat16 and a float32 engine with the same random weights (the device generator is
     seeded per tensor name), attention sharpened in both."""
     from tinyinfer_b200 import Engine
     pair = []
     for dtype in ("bfloat16", "float32"):
-        eng = Engine(config=BENCH_SHAPE, seed=SEED, dtype=dtype, page_size=page_size,
+        eng = Engine(config=config or BENCH_SHAPE, seed=SEED, dtype=dtype, page_size=page_size,
                      max_tokens=max_tokens, max_requests=max_requests,
                      **(kw if dtype == "bfloat16" else {}))
         for blk in eng.model.blocks:
@@ -122,6 +122,29 @@ def test_long_prompt_with_two_heads_per_attention_block():
         fp.finish("p")
         bf.finish("p")
     assert bf.ops.launches > before
+    bf.ops.check_status()
+
+
+def test_portions_that_reach_far_back():
+    """Portions of a prompt past 6,144 keys (the step's `long_portions`) take the two-heads
+    attention kernel, with the keys of their tiles cut into runs when there are fewer blocks than
+    SMs; shorter ones the one-head kernel, cut as well.  Against the 32-bit engine, eagerly and
+    from the steps' graphs (a shape's graph is kept per class)."""
+    from tinyinfer_b200 import StepEntry
+    bf, fp = _engines(8192, 1, config=dict(BENCH_SHAPE, max_position_embeddings=8192), step_graphs=True)
+    toks = _tokens(5120 + 5 * 512, seed=91)
+    head = [StepEntry("p", toks[:5120], [])]
+    bf.step(head)
+    fp.step(head)
+    classes = set()
+    for i in range(5):                     # contexts 5,632 and 6,144: not long; 6,656 to 7,680: long
+        lo = 5120 + i * 512
+        entries = [StepEntry("p", toks[lo:lo + 512], [0, 130, 511])]
+        want = fp.step(entries)
+        got = bf.step(entries).clone()
+        _check(got, want, f"512-token portion ending at {lo + 512}")
+        classes.add(lo + 512 > 6144)
+    assert classes == {False, True} and len(bf._step_graphs.graphs) == 2
     bf.ops.check_status()
 
 

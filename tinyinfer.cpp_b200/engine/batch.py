@@ -56,6 +56,9 @@ class StepBatch:
     ctx_lens: list[int]
     max_q_len: int
     max_ctx_len: int
+    # whether a request that brings several tokens reaches past LONG_CONTEXT keys: kernels may
+    # choose by it (a step's graph is kept per class, since the choice is captured with it)
+    long_portions: bool
     # device tensors, int32
     token_ids: torch.Tensor          # [T]
     positions: torch.Tensor          # [T] absolute position of each token in its request
@@ -85,6 +88,14 @@ def build_lists(lists: Sequence[StepList], q_lens: Sequence[int], starts: Sequen
             raise ValueError(f"two step lists are named {sl.name!r}")
         out[sl.name] = arr.astype(np.int64, copy=False)
     return out
+
+
+LONG_CONTEXT = 6144     # keys: from here on a prompt portion's attention is a long walk over keys
+
+
+def long_portions(q_lens, ctx_lens) -> bool:
+    """Whether any request that brings several tokens ends past LONG_CONTEXT keys."""
+    return any(n > 1 and c > LONG_CONTEXT for n, c in zip(q_lens, ctx_lens))
 
 
 def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
@@ -159,6 +170,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         num_tokens=t, num_requests=r, num_logit_rows=k, act_dtype=act_dtype,
         q_lens=q_lens, q_starts=list(starts), ctx_lens=ctx,
         max_q_len=max(q_lens, default=0), max_ctx_len=max(ctx, default=0),
+        long_portions=long_portions(q_lens, ctx),
         token_ids=view("tok"), positions=view("pos"), req_of_tok=view("roft"), cu_q=view("cu"),
         q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
         state_slots=view("slots"),

@@ -669,7 +669,17 @@ class CudaOps:
                 # runs of two heads against the uncut one-head kernel lose at short contexts
                 # (1,024 tokens at 2,048: 28 -> 34 us).
                 runs = 1
-                if not two and self.split_prompt_keys and n_tiles * num_heads < self.num_sms:
+                # Portions that reach far back (the step's `long_portions`): every block walks a
+                # long row of keys, where the two-heads kernel's shorter time per head and tile
+                # counts and its longer start does not (2,048 tokens at a context of 16,384: 350 ->
+                # 287 us; at 4,096 the two are equal, below it the one-head kernel wins); with fewer
+                # blocks than SMs it cuts the keys into runs.
+                if (not two and pairs_ok and getattr(step, "long_portions", False) and not win
+                        and self.tc_attention_pairs_from is not None):
+                    two = True
+                    if self.split_prompt_keys:
+                        runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2))
+                elif not two and self.split_prompt_keys and n_tiles * num_heads < self.num_sms:
                     runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads))
                     runs2 = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2)) if pairs_ok else 0
                     if runs2 > 1.5 * runs and runs2 >= 4:
