@@ -200,21 +200,22 @@ def test_mixed_step_of_decoding_rows_beside_a_long_portion():
     bf.ops.check_status()
 
 
-@pytest.mark.parametrize("decoders", [3, 8, 40])
-def test_decoding_rows_run_beside_a_portion_with_the_same_bits(decoders):
+@pytest.mark.parametrize("decoders,before", [(3, 384), (8, 384), (40, 384), (5, 6400)])
+def test_decoding_rows_run_beside_a_portion_with_the_same_bits(decoders, before):
     """In a step of single-token rows and a prompt portion, flash-decoding is released by the
     prompt-attention kernel after that kernel's own wait and runs beside it, with one block
     waiting for it at the end.  The logits are those of the two kernels one after the other,
-    eagerly and replayed from the step's graph."""
+    eagerly and replayed from the step's graph; with 6,400 earlier tokens the portion takes the
+    two-heads kernel."""
     from tinyinfer_b200 import Engine, StepEntry
-    eng = Engine(config=BENCH_SHAPE, seed=SEED, dtype="bfloat16", max_tokens=decoders * 512 + 2048,
-                 max_requests=decoders + 1, step_graphs=True)
+    eng = Engine(config=dict(BENCH_SHAPE, max_position_embeddings=8192), seed=SEED, dtype="bfloat16",
+                 max_tokens=decoders * 512 + before + 1664, max_requests=decoders + 1, step_graphs=True)
     for blk in eng.model.blocks:
         blk.mixer.q_norm.mul_(SHARPEN)
         blk.mixer.k_norm.mul_(SHARPEN)
     ids = [f"s{i}" for i in range(decoders)]
     prompts = [_tokens(200 + 37 * (i % 7), seed=500 + i) for i in range(decoders)]
-    long_prompt = _tokens(384 + 3 * 300, seed=78)
+    long_prompt = _tokens(before + 3 * 300, seed=78)
     assert eng.ops.attention_side_by_side
     logits = {}
     try:
@@ -223,10 +224,10 @@ def test_decoding_rows_run_beside_a_portion_with_the_same_bits(decoders):
             eng.ops.attention_side_by_side = beside
             for lo in range(0, decoders, 4):
                 eng.step([StepEntry(ids[i], prompts[i], []) for i in range(lo, min(decoders, lo + 4))])
-            eng.step([StepEntry("long", long_prompt[:384], [])])
+            eng.step([StepEntry("long", long_prompt[:before], [])])
             outs = []
             for i in range(3):                          # the third is replayed from the graph
-                lo = 384 + i * 300
+                lo = before + i * 300
                 entries = [StepEntry(r, [(5 * i + 13 * k) % 1000], [0]) for k, r in enumerate(ids)]
                 entries.append(StepEntry("long", long_prompt[lo:lo + 300], [0, 150, 299]))
                 outs.append(eng.step(entries).clone())
