@@ -84,7 +84,9 @@ class CudaOps:
         self._counters = None
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
-        self.pair_min_tiles = torch.cuda.get_device_properties(self.device).multi_processor_count // 2
+        # (from about a third of the pairs busy on: a gate/up product of 512 rows, 48 pair tiles,
+        # takes 10.5 against 12.6 us; at 32 pair tiles and fewer the one-SM kernel is ahead)
+        self.pair_min_tiles = torch.cuda.get_device_properties(self.device).multi_processor_count * 3 // 10
         self.fuse_qkv_epilogue = True     # the prompt QKV product norms, rotates and stores its heads
         # steps of single tokens: flash-decoding norms, rotates and stores by itself, one launch less
         # per layer.  Off: measured equal to the separate kernels within 1 % at batch 8 and 4 %
