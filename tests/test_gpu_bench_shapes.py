@@ -126,7 +126,7 @@ def test_long_prompt_with_two_heads_per_attention_block():
 
 
 def test_portions_that_reach_far_back():
-    """Portions of a prompt past 6,144 keys (the step's `long_portions`) take the two-heads
+    """Portions of a prompt past 6,144 keys (the step's `portion_reach` 2) take the two-heads
     attention kernel, with the keys of their tiles cut into runs when there are fewer blocks than
     SMs; shorter ones the one-head kernel, cut as well.  Against the 32-bit engine, eagerly and
     from the steps' graphs (a shape's graph is kept per class)."""

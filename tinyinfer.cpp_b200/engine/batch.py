@@ -56,9 +56,10 @@ class StepBatch:
     ctx_lens: list[int]
     max_q_len: int
     max_ctx_len: int
-    # whether a request that brings several tokens reaches past LONG_CONTEXT keys: kernels may
-    # choose by it (a step's graph is kept per class, since the choice is captured with it)
-    long_portions: bool
+    # how far back the requests that bring several tokens reach (0: at most SHORT_CONTEXT keys,
+    # 1: at most LONG_CONTEXT, 2: further): kernels may choose by it (a step's graph is kept per
+    # class, since the choice is captured with it)
+    portion_reach: int
     # device tensors, int32
     token_ids: torch.Tensor          # [T]
     positions: torch.Tensor          # [T] absolute position of each token in its request
@@ -90,12 +91,15 @@ def build_lists(lists: Sequence[StepList], q_lens: Sequence[int], starts: Sequen
     return out
 
 
-LONG_CONTEXT = 6144     # keys: from here on a prompt portion's attention is a long walk over keys
+SHORT_CONTEXT = 1536    # keys: up to here a prompt portion's attention walks few tiles of keys
+LONG_CONTEXT = 6144     # keys: from here on it is a long walk
 
 
-def long_portions(q_lens, ctx_lens) -> bool:
-    """Whether any request that brings several tokens ends past LONG_CONTEXT keys."""
-    return any(n > 1 and c > LONG_CONTEXT for n, c in zip(q_lens, ctx_lens))
+def portion_reach(q_lens, ctx_lens) -> int:
+    """The class of a step by the longest context of a request that brings several tokens:
+    0 up to SHORT_CONTEXT keys (or no such request), 1 up to LONG_CONTEXT, 2 beyond."""
+    far = max((c for n, c in zip(q_lens, ctx_lens) if n > 1), default=0)
+    return 0 if far <= SHORT_CONTEXT else 1 if far <= LONG_CONTEXT else 2
 
 
 def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
@@ -170,7 +174,7 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int],
         num_tokens=t, num_requests=r, num_logit_rows=k, act_dtype=act_dtype,
         q_lens=q_lens, q_starts=list(starts), ctx_lens=ctx,
         max_q_len=max(q_lens, default=0), max_ctx_len=max(ctx, default=0),
-        long_portions=long_portions(q_lens, ctx),
+        portion_reach=portion_reach(q_lens, ctx),
         token_ids=view("tok"), positions=view("pos"), req_of_tok=view("roft"), cu_q=view("cu"),
         q_start_dev=view("qs"), ctx_len_dev=view("ctx"), logit_rows=view("rows"),
         state_slots=view("slots"),

@@ -82,7 +82,7 @@ class _Bucket:
         self.batch = StepBatch(
             num_tokens=b, num_requests=b, num_logit_rows=b, act_dtype=engine.dtype,
             q_lens=[1] * b, q_starts=[0] * b, ctx_lens=[engine.plan.max_position] * b,
-            max_q_len=1, max_ctx_len=engine.plan.max_position, long_portions=False,
+            max_q_len=1, max_ctx_len=engine.plan.max_position, portion_reach=0,
             token_ids=d[0:b], positions=d[b:2 * b], req_of_tok=ar,
             cu_q=torch.arange(b + 1, dtype=torch.int32, device=dev),
             q_start_dev=d[b:2 * b], ctx_len_dev=d[2 * b:3 * b], logit_rows=ar,
@@ -270,10 +270,10 @@ class StepGraphs(_OfEngine):
     def run(self, entries, starts, tables, slots):
         """Logits of the step, or None if the step should run eagerly (a shape seen for the first time)."""
         eng = self.engine
-        from .batch import long_portions
+        from .batch import portion_reach
         lens = [len(e.tokens) for e in entries]
         key = (tuple(lens), tuple(tuple(e.want) for e in entries),
-               long_portions(lens, [s + n for s, n in zip(starts, lens)]))
+               portion_reach(lens, [s + n for s, n in zip(starts, lens)]))
         ent = self.graphs.get(key)
         build = dict(act_dtype=eng.dtype, device=eng.device, min_blocks=self.width,
                      max_position=eng.plan.max_position, lists=eng.step_lists)

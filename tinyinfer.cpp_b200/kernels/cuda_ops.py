@@ -663,25 +663,26 @@ class CudaOps:
                 # many tiles per SM: the kernel that takes two heads of a kv group per block
                 two = (self.tc_attention_pairs_from is not None and pairs_ok
                        and n_tiles * num_heads >= self.tc_attention_pairs_from * self.num_sms)
-                # Fewer (tile, head) pairs than SMs (a portion of a long prompt: few tiles with long
-                # rows of keys): every tile's keys in as many runs as fill the SMs, a block each,
+                # Fewer (tile, head) pairs than SMs and rows of more than a few key tiles (a portion of
+                # a long prompt; `portion_reach` 1 or 2): every tile's keys in as many runs as fill the SMs, a block each,
                 # added by a second launch.  With two heads per block a run of a tile takes about
                 # 1.5 times as long and there may be twice as many runs; measured, that pays from
                 # four runs on (a 512-token portion at a context of 16,384: 101 -> 87 us), while two
                 # runs of two heads against the uncut one-head kernel lose at short contexts
                 # (1,024 tokens at 2,048: 28 -> 34 us).
                 runs = 1
-                # Portions that reach far back (the step's `long_portions`): every block walks a
+                reach = getattr(step, "portion_reach", 1)   # 0: few key tiles per row, 2: a long walk
+                # Portions that reach far back (the step's `portion_reach` 2): every block walks a
                 # long row of keys, where the two-heads kernel's shorter time per head and tile
                 # counts and its longer start does not (2,048 tokens at a context of 16,384: 350 ->
                 # 287 us; at 4,096 the two are equal, below it the one-head kernel wins); with fewer
                 # blocks than SMs it cuts the keys into runs.
-                if (not two and pairs_ok and getattr(step, "long_portions", False) and not win
+                if (not two and pairs_ok and reach == 2 and not win
                         and self.tc_attention_pairs_from is not None):
                     two = True
                     if self.split_prompt_keys:
                         runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2))
-                elif not two and self.split_prompt_keys and n_tiles * num_heads < self.num_sms:
+                elif not two and self.split_prompt_keys and reach >= 1 and n_tiles * num_heads < self.num_sms:
                     runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads))
                     runs2 = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2)) if pairs_ok else 0
                     if runs2 > 1.5 * runs and runs2 >= 4:
