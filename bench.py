@@ -19,7 +19,8 @@ prefill    one request's 2,048-token prompt in one step: tokens a second and the
 roofline   the bytes a decode step has to read (every weight once, and the keys and values of
            the live requests) / its time, against the copy bandwidth;
 points     decode tokens a second at batch 1 and 64, the same steps without a CUDA graph, a mixed
-           step (63 requests decoding beside a 512-token portion); then, as `page16_*`, `8b_*` and
+           step (63 requests decoding beside a 512-token portion of a prompt that ends between
+           3,072 and 4,096 tokens); then, as `page16_*`, `8b_*` and
            `32b_*`, the page size of 16 tokens and the Qwen3-8B and Qwen3-32B shapes (decode at
            batch 1, 8, 64, the 2,048-token prefill, the 8B mixed step);
 points_frac  for each point its fraction of its roofline (decode: bytes / time / copy bandwidth;
@@ -293,25 +294,28 @@ def measure_prefill(engine, tokens, reps, torch):
 def measure_mixed(engine, decoders, chunk, context, torch):
     """One step with ``decoders`` requests decoding near ``context`` and a portion of ``chunk``
     tokens of another request's prompt beside them (the step shape of chunked prefill under
-    load).  The portion moves along its prompt from step to step; the first three steps run
-    eagerly and capture the shape's graph.  Returns ms per step (median)."""
+    load).  The prompt's first tokens run alone; then five portions follow beside the decoders, the
+    last one ending at ``context``: the first two steps run eagerly and capture the shape's
+    graph, the other three are timed.  Returns ms per step (median)."""
     from tinyinfer_b200 import StepEntry
     g = torch.Generator().manual_seed(2)
-    timed = max(1, min(5, context // chunk - 3))
-    ids = fill_requests(engine, decoders, context - timed - 5, torch)
-    prompt = torch.randint(0, engine.plan.vocab_size, ((timed + 3) * chunk,), generator=g).tolist()
+    steps, timed = 5, 3
+    lead = max(chunk, context - steps * chunk)
+    ids = fill_requests(engine, decoders, context - steps - 2, torch)
+    prompt = torch.randint(0, engine.plan.vocab_size, (lead + steps * chunk,), generator=g).tolist()
     times = []
     try:
-        for i in range(timed + 3):
+        engine.step([StepEntry(("bench", "prompt"), prompt[:lead], [])])
+        for i in range(steps):
             entries = [StepEntry(r, [1], [0]) for r in ids]
-            entries.append(StepEntry(("bench", "prompt"), prompt[i * chunk:(i + 1) * chunk], []))
+            entries.append(StepEntry(("bench", "prompt"), prompt[lead + i * chunk:lead + (i + 1) * chunk], []))
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
             engine.step(entries)
             stop.record()
             torch.cuda.synchronize()
-            if i >= 3:
+            if i >= steps - timed:
                 times.append(start.elapsed_time(stop))
     finally:
         for r in ids + [("bench", "prompt")]:

@@ -53,7 +53,7 @@ class RefOps:
         gate, up = gu[:, :inter], gu[:, inter:]
         out.copy_((gate / (1.0 + torch.exp(-gate)) * up).to(out.dtype))
 
-    def swiglu_ffn(self, h, w_gate_up, w_down, residual):
+    def swiglu_ffn(self, h, w_gate_up, w_down, residual, may_defer=False):
         y = torch.empty((h.shape[0], w_down.shape[1]), dtype=h.dtype, device=h.device)
         self.gate_up_swiglu(h, w_gate_up, y)
         self.linear(y, w_down, residual, accumulate=True)

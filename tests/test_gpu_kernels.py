@@ -366,6 +366,47 @@ def test_linear_with_k_cut_into_runs(ops, shape):
         _close(out, want, _sum_rtol(k), f"K in {runs} runs m={m} n={n} k={k} acc={acc}")
 
 
+@pytest.mark.parametrize("shape", [(512, 1024, 2048), (128, 1024, 3072), (300, 1000, 2056), (100, 4096, 4096)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_norm_that_adds_the_runs_of_a_cut_product(ops, shape, accumulate):
+    """A product whose K is cut, asked for with ``may_defer``, leaves its runs to the norm of its
+    output that follows: output and normed rows have the bits of product, adding launch and
+    norm in turn, with one launch less; anything else that follows adds the runs first."""
+    m, n, k = shape
+    a, w = _rand((m, k), torch.bfloat16), _rand((n, k), torch.bfloat16, seed=1, scale=0.05)
+    base = _rand((m, n), seed=2)
+    norm_w = 1.0 + 0.1 * _rand((n,), torch.float32, seed=3)
+    assert ops.bf16.ti_gemm_tcgen05_splits(m, n, k, int(accumulate)) > 1
+    keep = ops.norm_adds_runs
+    res, normed, launches = {}, {}, {}
+    try:
+        for fused in (False, True):
+            ops.norm_adds_runs = fused
+            res[fused] = base.clone()
+            normed[fused] = torch.zeros((m, n), dtype=torch.bfloat16, device=DEV)
+            before = ops.launches
+            ops.linear(a, w, res[fused], accumulate=accumulate, may_defer=True)
+            ops.rmsnorm(res[fused], norm_w, 1e-6, normed[fused])
+            ops.flush()
+            launches[fused] = ops.launches - before
+        # something else than the norm of that output comes next: the runs are added first
+        other = base.clone()
+        ops.linear(a, w, other, accumulate=accumulate, may_defer=True)
+        h = torch.zeros((m, n), dtype=torch.bfloat16, device=DEV)
+        ops.rmsnorm(base.clone(), norm_w, 1e-6, h)
+        assert ops._pending_runs is None and torch.equal(other, res[False])
+        ops.linear(a, w, other, accumulate=False, may_defer=True)
+        ops.flush()
+        assert ops._pending_runs is None
+    finally:
+        ops.norm_adds_runs = keep
+    ops.check_status()
+    assert torch.equal(res[True], res[False]) and torch.equal(normed[True], normed[False])
+    assert launches[False] - launches[True] == 1
+    want = a.double() @ w.double().T + (base.double() if accumulate else 0)
+    _close(res[True], want, _sum_rtol(k), f"cut product m={m} n={n} k={k}")
+
+
 @pytest.mark.parametrize("shape", [(2048, 4096, 1024), (1100, 5000, 520), (2048, 6144, 136), (4096, 2560, 64)])
 def test_linear_on_pairs_of_sms(ops, shape):
     """Outputs with many 256 x 256 tiles run on pairs of SMs (tcgen05 cta_group::2): same bits as

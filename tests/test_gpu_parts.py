@@ -161,6 +161,7 @@ def test_feed_forward_part_alone(ops, dtype, rtol):
     base = _w((11, 72), 10, scale=1.0)
     res = base.clone().to(DEV)
     ffn.forward(ops, h.to(DEV), res, None)
+    ops.flush()                            # (the part lets its last product wait for what follows)
     _close(res, base.to(F64) + y @ w["down_proj.weight"].to(F64).T, rtol, "swiglu part")
 
 

@@ -339,7 +339,7 @@ int choose_splits(int m, int n, int k, int mode, int sms) {
 // width: the tiles' columns, 256, 128 or 64
 int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c, void* out_act, int m, int n,
                  int k, int lda, int ldw, int ldc, int ld_act, int mode, int width, float* ws, int splits,
-                 int* status, void* stream) {
+                 int* status, void* stream, bool add_runs = true) {
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -377,7 +377,7 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
                       splits, status);
     }
     if (int rc = ti_check_launch("gemm_tcgen05")) return rc;
-    if (splits > 1) {
+    if (splits > 1 && add_runs) {
         const long long quads = (long long)m * (n / 4);
         ti_launch_pdl(gemm_split_merge_kernel, (unsigned)((quads + 255) / 256), 256, 0, (cudaStream_t)stream,
                       (const float*)ws, c, m, n, ldc, splits, mode == MODE_ACCUMULATE ? 1 : 0);
@@ -403,11 +403,25 @@ extern "C" int ti_gemm_tcgen05_splits(int m, int n, int k, int mode) {
     return sms > 0 && m > 0 && n > 0 ? choose_splits(m, n, k, mode, sms) : 1;
 }
 
+// c (+)= the runs' slabs ws[run][m][n] of a product that was launched with `leave_runs`.
+extern "C" int ti_gemm_tcgen05_add_runs(const float* ws, float* c, int m, int n, int ldc, int runs,
+                                        int accumulate, void* stream) {
+    if (m == 0 || n == 0 || runs < 1) return 0;
+    TI_REQUIRE(n % 4 == 0 && ldc % 4 == 0 && (uintptr_t)ws % 16 == 0 && (uintptr_t)c % 16 == 0,
+               "gemm_tcgen05_add_runs: N=%d and the row stride %d must be multiples of 4", n, ldc);
+    const long long quads = (long long)m * (n / 4);
+    ti_launch_pdl(gemm_split_merge_kernel, (unsigned)((quads + 255) / 256), 256, 0, (cudaStream_t)stream, ws, c, m,
+                  n, ldc, runs, accumulate ? 1 : 0);
+    return ti_check_launch("gemm_split_merge");
+}
+
 // mode 0: c = a w^T; 1: c += a w^T; 2: out_act[m, n/2] = SwiGLU over groups of 8 gate + 8 up columns.
 // ws: null, or the scratch for ti_gemm_tcgen05_splits(m, n, k, mode) runs of K (16-byte aligned).
+// leave_runs: with K cut, do not add the runs into c; the caller does (ti_gemm_tcgen05_add_runs, or
+// a norm that completes its rows from the slabs).
 extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out_act, int m, int n,
                                int k, int lda, int ldw, int ldc, int ld_act, int mode, float* ws,
-                               int* status, void* stream) {
+                               int leave_runs, int* status, void* stream) {
     if (m == 0 || n == 0) return 0;
     TI_REQUIRE(mode >= MODE_STORE && mode <= MODE_SWIGLU, "gemm_tcgen05: mode %d", mode);
     TI_REQUIRE(ti_gemm_tcgen05_supported(m, n, k, lda, ldw, ldc, mode),
@@ -427,7 +441,7 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     if (splits > 1) {
         TI_REQUIRE((uintptr_t)ws % 16 == 0, "gemm_tcgen05: the scratch must be 16-byte aligned");
         return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, 128, ws,
-                            splits, status, stream);
+                            splits, status, stream, !leave_runs);
     }
     const int width = tiles_m * ((n + 255) / 256) >= sms ? 256 : tiles_m * ((n + 127) / 128) * 2 >= sms ? 128 : 64;
     return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, width, nullptr, 1,

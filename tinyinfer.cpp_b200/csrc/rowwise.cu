@@ -124,10 +124,16 @@ rmsnorm_warp_reg_kernel(const float* __restrict__ x, const float* __restrict__ w
 // 16 * THREADS: a thread keeps its up to four 16-byte pieces of the row in registers, so the row
 // is read once and all loads are in flight together; the weights are fetched before the wait on
 // the previous kernel.
+//
+// With `ws` (rows == null): the row is first completed from the slabs of a product whose K was cut
+// into `runs` (gemm_tcgen05.cu): x[r] = (accumulate ? x[r] : 0) + (ws[0][r] + ws[1][r] + ...), the
+// slabs added in ascending order as that product's own adding launch does, and written back; the
+// norm is then of the completed row (one launch and one pass over the rows less).
 template <typename TO, int THREADS>
 __global__ void __launch_bounds__(THREADS)
-rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
-                   float eps, int n, TO* __restrict__ out) {
+rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                   float eps, int n, TO* __restrict__ out, const float* __restrict__ ws, int runs,
+                   size_t slab, int accumulate) {
     __shared__ float scratch[32];
     pdl_launch();
     const int n4 = n >> 2;
@@ -140,12 +146,27 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, con
     }
     pdl_wait();
     const int r = blockIdx.x;
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)(rows ? rows[r] : r) * n);
     float ss = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int i = threadIdx.x + j * THREADS;
-        if (i < n4) v[j] = xr[i];
+        if (i < n4) v[j] = ws == nullptr || accumulate ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (ws != nullptr) {
+        const float4* part = reinterpret_cast<const float4*>(ws + (size_t)r * n);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * THREADS;
+            if (i >= n4) continue;
+            float4 sum = __ldcg(part + i);
+            for (int k = 1; k < runs; ++k) {
+                const float4 p = __ldcg(reinterpret_cast<const float4*>(ws + k * slab + (size_t)r * n) + i);
+                sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+            }
+            v[j] = make_float4(v[j].x + sum.x, v[j].y + sum.y, v[j].z + sum.z, v[j].w + sum.w);
+            xr[i] = v[j];
+        }
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -328,13 +349,17 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
         // few rows: a block per row that keeps the row in registers
         const bool small = n <= 16 * 256;
         if (out_dtype == TI_BF16 && small)
-            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256>, num_rows, 256, 0, s, x, weight, rows, eps, n, (bf16*)out);
+            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256>, num_rows, 256, 0, s, (float*)x, weight, rows, eps, n, (bf16*)out,
+                          (const float*)nullptr, 0, (size_t)0, 0);
         else if (out_dtype == TI_BF16)
-            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 1024>, num_rows, 1024, 0, s, x, weight, rows, eps, n, (bf16*)out);
+            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 1024>, num_rows, 1024, 0, s, (float*)x, weight, rows, eps, n, (bf16*)out,
+                          (const float*)nullptr, 0, (size_t)0, 0);
         else if (small)
-            ti_launch_pdl(rmsnorm_vec_kernel<float, 256>, num_rows, 256, 0, s, x, weight, rows, eps, n, (float*)out);
+            ti_launch_pdl(rmsnorm_vec_kernel<float, 256>, num_rows, 256, 0, s, (float*)x, weight, rows, eps, n, (float*)out,
+                          (const float*)nullptr, 0, (size_t)0, 0);
         else
-            ti_launch_pdl(rmsnorm_vec_kernel<float, 1024>, num_rows, 1024, 0, s, x, weight, rows, eps, n, (float*)out);
+            ti_launch_pdl(rmsnorm_vec_kernel<float, 1024>, num_rows, 1024, 0, s, (float*)x, weight, rows, eps, n, (float*)out,
+                          (const float*)nullptr, 0, (size_t)0, 0);
         return ti_check_launch("rmsnorm");
     }
     const int threads = n >= 1024 ? 256 : 128;
@@ -345,6 +370,27 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
     else
         return ti_fail("rmsnorm: output dtype code %d is not float32 or bfloat16", out_dtype);
     return ti_check_launch("rmsnorm");
+}
+
+// rmsnorm of rows that are first completed from the `runs` slabs ws[run][num_rows][n] of a
+// product whose K was cut (see rmsnorm_vec_kernel); x is written.  Returns -1, launching nothing,
+// for sizes this form does not take (the caller then adds and norms in turn).
+extern "C" int ti_rmsnorm_merge(float* x, const float* ws, int runs, int accumulate, const float* weight,
+                                int num_rows, int n, float eps, void* out, int out_dtype, void* stream) {
+    if (num_rows == 0) return 0;
+    if (!(n % 4 == 0 && n <= 16 * 1024 && out_dtype == TI_BF16 && num_rows < 1024 && runs >= 1 &&
+          (uintptr_t)x % 16 == 0 && (uintptr_t)ws % 16 == 0 && (uintptr_t)weight % 16 == 0 &&
+          (uintptr_t)out % 16 == 0))
+        return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t slab = (size_t)num_rows * n;
+    if (n <= 16 * 256)
+        ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256>, num_rows, 256, 0, s, x, weight, (const int*)nullptr, eps, n,
+                      (bf16*)out, ws, runs, slab, accumulate);
+    else
+        ti_launch_pdl(rmsnorm_vec_kernel<bf16, 1024>, num_rows, 1024, 0, s, x, weight, (const int*)nullptr, eps, n,
+                      (bf16*)out, ws, runs, slab, accumulate);
+    return ti_check_launch("rmsnorm_merge");
 }
 
 extern "C" int ti_swiglu(const float* gu, int num_tokens, int inter, int interleaved, void* out,

@@ -110,6 +110,10 @@ class CudaOps:
         # a product of many rows whose output has few tiles (a short prompt portion into a narrow
         # output): K cut into runs, added by a second launch
         self.split_k_portions = True
+        # ... and when the norm of the output follows at once (``may_defer``), that norm adds the
+        # runs as it reads its rows: one launch and one pass over the rows less
+        self.norm_adds_runs = True
+        self._pending_runs = None         # (scratch, runs, out, accumulate) of a product whose runs are not added yet
         # the feed-forward of a decode step of at most 16 rows as one launch, when a layer's
         # feed-forward weights fit into the GPU's shared memory (csrc/ffn_decode.cu); same bits as
         # the two products it replaces
@@ -135,6 +139,7 @@ class CudaOps:
         c = self.core
         c.ti_embed.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp]
         c.ti_rmsnorm.argtypes = [_vp, _vp, _vp, _i, _i, _f, _vp, _i, _vp]
+        c.ti_rmsnorm_merge.argtypes = [_vp, _vp, _i, _i, _vp, _i, _i, _f, _vp, _i, _vp]
         c.ti_swiglu.argtypes = [_vp, _i, _i, _i, _vp, _i, _vp]
         c.ti_argmax.argtypes = [_vp, _i, _i, _vp, _vp]
         c.ti_argmax_sliced.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _vp]
@@ -171,7 +176,8 @@ class CudaOps:
             b.ti_attn_decode_qkv_supported.argtypes = [_i, _i, _i]
             b.ti_attn_decode_qkv.argtypes = [_vp, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i,
                                              _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]
-            b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]
+            b.ti_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
+            b.ti_gemm_tcgen05_add_runs.argtypes = [_vp, _vp, _i, _i, _i, _i, _i, _vp]
             b.ti_gemm_tcgen05_splits.argtypes = [_i, _i, _i, _i]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
@@ -253,7 +259,7 @@ class CudaOps:
             return self.bf16.ti_gemm_tcgen05_2sm
         return self.bf16.ti_gemm_tcgen05
 
-    def _run_tc_gemm(self, a, w, c, out_act, m, n, k, ldc, ld_act, mode) -> None:
+    def _run_tc_gemm(self, a, w, c, out_act, m, n, k, ldc, ld_act, mode, may_defer=False) -> None:
         """The tcgen05 product of many rows; an output of few tiles has its K cut into runs that a
         second launch adds (the one-SM kernel decides, this side brings the scratch)."""
         fn = self._tc_gemm(m, n)
@@ -263,8 +269,13 @@ class CudaOps:
             return
         runs = int(self.bf16.ti_gemm_tcgen05_splits(m, n, k, mode)) if self.split_k_portions else 1
         ws = torch.empty(runs * m * n, dtype=torch.float32, device=a.device) if runs > 1 else None
+        leave = bool(runs > 1 and may_defer and self.norm_adds_runs and c is not None and c.is_contiguous())
         self._ok(fn(a.data_ptr(), w.data_ptr(), _ptr(c), _ptr(out_act), m, n, k, a.stride(0), w.stride(0),
-                    ldc, ld_act, mode, _ptr(ws), self.status.data_ptr(), self._stream()), self.bf16)
+                    ldc, ld_act, mode, _ptr(ws), int(leave), self.status.data_ptr(), self._stream()), self.bf16)
+        if leave:
+            self._pending_runs = (ws, runs, c, mode == 1)
+        elif runs > 1:
+            self.launches += 1            # the launch that adds the runs
 
     def _few_tc(self, a, w, c, out_act, mode) -> bool:
         """Runs the split-K tcgen05 product for few rows if it applies to these operands."""
@@ -313,6 +324,22 @@ class CudaOps:
                                     self._stream()))
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
+        pr = self._pending_runs
+        if pr is not None:
+            self._pending_runs = None
+            ws, runs, c, accumulate = pr
+            rc = -1
+            if (rows is None and x is c and out.dtype == torch.bfloat16 and out.is_contiguous()
+                    and weight.dtype == torch.float32 and weight.shape[0] == x.shape[1] == out.shape[1]
+                    and out.shape[0] == x.shape[0]):
+                rc = self.core.ti_rmsnorm_merge(x.data_ptr(), ws.data_ptr(), runs, int(accumulate),
+                                                weight.data_ptr(), x.shape[0], x.shape[1], float(eps),
+                                                out.data_ptr(), _code(out, "rmsnorm"), self._stream())
+            if rc == -1:                  # not a norm of that output, or sizes the fused form does not take
+                self._add_runs(pr)
+            else:
+                self._ok(rc)
+                return
         p = self._pending
         if p is not None:
             if (p.get("norm") is None and rows is None and x is p["out"] and out.dtype == torch.bfloat16
@@ -333,8 +360,16 @@ class CudaOps:
                                       x.shape[1], float(eps), out.data_ptr(),
                                       _code(out, "rmsnorm"), self._stream()))
 
+    def _add_runs(self, pr) -> None:
+        ws, runs, c, accumulate = pr
+        self._ok(self.bf16.ti_gemm_tcgen05_add_runs(ws.data_ptr(), c.data_ptr(), c.shape[0], c.shape[1],
+                                                    c.stride(0), runs, int(accumulate), self._stream()), self.bf16)
+
     def flush(self) -> None:
         """Launch what ``linear(..., may_defer=True)`` and a norm after it have held back."""
+        pr, self._pending_runs = self._pending_runs, None
+        if pr is not None:
+            self._add_runs(pr)
         p, self._pending = self._pending, None
         if p is None:
             return
@@ -349,7 +384,7 @@ class CudaOps:
         that follow immediately; any other operation of the kernel set, ``stream()`` and
         ``flush()`` launch it first.  The caller must not touch ``a`` or ``out`` by other means
         until then."""
-        if self._pending is not None:
+        if self._pending is not None or self._pending_runs is not None:
             self.flush()
         m, k = a.shape
         n = w.shape[0]
@@ -375,7 +410,7 @@ class CudaOps:
             if (m > 64 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and
                     out.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                         m, n, k, a.stride(0), w.stride(0), out.stride(0), mode)):
-                self._run_tc_gemm(a, w, out, None, m, n, k, out.stride(0), 0, mode)
+                self._run_tc_gemm(a, w, out, None, m, n, k, out.stride(0), 0, mode, may_defer=may_defer)
                 return
         self._ok(self.core.ti_gemm_simple(
             a.data_ptr(), _code(a, "linear"), w.data_ptr(), _code(w, "linear"), out.data_ptr(),
@@ -407,8 +442,10 @@ class CudaOps:
         self._ok(self.core.ti_swiglu(gu.data_ptr(), m, inter, int(interleaved), out.data_ptr(),
                                      _code(out, "swiglu"), self._stream()))
 
-    def swiglu_ffn(self, h, w_gate_up, w_down, residual):
-        """residual += (silu(h Wgate^T) * (h Wup^T)) Wdown^T, with ``w_gate_up`` from pack_gate_up."""
+    def swiglu_ffn(self, h, w_gate_up, w_down, residual, may_defer=False):
+        """residual += (silu(h Wgate^T) * (h Wup^T)) Wdown^T, with ``w_gate_up`` from pack_gate_up.
+        ``may_defer`` as for ``linear``: the last product may be held back (or its runs of K left
+        unadded) for what follows, until the next operation or ``flush()``."""
         m, k = h.shape
         inter = w_down.shape[1]
         _need(w_gate_up.shape == (2 * inter, k) and w_down.shape[0] == residual.shape[1] == k
@@ -451,7 +488,7 @@ class CudaOps:
                 self._stream()), self.bf16)
             return
         self.gate_up_swiglu(h, w_gate_up, y)
-        self.linear(y, w_down, residual, accumulate=True)
+        self.linear(y, w_down, residual, accumulate=True, may_defer=may_defer)
 
     # ---- attention -----------------------------------------------------------------------
     def register_rotation(self, kind: str, handler) -> None:
@@ -767,7 +804,7 @@ def _flush_first(fn):
 
     @functools.wraps(fn)
     def wrapper(self, *args, **kwargs):
-        if self._pending is not None:
+        if self._pending is not None or self._pending_runs is not None:
             self.flush()
         return fn(self, *args, **kwargs)
     return wrapper

@@ -35,7 +35,7 @@ class SwiGLU(Part):
         self.w_down = ops.pack_linear(tensors["down_proj.weight"])
 
     def forward(self, ops, h, residual, step):
-        ops.swiglu_ffn(h, self.w_gate_up, self.w_down, residual)
+        ops.swiglu_ffn(h, self.w_gate_up, self.w_down, residual, may_defer=True)
 
 
 register_part("ffn", "swiglu", SwiGLU)
