@@ -129,7 +129,7 @@ rmsnorm_warp_reg_kernel(const float* __restrict__ x, const float* __restrict__ w
 // into `runs` (gemm_tcgen05.cu): x[r] = (accumulate ? x[r] : 0) + (ws[0][r] + ws[1][r] + ...), the
 // slabs added in ascending order as that product's own adding launch does, and written back; the
 // norm is then of the completed row (one launch and one pass over the rows less).
-template <typename TO, int THREADS>
+template <typename TO, int THREADS, bool ADD_RUNS = false>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
                    float eps, int n, TO* __restrict__ out, const float* __restrict__ ws, int runs,
@@ -151,9 +151,9 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int i = threadIdx.x + j * THREADS;
-        if (i < n4) v[j] = ws == nullptr || accumulate ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < n4) v[j] = !ADD_RUNS || accumulate ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
-    if (ws != nullptr) {
+    if constexpr (ADD_RUNS) {
         const float4* part = reinterpret_cast<const float4*>(ws + (size_t)r * n);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -385,10 +385,10 @@ extern "C" int ti_rmsnorm_merge(float* x, const float* ws, int runs, int accumul
     cudaStream_t s = (cudaStream_t)stream;
     const size_t slab = (size_t)num_rows * n;
     if (n <= 16 * 256)
-        ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256>, num_rows, 256, 0, s, x, weight, (const int*)nullptr, eps, n,
+        ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256, true>, num_rows, 256, 0, s, x, weight, (const int*)nullptr, eps, n,
                       (bf16*)out, ws, runs, slab, accumulate);
     else
-        ti_launch_pdl(rmsnorm_vec_kernel<bf16, 1024>, num_rows, 1024, 0, s, x, weight, (const int*)nullptr, eps, n,
+        ti_launch_pdl(rmsnorm_vec_kernel<bf16, 1024, true>, num_rows, 1024, 0, s, x, weight, (const int*)nullptr, eps, n,
                       (bf16*)out, ws, runs, slab, accumulate);
     return ti_check_launch("rmsnorm_merge");
 }
