@@ -129,7 +129,7 @@ rmsnorm_warp_reg_kernel(const float* __restrict__ x, const float* __restrict__ w
 // into `runs` (gemm_tcgen05.cu): x[r] = (accumulate ? x[r] : 0) + (ws[0][r] + ws[1][r] + ...), the
 // slabs added in ascending order as that product's own adding launch does, and written back; the
 // norm is then of the completed row (one launch and one pass over the rows less).
-template <typename TO, int THREADS, bool ADD_RUNS = false>
+template <typename TO, int THREADS, bool ADD_RUNS = false, int PIECES = 4>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
                    float eps, int n, TO* __restrict__ out, const float* __restrict__ ws, int runs,
@@ -138,9 +138,9 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int
     pdl_launch();
     const int n4 = n >> 2;
     const float4* w4 = reinterpret_cast<const float4*>(w);
-    float4 g[4], v[4];
+    float4 g[PIECES], v[PIECES];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PIECES; ++j) {
         const int i = threadIdx.x + j * THREADS;
         if (i < n4) g[j] = w4[i];
     }
@@ -149,14 +149,14 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int
     float4* xr = reinterpret_cast<float4*>(x + (size_t)(rows ? rows[r] : r) * n);
     float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PIECES; ++j) {
         const int i = threadIdx.x + j * THREADS;
         if (i < n4) v[j] = !ADD_RUNS || accumulate ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     if constexpr (ADD_RUNS) {
         const float4* part = reinterpret_cast<const float4*>(ws + (size_t)r * n);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < PIECES; ++j) {
             const int i = threadIdx.x + j * THREADS;
             if (i >= n4) continue;
             float4 sum = __ldcg(part + i);
@@ -169,7 +169,7 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int
         }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PIECES; ++j) {
         if (threadIdx.x + j * THREADS < n4) {
             ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
             ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
@@ -178,7 +178,7 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
     TO* o = out + (size_t)r * n;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PIECES; ++j) {
         const int i = threadIdx.x + j * THREADS;
         if (i >= n4) continue;
         const float4 y = make_float4(v[j].x * inv * g[j].x, v[j].y * inv * g[j].y, v[j].z * inv * g[j].z,
@@ -348,7 +348,12 @@ extern "C" int ti_rmsnorm(const float* x, const float* weight, const int* rows, 
         (uintptr_t)x % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0) {
         // few rows: a block per row that keeps the row in registers
         const bool small = n <= 16 * 256;
-        if (out_dtype == TI_BF16 && small)
+        if (out_dtype == TI_BF16 && n <= 4 * 256)
+            // one piece of the row per thread (the same sums in the same order: the other pieces
+            // are empty): the short kernel a small model's decode step waits for twice a layer
+            ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256, false, 1>, num_rows, 256, 0, s, (float*)x, weight, rows, eps, n,
+                          (bf16*)out, (const float*)nullptr, 0, (size_t)0, 0);
+        else if (out_dtype == TI_BF16 && small)
             ti_launch_pdl(rmsnorm_vec_kernel<bf16, 256>, num_rows, 256, 0, s, (float*)x, weight, rows, eps, n, (bf16*)out,
                           (const float*)nullptr, 0, (size_t)0, 0);
         else if (out_dtype == TI_BF16)
