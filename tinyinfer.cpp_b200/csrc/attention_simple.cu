@@ -102,7 +102,7 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
 // The same work for head sizes up to 64 * VEC with head_dim / 2 a multiple of VEC: a lane keeps
 // VEC consecutive elements of each half of the vector in registers (the rotation pairs element
 // k with k + head_dim / 2, so a lane owns whole pairs); no shared memory.
-template <typename TQ, typename TC, int VEC>
+template <typename TQ, typename TC, int VEC, int MAX_TURNS = 8>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
                               const float* __restrict__ q_weight, const float* __restrict__ k_weight,
@@ -125,8 +125,8 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
     pdl_wait();
     __syncthreads();
     // With many tokens a warp takes up to MAX_TURNS vectors, so that blocks are not tiny; all of
-    // their loads are issued before any of them is used.
-    constexpr int MAX_TURNS = 8;
+    // their loads are issued before any of them is used.  (MAX_TURNS = 1: the short kernel of a
+    // decode step.)
     const int items = num_heads + 2 * num_kv_heads;
     const int k0 = lane * VEC;
     const bool active = k0 < half;
@@ -318,7 +318,12 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
     const int vec = rotary_dim != head_dim ? 0
                     : (half % 4 == 0 && half > 64) ? 4 : (half % 2 == 0 && half <= 64) ? 2 : 0;
 #define CALL(TQ, TC)                                                                          \
-    if (vec == 2)                                                                             \
+    if (vec == 2 && ipw == 1)                                                                 \
+        ti_launch_pdl((qk_norm_rope_store_vec_kernel<TQ, TC, 2, 1>), vgrid, WARPS * 32, 0, s,  \
+            qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
+            bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
+            head_dim, ipw, (TQ*)q_out, status);                                                \
+    else if (vec == 2)                                                                        \
         ti_launch_pdl(qk_norm_rope_store_vec_kernel<TQ, TC, 2>, vgrid, WARPS * 32, 0, s,       \
             qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
             bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
