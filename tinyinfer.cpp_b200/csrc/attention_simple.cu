@@ -102,7 +102,7 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
 // The same work for head sizes up to 64 * VEC with head_dim / 2 a multiple of VEC: a lane keeps
 // VEC consecutive elements of each half of the vector in registers (the rotation pairs element
 // k with k + head_dim / 2, so a lane owns whole pairs); no shared memory.
-template <typename TQ, typename TC, int VEC, int MAX_TURNS = 8>
+template <typename TQ, typename TC, int VEC>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
                               const float* __restrict__ q_weight, const float* __restrict__ k_weight,
@@ -125,8 +125,9 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
     pdl_wait();
     __syncthreads();
     // With many tokens a warp takes up to MAX_TURNS vectors, so that blocks are not tiny; all of
-    // their loads are issued before any of them is used.  (MAX_TURNS = 1: the short kernel of a
-    // decode step.)
+    // their loads are issued before any of them is used.  (Few tokens take
+    // qk_norm_rope_store_one_kernel below.)
+    constexpr int MAX_TURNS = 8;
     const int items = num_heads + 2 * num_kv_heads;
     const int k0 = lane * VEC;
     const bool active = k0 < half;
@@ -197,6 +198,101 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
                 dst[k0 + i] = from_f32<TC>(y0);
                 dst[half + k0 + i] = from_f32<TC>(y1);
             }
+        }
+    }
+}
+
+// The same work for the few tokens of a decode step, one vector per warp: everything that does
+// not come from the kernel before (the token's position and page, its sines and cosines, the norm
+// weights) is in registers before the wait for that kernel returns, so that behind the wait
+// there is one round of loads, the norm, the rotation and the stores.  Arithmetic and order are
+// those of qk_norm_rope_store_vec_kernel.
+template <typename TQ, typename TC, int VEC>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_one_kernel(const float* __restrict__ qkv, int qkv_stride,
+                              const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                              float eps, const float* __restrict__ inv_freq,
+                              const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                              const int* __restrict__ block_table, int bt_stride,
+                              TC* __restrict__ pages, int num_pages, int page_size, int write_kv,
+                              int num_heads, int num_kv_heads, int head_dim,
+                              TQ* __restrict__ q_out, int* __restrict__ status) {
+    pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int items = num_heads + 2 * num_kv_heads;
+    const int item = blockIdx.y * WARPS + warp;
+    const int k0 = lane * VEC;
+    const bool active = k0 < half, live = item < items;
+    // the vectors of a token lie one after the other: query heads, key heads, value heads
+    const int kind = item < num_heads ? 0 : item < num_heads + num_kv_heads ? 1 : 2;
+    const int head = kind == 0 ? item : kind == 1 ? item - num_heads : item - num_heads - num_kv_heads;
+    const int pos = positions[t];
+    int page = -1;
+    if (write_kv && kind != 0 && live) {
+        page = block_table[(size_t)req_of_tok[t] * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+            page = -1;
+        }
+    }
+    float sn[VEC], cs[VEC], w0[VEC], w1[VEC];
+    if (live && active && kind != 2) {
+        const float* w = kind == 0 ? q_weight : k_weight;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            sincosf((float)pos * inv_freq[k0 + i], &sn[i], &cs[i]);
+            w0[i] = w[k0 + i];
+            w1[i] = w[half + k0 + i];
+        }
+    }
+    pdl_wait();
+    if (!live) return;
+    float lo[VEC], hi[VEC];
+    const float* src = qkv + (size_t)t * qkv_stride + (size_t)item * head_dim;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        lo[i] = active ? src[k0 + i] : 0.0f;
+        hi[i] = active ? src[half + k0 + i] : 0.0f;
+    }
+    if (kind != 0 && page < 0) return;
+    TC* dst = nullptr;
+    if (kind != 0)
+        dst = pages + ((((size_t)page * 2 + (kind - 1)) * num_kv_heads + head) * page_size +
+                       pos % page_size) * head_dim;
+    if (kind == 2) {
+        if (active) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                dst[k0 + i] = from_f32<TC>(lo[i]);
+                dst[half + k0 + i] = from_f32<TC>(hi[i]);
+            }
+        }
+        return;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        ss = fmaf(lo[i], lo[i], ss);
+        ss = fmaf(hi[i], hi[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+    if (!active) return;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const float x0 = lo[i] * inv * w0[i];
+        const float x1 = hi[i] * inv * w1[i];
+        const float y0 = x0 * cs[i] - x1 * sn[i];
+        const float y1 = x0 * sn[i] + x1 * cs[i];
+        if (kind == 0) {
+            TQ* q = q_out + ((size_t)t * num_heads + head) * head_dim;
+            q[k0 + i] = from_f32<TQ>(y0);
+            q[half + k0 + i] = from_f32<TQ>(y1);
+        } else {
+            dst[k0 + i] = from_f32<TC>(y0);
+            dst[half + k0 + i] = from_f32<TC>(y1);
         }
     }
 }
@@ -319,10 +415,15 @@ extern "C" int ti_qk_norm_rope_store(const float* qkv, int qkv_stride, const flo
                     : (half % 4 == 0 && half > 64) ? 4 : (half % 2 == 0 && half <= 64) ? 2 : 0;
 #define CALL(TQ, TC)                                                                          \
     if (vec == 2 && ipw == 1)                                                                 \
-        ti_launch_pdl((qk_norm_rope_store_vec_kernel<TQ, TC, 2, 1>), vgrid, WARPS * 32, 0, s,  \
+        ti_launch_pdl((qk_norm_rope_store_one_kernel<TQ, TC, 2>), vgrid, WARPS * 32, 0, s,     \
             qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
             bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
-            head_dim, ipw, (TQ*)q_out, status);                                                \
+            head_dim, (TQ*)q_out, status);                                                     \
+    else if (vec == 4 && ipw == 1)                                                            \
+        ti_launch_pdl((qk_norm_rope_store_one_kernel<TQ, TC, 4>), vgrid, WARPS * 32, 0, s,     \
+            qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
+            bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads,     \
+            head_dim, (TQ*)q_out, status);                                                     \
     else if (vec == 2)                                                                        \
         ti_launch_pdl(qk_norm_rope_store_vec_kernel<TQ, TC, 2>, vgrid, WARPS * 32, 0, s,       \
             qkv, qkv_stride, q_weight, k_weight, eps, inv_freq, positions, req_of_tok, block_table, \
