@@ -20,7 +20,7 @@ enum { TI_ERR_BAD_PAGE = 1 };
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(WARPS * 32)
-qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
+qk_norm_rope_store_kernel(const float* qkv, int qkv_stride,
                           const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                           float eps, const float* __restrict__ inv_freq,
                           const int* __restrict__ positions, const int* __restrict__ req_of_tok,
@@ -104,7 +104,7 @@ qk_norm_rope_store_kernel(const float* __restrict__ qkv, int qkv_stride,
 // k with k + head_dim / 2, so a lane owns whole pairs); no shared memory.
 template <typename TQ, typename TC, int VEC>
 __global__ void __launch_bounds__(WARPS * 32)
-qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
+qk_norm_rope_store_vec_kernel(const float* qkv, int qkv_stride,
                               const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                               float eps, const float* __restrict__ inv_freq,
                               const int* __restrict__ positions, const int* __restrict__ req_of_tok,
@@ -209,7 +209,7 @@ qk_norm_rope_store_vec_kernel(const float* __restrict__ qkv, int qkv_stride,
 // those of qk_norm_rope_store_vec_kernel.
 template <typename TQ, typename TC, int VEC>
 __global__ void __launch_bounds__(WARPS * 32)
-qk_norm_rope_store_one_kernel(const float* __restrict__ qkv, int qkv_stride,
+qk_norm_rope_store_one_kernel(const float* qkv, int qkv_stride,
                               const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                               float eps, const float* __restrict__ inv_freq,
                               const int* __restrict__ positions, const int* __restrict__ req_of_tok,

@@ -29,7 +29,7 @@ using namespace attn_decode_core;
 // blocks still to come), so that whoever waits for this kernel has waited for both.
 template <int HD, bool SINGLE, bool LATE_WAIT = false>
 __global__ void __launch_bounds__(32)
-attn_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
+attn_decode_kernel(const bf16* q, const int* __restrict__ rows,
                    const int* __restrict__ positions, const int* __restrict__ req_of_tok,
                    const int* __restrict__ block_table, int bt_stride,
                    const bf16* __restrict__ pages, int num_pages, int page_size,
@@ -94,7 +94,7 @@ constexpr int QKV_MAX_GROUP = 8;           // query heads per kv head that the k
 // memory itself.  No other item reads that key: it lies in the last tile, which one split owns.
 template <int HD>
 __global__ void __launch_bounds__(32)
-attn_decode_qkv_kernel(const float* __restrict__ qkv, int width, const float* __restrict__ q_weight,
+attn_decode_qkv_kernel(const float* qkv, int width, const float* __restrict__ q_weight,
                        const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
                        const int* __restrict__ rows, const int* __restrict__ positions,
                        const int* __restrict__ req_of_tok, const int* __restrict__ block_table, int bt_stride,

@@ -361,8 +361,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // m_s.  A warp per query row, a lane per four elements of the head.
 constexpr int MERGE_ROWS = 16;
 __global__ void __launch_bounds__(MERGE_ROWS * 32)
-attn_prefill_merge_kernel(const int* __restrict__ tiles, const float* __restrict__ part_o,
-                          const float* __restrict__ part_ml, int num_heads, int splits,
+attn_prefill_merge_kernel(const int* __restrict__ tiles, const float* part_o,
+                          const float* part_ml, int num_heads, int splits,
                           bf16* __restrict__ out) {
     pdl_launch();
     const int h = blockIdx.x, tile_id = blockIdx.y;

@@ -38,6 +38,11 @@ struct TiPerDevice {
 // kernel before it in the stream is still running; it must call pdl_wait() before it reads
 // anything that kernel wrote (what it does before that, such as fetching weights, overlaps
 // with the predecessor).  pdl_launch() lets the next kernel's blocks be scheduled early.
+// What the kernel before produced must not reach this kernel through a `const T* __restrict__`
+// parameter: loads from such a parameter count as loads of memory that never changes, and the
+// compiler may move them in front of the wait (it did, in the few-rows product, once its loads
+// of the activations stood directly behind the wait).  Weights and the step's host-written
+// integers may keep the qualifier; activations, partial results and outputs of the chain do not.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::); }
 

@@ -44,7 +44,7 @@ constexpr int SHORT_K = WARPS * CHUNK * 4;     // what four chunks per warp cove
 // for three blocks per SM (384 blocks of a 6,144-row weight then run as one wave instead of 1.3).
 template <int NT, int ROWS, int BATCH>
 __global__ void __launch_bounds__(WARPS * 32, BATCH == 4 && NT == 1 ? 3 : 2)
-gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ c,
+gemm_skinny_kernel(const bf16* a, const bf16* __restrict__ w, float* __restrict__ c,
                    bf16* __restrict__ out_act, int m, int n, int k, int lda, int ldw, int ldc,
                    int ld_act, int mode) {
     constexpr int MP = NT * 8;                                  // padded token count
@@ -78,16 +78,42 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
         }
         // the weights do not depend on the kernel before this one; the activations do
         if (c0 == warp) pdl_wait();
+        if constexpr (NT * BATCH <= 16) {
+            // few tokens: all activations of the batch are requested at once (one round trip to
+            // L2 behind the wait instead of one per chunk)
+            uint4 xr[BATCH][NT];
 #pragma unroll
-        for (int u = 0; u < BATCH; ++u) {
-            const int ch = c0 + u * WARPS;
-            if (ch >= chunks) break;
-            if (ROWS == 8) wh[u] = make_uint4(0u, 0u, 0u, 0u);
+            for (int u = 0; u < BATCH; ++u) {
+                const int ch = c0 + u * WARPS;
+                if (ch < chunks) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const uint4 x = *reinterpret_cast<const uint4*>(a_row[j] + (size_t)ch * CHUNK);
-                mma_bf16(acc[j], wl[u].x, wh[u].x, wl[u].y, wh[u].y, x.x, x.y);
-                mma_bf16(acc[j], wl[u].z, wh[u].z, wl[u].w, wh[u].w, x.z, x.w);
+                    for (int j = 0; j < NT; ++j)
+                        xr[u][j] = *reinterpret_cast<const uint4*>(a_row[j] + (size_t)ch * CHUNK);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+                const int ch = c0 + u * WARPS;
+                if (ch >= chunks) break;
+                if (ROWS == 8) wh[u] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    mma_bf16(acc[j], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xr[u][j].x, xr[u][j].y);
+                    mma_bf16(acc[j], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xr[u][j].z, xr[u][j].w);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+                const int ch = c0 + u * WARPS;
+                if (ch >= chunks) break;
+                if (ROWS == 8) wh[u] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(a_row[j] + (size_t)ch * CHUNK);
+                    mma_bf16(acc[j], wl[u].x, wh[u].x, wl[u].y, wh[u].y, x.x, x.y);
+                    mma_bf16(acc[j], wl[u].z, wh[u].z, wl[u].w, wh[u].w, x.z, x.w);
+                }
             }
         }
     }

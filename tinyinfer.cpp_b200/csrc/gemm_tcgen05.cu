@@ -290,7 +290,7 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 
 // c (+)= the sum of the runs' slabs ws[run][m][n], in ascending order of the run (of K).
 __global__ void __launch_bounds__(256)
-gemm_split_merge_kernel(const float* __restrict__ ws, float* __restrict__ c, int m, int n, int ldc, int splits,
+gemm_split_merge_kernel(const float* ws, float* __restrict__ c, int m, int n, int ldc, int splits,
                         int accumulate) {
     pdl_launch();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // a float4 of the output

@@ -18,7 +18,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 
 // out[r, :] = x[src(r), :] * (1 / sqrt(mean(x^2) + eps)) * w, src(r) = rows ? rows[r] : r
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+__global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w,
                                const int* __restrict__ rows, float eps, int n,
                                TO* __restrict__ out) {
     __shared__ float scratch[32];
@@ -41,7 +41,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // of 4: no shared memory, no block barrier; the second pass reads the row from L1.
 template <typename TO>
 __global__ void __launch_bounds__(256)
-rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
+rmsnorm_warp_kernel(const float* x, const float* __restrict__ w,
                     const int* __restrict__ rows, float eps, int n, int num_rows,
                     TO* __restrict__ out) {
     pdl_launch();
@@ -78,7 +78,7 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
 // of squares runs in the same order as in rmsnorm_warp_kernel.
 template <typename TO>
 __global__ void __launch_bounds__(256)
-rmsnorm_warp_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
+rmsnorm_warp_reg_kernel(const float* x, const float* __restrict__ w,
                         const int* __restrict__ rows, float eps, int n, int num_rows,
                         TO* __restrict__ out) {
     constexpr int MAXV = 16;
@@ -132,7 +132,7 @@ rmsnorm_warp_reg_kernel(const float* __restrict__ x, const float* __restrict__ w
 template <typename TO, int THREADS, bool ADD_RUNS = false, int PIECES = 4>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
-                   float eps, int n, TO* __restrict__ out, const float* __restrict__ ws, int runs,
+                   float eps, int n, TO* __restrict__ out, const float* ws, int runs,
                    size_t slab, int accumulate) {
     __shared__ float scratch[32];
     pdl_launch();
@@ -213,7 +213,7 @@ __device__ __forceinline__ void keep_best(float v, int i, float& bv, int& bi) {
 }
 
 // Row argmax; among equal maxima the lowest index wins.
-__global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+__global__ void argmax_kernel(const float* logits, int vocab, int* __restrict__ out) {
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -248,7 +248,7 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* 
 constexpr int ARGMAX_SLICES = 64;
 
 __global__ void __launch_bounds__(256)
-argmax_slice_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ part_v,
+argmax_slice_kernel(const float* logits, int vocab, float* __restrict__ part_v,
                     int* __restrict__ part_i) {
     __shared__ float sv[8];
     __shared__ int si[8];
@@ -276,7 +276,7 @@ argmax_slice_kernel(const float* __restrict__ logits, int vocab, float* __restri
 }
 
 __global__ void __launch_bounds__(ARGMAX_SLICES)
-argmax_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+argmax_pick_kernel(const float* part_v, const int* part_i,
                    int* __restrict__ out) {
     __shared__ float sv[2];
     __shared__ int si[2];
