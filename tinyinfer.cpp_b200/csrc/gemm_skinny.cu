@@ -42,13 +42,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 constexpr int SHORT_K = WARPS * CHUNK * 4;     // what four chunks per warp cover: 1,024
 // BATCH: chunks of W a warp has in flight.  4 covers K <= 1,024 in one round and leaves registers
 // for three blocks per SM (384 blocks of a 6,144-row weight then run as one wave instead of 1.3).
-template <int NT, int ROWS, int BATCH>
+// STORE_ONLY: the kernel without its other two epilogues (the QKV product of a small model's
+// decode step, which waits for this kernel once a layer: the shorter the kernel the better).
+template <int NT, int ROWS, int BATCH, bool STORE_ONLY = false>
 __global__ void __launch_bounds__(WARPS * 32, BATCH == 4 && NT == 1 ? 3 : 2)
 gemm_skinny_kernel(const bf16* a, const bf16* __restrict__ w, float* __restrict__ c,
                    bf16* __restrict__ out_act, int m, int n, int k, int lda, int ldw, int ldc,
                    int ld_act, int mode) {
     constexpr int MP = NT * 8;                                  // padded token count
     __shared__ float part[WARPS][ROWS][MP + 1];
+    if (STORE_ONLY) mode = MODE_STORE;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
     const int n0 = blockIdx.x * ROWS;
@@ -196,6 +199,10 @@ extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_
         ti_launch_pdl(gemm_skinny_kernel<NT, 8, 8>, (unsigned)((n + 7) / 8), WARPS * 32, 0, s,      \
                       (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, lda, ldw, ldc,    \
                       ld_act, mode);                                                                \
+    else if (k <= SHORT_K && mode == MODE_STORE && NT <= 2)                                         \
+        ti_launch_pdl((gemm_skinny_kernel<NT <= 2 ? NT : 1, 16, 4, true>), (unsigned)((n + STRIP - 1) / STRIP), \
+                      WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
+                      lda, ldw, ldc, ld_act, mode);                                                 \
     else if (k <= SHORT_K)                                                                          \
         ti_launch_pdl(gemm_skinny_kernel<NT, 16, 4>, (unsigned)((n + STRIP - 1) / STRIP),           \
                       WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
