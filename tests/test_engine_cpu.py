@@ -151,3 +151,20 @@ def test_step_lists_are_packed_with_the_step():
         build_lists([lists[0], lists[0]], [1], [0])
     with pytest.raises(TypeError, match="integers"):
         build_lists([StepList("bad", lambda q, s: np.asarray([0.5]))], [1], [0])
+
+
+def test_a_step_is_classed_by_how_far_its_portions_reach_back():
+    """Single tokens never count, however long their context; a portion counts by where it ends."""
+    from tinyinfer_b200.engine.batch import LONG_CONTEXT, SHORT_CONTEXT, build_step_batch, portion_reach
+    assert portion_reach([1, 1], [30000, 9000]) == 0
+    assert portion_reach([512, 1], [SHORT_CONTEXT, 30000]) == 0
+    assert portion_reach([512, 1], [SHORT_CONTEXT + 1, 5]) == 1
+    assert portion_reach([2, 300], [LONG_CONTEXT, 400]) == 1
+    assert portion_reach([2, 300], [LONG_CONTEXT + 1, 400]) == 2
+    assert portion_reach([], []) == 0
+    entries = [StepEntry("a", [1] * 40, []), StepEntry("b", [2], [0])]
+    for start, want in ((0, 0), (SHORT_CONTEXT, 1), (LONG_CONTEXT, 2)):
+        blocks = -(-(start + 40) // 16)
+        batch = build_step_batch(entries, [start, 9000], [[list(range(blocks)), list(range(600))]], [0, 1],
+                                 torch.float32, "cpu")
+        assert batch.portion_reach == want
