@@ -168,3 +168,33 @@ def test_a_step_is_classed_by_how_far_its_portions_reach_back():
         batch = build_step_batch(entries, [start, 9000], [[list(range(blocks)), list(range(600))]], [0, 1],
                                  torch.float32, "cpu")
         assert batch.portion_reach == want
+
+
+def test_which_prompt_attention_kernel_takes_a_step():
+    """The choice between the one-head and the two-heads tcgen05 prompt kernels and the number of
+    runs a tile's keys are cut into follow from the step's shape (B200: 148 SMs)."""
+    from tinyinfer_b200.kernels.cuda_ops import choose_prompt_attention as choose
+    sms = 148
+    # a whole 2,048-token prompt of 16 heads: 256 pairs, one head per block, uncut
+    assert choose(16, 16, sms, reach=1) == (False, 1)
+    # 16,384 tokens: 128 tiles, many pairs per SM: two heads per block
+    assert choose(128, 16, sms, reach=2) == (True, 1)
+    # a fresh 512-token prompt: few key tiles per row, nothing to cut
+    assert choose(4, 16, sms, reach=0) == (False, 1)
+    # a 512-token portion at a context of 4,096: 64 pairs, two runs of one head; four of two heads pay
+    assert choose(4, 16, sms, reach=1) == (True, 4)
+    assert choose(4, 16, sms, reach=1, two_heads_ok=False) == (False, 2)
+    # 1,024 tokens at a middling context: 128 pairs, left alone; far back: two heads, two runs
+    assert choose(8, 16, sms, reach=1) == (False, 1)
+    assert choose(8, 16, sms, reach=2) == (True, 2)
+    # 2,048 tokens far back: two heads, uncut (128 blocks); with a window the walk is short
+    assert choose(16, 16, sms, reach=2) == (True, 1)
+    assert choose(16, 16, sms, reach=2, window=512) == (False, 1)
+    # one tile: at most eight runs
+    assert choose(1, 16, sms, reach=1) == (False, 8)
+    # beside flash-decoding: uncut when its blocks fit on the SMs the uncut kernel leaves free
+    assert choose(4, 16, sms, reach=1, decode_blocks=320) == (False, 1)
+    assert choose(4, 16, sms, reach=1, decode_blocks=504) == (True, 4)
+    # switched off
+    assert choose(4, 16, sms, reach=1, cut_keys=False) == (False, 1)
+    assert choose(128, 16, sms, reach=2, pairs_from=None) == (False, 1)

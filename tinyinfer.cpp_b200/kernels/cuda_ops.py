@@ -63,6 +63,52 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
+MAX_KEY_RUNS = 8            # csrc/attn_prefill_tc.cu takes at most this many runs per tile
+
+
+def choose_prompt_attention(n_tiles: int, num_heads: int, num_sms: int, *, reach: int = 1, window: int = 0,
+                            two_heads_ok: bool = True, pairs_from: Optional[int] = 3, cut_keys: bool = True,
+                            decode_blocks: Optional[int] = None, decode_blocks_per_sm: int = 4):
+    """Which tcgen05 prompt-attention kernel takes a step's portions, and into how many runs the
+    keys of every tile are cut: ``(two heads per block?, runs)``.  It depends on the step's shape
+    alone (``reach``: ``StepBatch.portion_reach``), never on its data.
+
+    * Many tiles per SM (``pairs_from`` (tile, head) pairs per SM or more): two heads of a kv
+      group per block, uncut.
+    * Portions that reach far back (``reach`` 2, no window): every block walks a long row of
+      keys, where the two-heads kernel's shorter time per head and tile counts and its longer
+      start does not (2,048 tokens at a context of 16,384: 350 -> 287 us; at 4,096 the two are
+      equal, below it the one-head kernel wins); with fewer blocks than SMs it cuts the keys.
+    * Fewer (tile, head) pairs than SMs and rows of more than a few key tiles (``reach`` 1):
+      every tile's keys in as many runs as fill the SMs once, a block each, added by a second
+      launch.  With two heads per block a run of a tile takes about 1.5 times as long and there
+      may be twice as many runs; measured, that pays from four runs on (a 512-token portion at a
+      context of 16,384: 101 -> 87 us), while two runs of two heads against the uncut one-head
+      kernel lose at short contexts (1,024 tokens at 2,048: 28 -> 34 us).
+    * ``decode_blocks`` (flash-decoding runs beside the prompt kernel): if all of its blocks
+      find room on the SMs that the uncut one-head kernel leaves free, the keys stay uncut and
+      that kernel's time hides behind them.
+    """
+    def runs_for(blocks: int) -> int:
+        return max(1, min(MAX_KEY_RUNS, num_sms // max(1, blocks)))
+
+    pairs = n_tiles * num_heads
+    two = pairs_from is not None and two_heads_ok and pairs >= pairs_from * num_sms
+    runs = 1
+    if not two and two_heads_ok and reach == 2 and not window and pairs_from is not None:
+        two = True
+        if cut_keys:
+            runs = runs_for(pairs // 2)
+    elif not two and cut_keys and reach >= 1 and pairs < num_sms:
+        runs = runs_for(pairs)
+        runs2 = runs_for(pairs // 2) if two_heads_ok else 0
+        if runs2 > 1.5 * runs and runs2 >= 4:
+            two, runs = True, runs2
+        if decode_blocks is not None and runs > 1 and decode_blocks <= (num_sms - pairs) * decode_blocks_per_sm:
+            two, runs = False, 1
+    return two, runs
+
+
 class CudaOps:
     name = "cuda"
 
@@ -697,41 +743,15 @@ class CudaOps:
                 n_tiles = tiles.shape[0]
                 pairs_ok = bool(self.bf16.ti_attn_prefill_tc2_supported(head_dim, cache.page_size, num_heads,
                                                                         num_kv_heads))
-                # many tiles per SM: the kernel that takes two heads of a kv group per block
-                two = (self.tc_attention_pairs_from is not None and pairs_ok
-                       and n_tiles * num_heads >= self.tc_attention_pairs_from * self.num_sms)
-                # Fewer (tile, head) pairs than SMs and rows of more than a few key tiles (a portion of
-                # a long prompt; `portion_reach` 1 or 2): every tile's keys in as many runs as fill the SMs, a block each,
-                # added by a second launch.  With two heads per block a run of a tile takes about
-                # 1.5 times as long and there may be twice as many runs; measured, that pays from
-                # four runs on (a 512-token portion at a context of 16,384: 101 -> 87 us), while two
-                # runs of two heads against the uncut one-head kernel lose at short contexts
-                # (1,024 tokens at 2,048: 28 -> 34 us).
-                runs = 1
-                reach = getattr(step, "portion_reach", 1)   # 0: few key tiles per row, 2: a long walk
-                # Portions that reach far back (the step's `portion_reach` 2): every block walks a
-                # long row of keys, where the two-heads kernel's shorter time per head and tile
-                # counts and its longer start does not (2,048 tokens at a context of 16,384: 350 ->
-                # 287 us; at 4,096 the two are equal, below it the one-head kernel wins); with fewer
-                # blocks than SMs it cuts the keys into runs.
-                if (not two and pairs_ok and reach == 2 and not win
-                        and self.tc_attention_pairs_from is not None):
-                    two = True
-                    if self.split_prompt_keys:
-                        runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2))
-                elif not two and self.split_prompt_keys and reach >= 1 and n_tiles * num_heads < self.num_sms:
-                    runs = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads))
-                    runs2 = int(self.bf16.ti_attn_prefill_tc_splits(n_tiles, num_heads // 2)) if pairs_ok else 0
-                    if runs2 > 1.5 * runs and runs2 >= 4:
-                        two, runs = True, runs2
-                    if beside and runs > 1:
-                        # ... unless all of flash-decoding's blocks find room on the SMs that the
-                        # uncut one-head kernel leaves free: then that kernel's time hides behind them
-                        free = ((self.num_sms - n_tiles * num_heads)
-                                * int(self.bf16.ti_attn_decode_blocks_per_sm(head_dim)))
-                        if n_dec * num_kv_heads * self.decode_splits(
-                                n_dec, num_kv_heads, step.max_position or step.max_ctx_len, head_dim) <= free:
-                            two, runs = False, 1
+                decode_blocks = 0
+                if beside:
+                    decode_blocks = n_dec * num_kv_heads * self.decode_splits(
+                        n_dec, num_kv_heads, step.max_position or step.max_ctx_len, head_dim)
+                two, runs = choose_prompt_attention(
+                    n_tiles, num_heads, self.num_sms, reach=getattr(step, "portion_reach", 1), window=win,
+                    two_heads_ok=pairs_ok, pairs_from=self.tc_attention_pairs_from,
+                    cut_keys=self.split_prompt_keys, decode_blocks=decode_blocks if beside else None,
+                    decode_blocks_per_sm=int(self.bf16.ti_attn_decode_blocks_per_sm(head_dim)))
                 part_o = part_ml = None
                 if runs > 1:
                     part_o = torch.empty((n_tiles, num_heads, runs, big, head_dim), dtype=torch.float32,
